@@ -1,0 +1,55 @@
+"""ctypes binding of libalignedkv_b200.so (the C ABI declared in include/alignedkv_b200.h).
+
+There is no CPU or PyTorch fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libalignedkv_b200.so")
+
+# every symbol include/alignedkv_b200.h declares, with its ctypes signature
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+SIGNATURES = {
+    "akv_abi_version": (_I, []),
+    "akv_last_error": (ctypes.c_char_p, []),
+    "akv_k_cache_save": (_I, [_P] * 4 + [_I] * 8 + [_P]),
+    "akv_k_cache_compute": (_I, [_P] * 7 + [_I] * 7 + [_F, _I, _P]),
+    "akv_v_cache_save": (_I, [_P] * 4 + [_I] * 7 + [_P]),
+    "akv_v_cache_test_compute": (_I, [_P] * 6 + [_I] * 5 + [_P]),
+    "akv_v_cache_compute": (_I, [_P] * 6 + [_I] * 7 + [_P]),
+}
+
+_lib = None
+
+
+class AlignedKVError(RuntimeError):
+    """A C-ABI call returned a negative AKV_ERR_* code."""
+
+    def __init__(self, fn: str, code: int, text: str):
+        super().__init__(f"{fn} failed with code {code}: {text}")
+        self.code = code
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once).  Raises if it has not been built: the product has no fallback path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m alignedkv_b200.build` "
+                "(alignedkv_b200 has no CPU or PyTorch fallback)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(fn: str, code: int) -> None:
+    if code != 0:
+        raise AlignedKVError(fn, code, load().akv_last_error().decode("utf-8", "replace"))

@@ -1,0 +1,100 @@
+/*
+ * alignedkv_b200 - C ABI of the B200-native AlignedKV decode hot path.
+ *
+ * One entry point per operator of the reference's torch extension (extension/csrc/KV_cache_ops.cpp:69-75).
+ * A binding passes raw DEVICE pointers, the reference op's own integer arguments in the reference's order,
+ * and a CUDA stream handle.  Differences from the pybind surface, all forced by a C ABI:
+ *   - outputs the reference allocates with torch::empty are allocated by the caller and passed in;
+ *   - tensor extents the reference reads from a tensor object (v_new.size(1)) are passed as integers;
+ *   - every call returns 0 or a negative AKV_ERR_* code and never throws, allocates or synchronises.
+ * All byte tensors are contiguous with the reference's layouts:
+ *   K planes  first_8 [B,H,n_max_blocks,D,d_block] u8, mid_4 / last_4 [B,H,n_max_blocks,D,d_block/2] u8
+ *             (extension/k_cache_file.py:45-53); adjacent TOKENS share a nibble byte, even token high nibble.
+ *   V planes  first_8 [B,H,max_seq_len,D] u8, mid_4 / last_4 [B,H,max_seq_len,D/2] u8
+ *             (extension/v_cache_file.py:46-54); adjacent CHANNELS share a nibble byte, even channel high nibble.
+ * fp16 tensors cross as bytes, little-endian, exactly as the reference's `.view(torch.uint8)` arguments.
+ * Calls are asynchronous on `stream` (a cudaStream_t cast to void*; NULL = legacy default stream) and are
+ * thread-safe for distinct streams.
+ */
+#ifndef ALIGNEDKV_B200_H
+#define ALIGNEDKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AKV_OK 0
+#define AKV_ERR_NULL (-1)        /* a required pointer is NULL */
+#define AKV_ERR_SHAPE (-2)       /* negative / zero / inconsistent extent, or a shape this build does not cover */
+#define AKV_ERR_ALIGN (-3)       /* a pointer is not aligned as the layout requires (16 bytes for planes) */
+#define AKV_ERR_OVERFLOW (-4)    /* an extent product does not fit the index type */
+#define AKV_ERR_CUDA (-5)        /* the CUDA runtime reported an error at launch; see akv_last_error() */
+
+/* Library version of this ABI (bumped on any signature change). */
+int akv_abi_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* akv_last_error(void);
+
+/*
+ * Replaces k_cache_save (extension/csrc/KV_cache_ops.cpp:5-16; extension/csrc/K_cache.cu:97-164).
+ * Splits fp16 keys k_new [B,seqlen,H,D] into the three K planes.  Same dispatch as the reference:
+ * start_pos==0 or seqlen%d_block==0 -> writes n_blocks blocks starting at block start_pos/d_block (nothing when
+ * n_blocks==0); else seqlen==1 -> writes the single token at position start_pos; any other combination is a
+ * silent no-op that returns AKV_OK.  The high byte is stored, nibbles are ADDED onto the existing plane bytes
+ * (mod 256) as in K_cache.cu:49-56, so planes must start zeroed.
+ */
+int akv_k_cache_save(void* k_first_8, void* k_mid_4, void* k_last_4, const void* k_new,
+                     int bsz, int n_kv_heads, int n_blocks, int n_max_blocks, int d_head, int d_block,
+                     int start_pos, int seqlen, void* stream);
+
+/*
+ * Replaces k_cache_compute (KV_cache_ops.cpp:18-32; K_cache.cu:314-395).
+ * s_out: caller-allocated fp16 bytes [B,H,1,(n_blocks+1)*d_block]; only [..., :n_blocks*d_block] is written,
+ * bit-identical to the reference kernel (fp16 fused multiply-add in channel order, then * half(sqrt_dim)).
+ * kq [B,1,H,D] u8, kqmax [B,1,H,1] u8, q fp16 bytes [B,1,H,D].  `seqlen` is accepted and unused, as in the
+ * reference.  Unlike the reference (which computes only heads below 4*floor(H/4)) every head is computed.
+ * reference!=0 reads every plane.
+ */
+int akv_k_cache_compute(const void* k_first_8, const void* k_mid_4, const void* k_last_4,
+                        const void* kq, const void* kqmax, const void* q, void* s_out,
+                        int bsz, int n_kv_heads, int n_blocks, int n_max_blocks, int d_head, int d_block,
+                        int seqlen, float sqrt_dim, int reference, void* stream);
+
+/*
+ * Replaces v_cache_save (KV_cache_ops.cpp:34-43; extension/csrc/V_cache.cu:44-80).
+ * v_new: fp16 bytes [B,v_new_tokens,H,D]; v_new_tokens is the tensor's own token extent, which the reference
+ * reads as v_new.size(1) (V_cache.cu:65).  Writes tokens [start_pos, start_pos+seq_len) with plain stores.
+ */
+int akv_v_cache_save(void* v_first_8, void* v_mid_4, void* v_last_4, const void* v_new,
+                     int bsz, int n_local_kv_heads, int max_seq_len, int head_dim, int start_pos, int seq_len,
+                     int v_new_tokens, void* stream);
+
+/*
+ * Replaces v_cache_test_compute (KV_cache_ops.cpp:45-54; V_cache.cu:125-168).
+ * test_s_value fp16 bytes [B,H,1,top_max_k], test_s_index int32 bytes [B,H,1,top_max_k],
+ * test_o: caller-allocated fp16 bytes [B,H,1,D].  Row index idx*top_max_k+j is clamped into
+ * [0, max_seq_len-1] (the reference reads out of bounds there).
+ */
+int akv_v_cache_test_compute(const void* v_first_8, const void* v_mid_4, const void* v_last_4,
+                             const void* test_s_value, const void* test_s_index, void* test_o,
+                             int bsz, int n_local_kv_heads, int max_seq_len, int head_dim, int top_max_k,
+                             void* stream);
+
+/*
+ * Replaces v_cache_compute (KV_cache_ops.cpp:56-67; V_cache.cu:310-374).
+ * s: fp16 bytes, row (b,h) starts at half index (b*H+h)*s_last_dim; amin: u8 read flat at b*H+h;
+ * o_out: caller-allocated fp16 bytes [B,H,1,D], bit-identical to the reference kernel (fp16 fused
+ * multiply-add in token order).  reference!=0 reads every plane.
+ */
+int akv_v_cache_compute(const void* v_first_8, const void* v_mid_4, const void* v_last_4,
+                        const void* s, const void* amin, void* o_out,
+                        int bsz, int n_local_kv_heads, int max_seq_len, int head_dim, int s_last_dim,
+                        int start_pos_add_seqlen, int reference, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALIGNEDKV_B200_H */

@@ -1,0 +1,20 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+@pytest.fixture(scope="session")
+def akv_lib():
+    """The C-ABI library, built in-tree if stale (nvcc cross-compiles without a GPU)."""
+    from alignedkv_b200 import _lib, build
+    build.build()
+    return _lib.load()
