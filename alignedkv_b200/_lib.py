@@ -15,6 +15,7 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 SIGNATURES = {
     "akv_abi_version": (_I, []),
     "akv_last_error": (ctypes.c_char_p, []),
+    "akv_set_tuning": (_I, [ctypes.c_char_p, _I]),
     "akv_k_cache_save": (_I, [_P] * 4 + [_I] * 8 + [_P]),
     "akv_k_cache_compute": (_I, [_P] * 7 + [_I] * 7 + [_F, _I, _P]),
     "akv_v_cache_save": (_I, [_P] * 4 + [_I] * 7 + [_P]),

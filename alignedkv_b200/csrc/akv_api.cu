@@ -1,6 +1,7 @@
 // extern "C" surface of libalignedkv_b200: argument validation, error text, dispatch to the launchers.
 #include <stdarg.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "akv_common.cuh"
 
@@ -36,6 +37,9 @@ static DevInfo dev_info() {
     }
     return info;
 }
+static Tuning g_tuning;
+Tuning& tuning() { return g_tuning; }
+
 int sm_count() { return dev_info().sms; }
 int max_dyn_smem() { return dev_info().smem; }
 
@@ -66,6 +70,24 @@ extern "C" {
 int akv_abi_version(void) { return 1; }
 
 const char* akv_last_error(void) { return g_err; }
+
+int akv_set_tuning(const char* key, int value) {
+    g_err[0] = 0;
+    AKV_REQUIRE(key, AKV_ERR_NULL, "set_tuning: null key");
+    Tuning& t = tuning();
+    if (!strcmp(key, "k_kch") && (value == 8 || value == 16)) t.k_kch = value;
+    else if (!strcmp(key, "k_stages") && value >= 3 && value <= 6) t.k_stages = value;
+    else if (!strcmp(key, "k_prefetch") && value >= 0 && value <= 101) t.k_prefetch = value;
+    else if (!strcmp(key, "debug") && value >= 0 && value <= 31) t.debug = value;
+    else if (!strcmp(key, "v_prefetch") && value >= 0 && value <= 64) t.v_prefetch = value;
+    else if (!strcmp(key, "k_wpc") && value >= 0 && value <= 16) t.k_wpc = value;
+    else if (!strcmp(key, "v_stages") && (value == 4 || value == 6 || value == 8)) t.v_stages = value;
+    else {
+        set_error("set_tuning: unknown key or value out of range (%s = %d)", key, value);
+        return AKV_ERR_SHAPE;
+    }
+    return AKV_OK;
+}
 
 int akv_k_cache_save(void* f8, void* m4, void* l4, const void* k_new, int bsz, int H, int n_blocks,
                      int n_max_blocks, int D, int d_block, int start_pos, int seqlen, void* stream) {

@@ -14,6 +14,18 @@ int cuda_status(cudaError_t e, const char* what);
 int sm_count();          // SMs of the current device (cached per device)
 int max_dyn_smem();      // opt-in dynamic shared memory per block of the current device
 
+// Launch-shape knobs (defaults are the measured best on B200); see akv_set_tuning().
+struct Tuning {
+    int k_kch = 16;     // channels per stage of the q.K^T kernel (8 or 16)
+    int k_stages = 3;   // ring depth per warp of the q.K^T kernel (3..6, see launch_k_compute)
+    int k_prefetch = 6; // L2 prefetch distance of the q.K^T kernel in stages (0 = off)
+    int v_prefetch = 8; // L2 prefetch distance of the P.V kernel in stages (0 = off)
+    int debug = 0;      // experiments only: 1 = skip the consumer math, 2 = skip the global copies (wrong results)
+    int k_wpc = 0;      // cap on warps per CTA of the q.K^T kernel (0 = as many as shared memory allows)
+    int v_stages = 6;   // ring depth of the P.V kernel (4, 6 or 8)
+};
+Tuning& tuning();
+
 #define AKV_REQUIRE(cond, code, ...)          \
     do {                                      \
         if (!(cond)) {                        \

@@ -5,29 +5,28 @@
 // fp16 multiply with half(sqrt_dim), and a nibble plane that the alignment rule skips is replaced by the same
 // constants (K_cache.cu:201-205,249-252).
 //
-// Design (B200): the kernel is a pure HBM stream, so it is organised around keeping ~100 KB of loads in flight
-// per SM.  Each WARP owns a private ring of shared-memory stages that it fills with 16-byte asynchronous copies
-// and drains itself - no block-level barrier exists.  A warp works on units of 4 consecutive 64-token blocks of
-// one (batch, head); a stage holds 16 channels of those 4 blocks: 4 x 1 KB of the high-byte plane plus, only for
-// the channels whose alignment code asks for them, the 32-byte rows of the mid / low nibble planes.  The plane
-// bytes that are skipped are never requested from memory.  Lane (tile, i) owns tokens 8i..8i+7 of its tile and
-// keeps four fp16x2 accumulators, so one 8-byte and two 4-byte shared loads feed four FMAs and no cross-lane
-// reduction is needed (which is what keeps the channel-order fp16 sum exact).
+// Design (B200): the kernel is a pure HBM stream.  Each WARP owns a private ring of shared-memory stages that
+// it fills with 16-byte asynchronous copies and drains itself - no block-level barrier exists.  A warp works
+// through a contiguous run of units; a unit is 4 consecutive 64-token blocks of one (batch, head), and a stage
+// holds KCH channels of those 4 blocks: the high-byte rows plus, only for the channels whose alignment code
+// asks for them, the 32-byte rows of the mid / low nibble planes (rows that are skipped are never requested
+// from memory; the producer writes the substitute constants into their slots so that the consumer is
+// branch-free).  Lane (tile, i) owns tokens 8i..8i+7 of its tile and keeps four fp16x2 accumulators: one 8-byte
+// and two 4-byte shared loads feed four FMAs, and no cross-lane reduction exists, which is what keeps the
+// channel-order fp16 sum exact.  Because a B200 needs well over 100 KB in flight per SM to saturate HBM and the
+// rings cannot hold that much, the producer also issues L2 prefetches a few stages ahead of the copies.
 #include "akv_common.cuh"
 
 namespace akv {
 
 namespace kc {
-constexpr int KCH = 16;                          // channels per stage
 constexpr int TILES = 4;                         // 64-token blocks per warp unit
-constexpr int F_TILE = KCH * 64 + 64;            // 1088: +64 staggers tiles across shared-memory banks
-constexpr int N_TILE = KCH * 32 + 32;            // 544
-constexpr int F_BYTES = TILES * F_TILE;          // 4352
-constexpr int N_BYTES = TILES * N_TILE;          // 2176
-constexpr int STAGE = F_BYTES + 2 * N_BYTES;     // 8704
 constexpr int MAX_D = 256;
-constexpr int META = 2 * MAX_D + MAX_D + 64;     // q halves + kq bytes + masks (16 words)
+constexpr int META = 64 + 4 * MAX_D;             // plane-read masks (16 words) + q as duplicated fp16x2 words
 constexpr int NMETA = 3;
+__host__ __device__ constexpr int f_tile(int kch) { return kch * 64 + 64; }   // +64: tiles land on distinct banks
+__host__ __device__ constexpr int n_tile(int kch) { return kch * 32 + 32; }
+__host__ __device__ constexpr int stage_bytes(int kch) { return TILES * f_tile(kch) + 2 * TILES * n_tile(kch); }
 }  // namespace kc
 
 struct KParams {
@@ -39,55 +38,113 @@ struct KParams {
     const uint8_t* q;
     uint8_t* s;
     int BH, nb, nmb, D, ngroups;
-    long long units;
-    uint32_t scale2;  // half(sqrt_dim) in both halves
+    int units, upw;       // total units, units per warp (contiguous run)
+    int pf_dist;          // L2 prefetch distance in stages (0 = off)
+    uint32_t scale2;      // half(sqrt_dim) in both halves
     int reference;
+    int debug;
 };
 
-__device__ __forceinline__ void k_unit_coords(const KParams& p, long long u, int& bh, int& g) {
-    bh = (int)(u / p.ngroups);
-    g = (int)(u - (long long)bh * p.ngroups);
+__device__ __forceinline__ void st_shared_v4(uint32_t a, uint32_t v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p), "r"(bytes) : "memory");
 }
 
-template <int STAGES>
-__global__ void __launch_bounds__(256, 1) k_compute_kernel(const KParams p) {
+__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t a, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar) : "memory");
+}
+
+// Position of a stream of stages (unit, channel chunk) inside one warp's run of units.
+struct KCursor {
+    int u, g, bh, c;          // absolute unit, group inside (batch, head), (batch, head), channel chunk
+    int slot;                 // metadata slot of the current (batch, head)
+    size_t row;               // plane row index of (tile 0 of the unit, first channel of the chunk)
+};
+
+template <int KCH, int STAGES>
+__global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     using namespace kc;
+    constexpr int F_TILE = f_tile(KCH), N_TILE = n_tile(KCH);
+    constexpr int F_BYTES = TILES * F_TILE, N_BYTES = TILES * N_TILE, STAGE = F_BYTES + 2 * N_BYTES;
+    constexpr int F_IT = KCH / 8;                 // 16-byte copies per lane and tile for the high-byte plane
+    constexpr int ROW_LANES = 2 * KCH;            // lanes that cover the nibble rows of one tile
+    constexpr int TILES_PER_IT = 32 / ROW_LANES;  // 1 (KCH 16) or 2 (KCH 8)
+    static_assert(KCH == 8 || KCH == 16, "channels per stage");
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wpc = blockDim.x >> 5;
-    const long long W = (long long)gridDim.x * wpc;
-    const long long w = (long long)blockIdx.x * wpc + warp;
-    if (w >= p.units) return;
-    const long long my_units = (p.units - w + W - 1) / W;
+    const int w = blockIdx.x * wpc + warp;
+    const int u_begin = w * p.upw;
+    if (u_begin >= p.units) return;
+    const int u_end = (u_begin + p.upw < p.units) ? u_begin + p.upw : p.units;
     const int nch = p.D / KCH;
-    const long long total = my_units * nch;
+    const int total = (u_end - u_begin) * nch;
+    const size_t tile_f = (size_t)p.D * 64, tile_n = (size_t)p.D * 32;
 
-    uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META);
+    uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META + 64);
+    const uint32_t mbar_a = smem_u32(ring + STAGES * STAGE + NMETA * META);
+    if (lane == 0) for (int i = 0; i < STAGES; ++i) mbar_init(mbar_a + i * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    __syncwarp();
     uint8_t* meta0 = ring + STAGES * STAGE;
     const uint32_t ring_a = smem_u32(ring);
-    const uint32_t meta_a = smem_u32(meta0);
 
-    // ---- metadata of a unit: q row, kq row (async) and the kqmax byte (register)
-    auto prefetch_meta = [&](long long k) -> uint32_t {
-        int bh, g;
-        k_unit_coords(p, w + k * W, bh, g);
-        const uint32_t m = meta_a + (uint32_t)(k % NMETA) * META;
-        const int qv = p.D >> 3;   // 16-byte pieces of the q row (2*D bytes)
-        const int kv = p.D >> 4;   // 16-byte pieces of the kq row
-        if (lane < qv) cp_async16(m + lane * 16, p.q + (size_t)bh * 2 * p.D + lane * 16);
-        if (lane < kv) cp_async16(m + 2 * MAX_D + lane * 16, p.kq + (size_t)bh * p.D + lane * 16);
-        return (uint32_t)__ldg(p.kqmax + bh);
+    auto cursor_at = [&](int u) {
+        KCursor k;
+        k.u = u;
+        k.bh = u / p.ngroups;
+        k.g = u - k.bh * p.ngroups;
+        k.c = 0;
+        k.slot = 0;
+        k.row = ((size_t)k.bh * p.nmb + (size_t)k.g * TILES) * p.D;
+        return k;
     };
-    // ---- alignment masks of unit k from its staged kq row: bit d of mid/last mask = plane row d is read
-    auto build_masks = [&](long long k, uint32_t top) {
-        uint8_t* m = meta0 + (size_t)(k % NMETA) * META;
-        uint32_t* masks = reinterpret_cast<uint32_t*>(m + 3 * MAX_D);
+    auto advance = [&](KCursor& k) {   // next stage; returns true when a new (batch, head) starts
+        k.row += KCH;
+        if (++k.c < nch) return false;
+        k.c = 0;
+        ++k.u;
+        if (++k.g < p.ngroups) {
+            k.row += (size_t)(TILES - 1) * p.D;          // next 4 tiles of the same (batch, head)
+            return false;
+        }
+        k.g = 0;
+        ++k.bh;
+        k.slot = (k.slot + 1 == NMETA) ? 0 : k.slot + 1;
+        k.row = (size_t)k.bh * p.nmb * p.D;
+        return true;
+    };
+    // Per (batch, head): plane-read masks (bit d set = row d of that plane is read: mid iff
+    // (u8)(kqmax - kq[d]) < 8, low iff < 4; K_cache.cu:211,249-250) and q as fp16x2 words with both halves equal.
+    auto load_meta = [&](int bh, int slot) {
+        uint32_t* masks = reinterpret_cast<uint32_t*>(meta0 + (size_t)slot * META);
+        uint32_t* q2 = masks + 16;
+        const uint32_t top = __ldg(p.kqmax + bh);
         for (int r = 0; r < (p.D + 31) / 32; ++r) {
-            int d = r * 32 + lane;
-            uint32_t diff = 0;
-            if (d < p.D) diff = (top - (uint32_t)m[2 * MAX_D + d]) & 0xFFu;
-            uint32_t mm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 8);
-            uint32_t lm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 4);
+            const int d = r * 32 + lane;
+            uint32_t diff = 0, qh = 0;
+            if (d < p.D) {
+                diff = (top - (uint32_t)__ldg(p.kq + (size_t)bh * p.D + d)) & 0xFFu;
+                qh = __ldg(reinterpret_cast<const uint16_t*>(p.q) + (size_t)bh * p.D + d);
+                q2[d] = qh | (qh << 16);
+            }
+            const uint32_t mm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 8);
+            const uint32_t lm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 4);
             if (lane == 0) {
                 masks[r] = mm;
                 masks[8 + r] = lm;
@@ -96,93 +153,147 @@ __global__ void __launch_bounds__(256, 1) k_compute_kernel(const KParams p) {
         __syncwarp();
     };
 
-    uint32_t top_next = 0;
-    // ---- producer: stage item j = (unit k, channel chunk c)
-    auto issue = [&](long long j) {
-        const long long k = j / nch;
-        const int c = (int)(j - k * nch);
-        if (c == 0) {
-            const uint32_t top = top_next;
-            build_masks(k, top);
-            if (k + 1 < my_units) top_next = prefetch_meta(k + 1);
-        }
-        int bh, g;
-        k_unit_coords(p, w + k * W, bh, g);
-        const uint32_t* masks = reinterpret_cast<const uint32_t*>(meta0 + (size_t)(k % NMETA) * META + 3 * MAX_D);
-        const uint32_t mm = (masks[c >> 1] >> ((c & 1) * 16)) & 0xFFFFu;
-        const uint32_t lm = (masks[8 + (c >> 1)] >> ((c & 1) * 16)) & 0xFFFFu;
-        const uint32_t st = ring_a + (uint32_t)(j % STAGES) * STAGE;
-        const int blk0 = g * TILES;
-        const size_t tile0 = ((size_t)bh * p.nmb + blk0) * p.D + (size_t)c * KCH;  // row index of (blk0, c*16)
+    const int nrow = (lane % ROW_LANES) >> 1, nhalf = (lane & 1) << 4, ntsub = lane / ROW_LANES;
+
+    // ---- producer: async copies of one stage
+    KCursor pk = cursor_at(u_begin);
+    int pstage = 0;
+    auto issue = [&]() {
+        const uint32_t* masks = reinterpret_cast<const uint32_t*>(meta0 + (size_t)pk.slot * META);
+        const int sh = ((pk.c * KCH) & 31) + nrow, wi = (pk.c * KCH) >> 5;
+        const bool need_m = (masks[wi] >> sh) & 1u;
+        const bool need_l = (masks[8 + wi] >> sh) & 1u;
+        const uint32_t st = ring_a + (uint32_t)pstage * STAGE;
+        const int ptiles = p.nb - pk.g * TILES;
+        const uint8_t* pf = p.first8 + pk.row * 64 + lane * 16;
+        if (p.debug & 16) {
+            if (lane == 0) {
+                const int nt = ptiles < TILES ? ptiles : TILES;
+                mbar_expect_tx(mbar_a + pstage * 8, nt * KCH * 64);
+                const uint8_t* src = p.first8 + pk.row * 64;
+                for (int t = 0; t < nt; ++t)
+                    bulk_g2s(st + t * F_TILE, (p.debug & 8) ? src + (size_t)t * KCH * 64 : src + t * tile_f, KCH * 64,
+                             mbar_a + pstage * 8);
+            }
+        } else if (!(p.debug & 2)) {
+            const size_t tf = (p.debug & 8) ? (size_t)KCH * 64 : tile_f;
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {  // high-byte plane: 4 tiles x 1 KB
-            const int t = it >> 1;
-            const int off = (((it & 1) << 5) + lane) << 4;
-            if (blk0 + t < p.nb)
-                cp_async16(st + t * F_TILE + off, p.first8 + (tile0 + (size_t)t * p.D) * 64 + off);
+        for (int it = 0; it < TILES * F_IT; ++it) {      // high-byte plane: KCH*64 contiguous bytes per tile
+            const int t = it / F_IT, v = it % F_IT;
+            if (t < ptiles) cp_async16(st + t * F_TILE + v * 512 + lane * 16, pf + t * tf + v * 512);
         }
-        const int row = lane >> 1, half = (lane & 1) << 4;
-        const bool need_m = (mm >> row) & 1u, need_l = (lm >> row) & 1u;
+        }
+        if (!(p.debug & 4)) {
+        const size_t pn = (pk.row + nrow) * 32 + nhalf;
+        const uint32_t nd = st + F_BYTES + nrow * 32 + nhalf;
 #pragma unroll
-        for (int t = 0; t < TILES; ++t) {  // nibble planes: only the rows the alignment rule reads
-            if (blk0 + t < p.nb) {
-                const size_t src = (tile0 + (size_t)t * p.D + row) * 32 + half;
-                if (need_m) cp_async16(st + F_BYTES + t * N_TILE + row * 32 + half, p.mid4 + src);
-                if (need_l) cp_async16(st + F_BYTES + N_BYTES + t * N_TILE + row * 32 + half, p.last4 + src);
+        for (int it = 0; it < TILES / TILES_PER_IT; ++it) {   // nibble planes: rows the rule reads, else constants
+            const int t = it * TILES_PER_IT + ntsub;
+            if (t < ptiles) {
+                const uint32_t dm = nd + t * N_TILE, dl = dm + N_BYTES;
+                if (need_m) cp_async16(dm, p.mid4 + pn + t * tile_n);
+                else st_shared_v4(dm, 0x88888888u);              // plane not read: low byte becomes 0x80
+                if (need_l) cp_async16(dl, p.last4 + pn + t * tile_n);
+                else st_shared_v4(dl, need_m ? 0x88888888u : 0u);  // low plane not read: low nibble becomes 8
             }
         }
+        }
+        if (p.pf_dist >= 100 && pk.c == 0 && pk.u + 1 < u_end) {
+            // whole next unit, tile by tile: DRAM sees 8 KB / 4 KB contiguous requests
+            const int nu = pk.u + 1;
+            const int nbh = nu / p.ngroups, ng = nu - nbh * p.ngroups;
+            const size_t nrow0 = ((size_t)nbh * p.nmb + (size_t)ng * TILES) * p.D;
+            const int nt = p.nb - ng * TILES;
+            if (lane < TILES && lane < nt) l2_prefetch(p.first8 + (nrow0 + (size_t)lane * p.D) * 64, p.D * 64);
+            if (p.pf_dist >= 101 && lane >= 4 && lane < 4 + TILES && lane - 4 < nt)
+                l2_prefetch(p.mid4 + (nrow0 + (size_t)(lane - 4) * p.D) * 32, p.D * 32);
+        }
+        pstage = (pstage + 1 == STAGES) ? 0 : pstage + 1;
+        if (advance(pk) && pk.u < u_end) load_meta(pk.bh, pk.slot);
+    };
+
+    // ---- L2 prefetch stream, pf_dist stages ahead of the copies (high-byte rows always; nibble rows when the
+    //      stage belongs to the (batch, head) whose masks are loaded)
+    KCursor fk = cursor_at(u_begin);
+    int fcount = 0;   // stages prefetched so far
+    auto prefetch = [&]() {
+        const int ptiles = p.nb - fk.g * TILES;
+        if (lane < TILES && lane < ptiles) l2_prefetch(p.first8 + (fk.row + (size_t)lane * p.D) * 64, KCH * 64);
+        if (fk.bh == pk.bh) {
+            const uint32_t* masks = reinterpret_cast<const uint32_t*>(meta0 + (size_t)pk.slot * META);
+            const int sh = ((fk.c * KCH) & 31) + nrow, wi = (fk.c * KCH) >> 5;
+            const bool need_m = (masks[wi] >> sh) & 1u;
+            const bool need_l = (masks[8 + wi] >> sh) & 1u;
+            if (nhalf == 0) {
+#pragma unroll
+                for (int it = 0; it < TILES / TILES_PER_IT; ++it) {
+                    const int t = it * TILES_PER_IT + ntsub;
+                    if (t < ptiles) {
+                        const size_t off = (fk.row + nrow) * 32 + t * tile_n;
+                        if (need_m) l2_prefetch(p.mid4 + off, 32);
+                        if (need_l) l2_prefetch(p.last4 + off, 32);
+                    }
+                }
+            }
+        }
+        ++fcount;
+        advance(fk);
     };
 
     // ---- prologue
-    top_next = prefetch_meta(0);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncwarp();
+    load_meta(pk.bh, 0);
+    if (p.pf_dist > 0 && p.pf_dist < 100)
+        for (int j = 0; j < p.pf_dist + STAGES - 1 && j < total; ++j) prefetch();
     for (int j = 0; j < STAGES - 1; ++j) {
-        if (j < total) issue(j);
+        if (j < total) issue();
         cp_async_commit();
     }
 
     const int tile = lane >> 3, li = lane & 7;
     uint32_t acc02 = 0, acc13 = 0, acc46 = 0, acc57 = 0;
-    for (long long i = 0; i < total; ++i) {
+    KCursor ck = cursor_at(u_begin);
+    int cstage = 0;
+    for (int i = 0; i < total; ++i) {
         cp_async_wait<STAGES - 2>();
-        __syncwarp();
-        if (i + STAGES - 1 < total) issue(i + STAGES - 1);
-        cp_async_commit();
-
-        const long long k = i / nch;
-        const int c = (int)(i - k * nch);
-        const uint32_t m = meta_a + (uint32_t)(k % NMETA) * META;
-        const uint32_t mm = (lds32(m + 3 * MAX_D + (c >> 1) * 4) >> ((c & 1) * 16)) & 0xFFFFu;
-        const uint32_t lm = (lds32(m + 3 * MAX_D + 32 + (c >> 1) * 4) >> ((c & 1) * 16)) & 0xFFFFu;
-        const uint32_t st = ring_a + (uint32_t)(i % STAGES) * STAGE;
-        const uint32_t fa = st + tile * F_TILE + li * 8;
-        const uint32_t ma = st + F_BYTES + tile * N_TILE + li * 4;
-        const uint32_t la = ma + N_BYTES;
-        const uint32_t qa = m + c * (KCH * 2);
-#pragma unroll
-        for (int r = 0; r < KCH; ++r) {
-            const uint2 f = lds64(fa + r * 64);
-            uint32_t M = 0x88888888u, L = 0u;        // neither nibble plane read: low byte becomes 0x80
-            if ((mm >> r) & 1u) {                    // warp-uniform
-                M = lds32(ma + r * 32);
-                L = 0x88888888u;                     // low plane skipped: low nibble becomes 8
-                if ((lm >> r) & 1u) L = lds32(la + r * 32);
-            }
-            const uint32_t lbe = (M & 0xF0F0F0F0u) | ((L >> 4) & 0x0F0F0F0Fu);   // low bytes of tokens 0,2,4,6
-            const uint32_t lbo = ((M << 4) & 0xF0F0F0F0u) | (L & 0x0F0F0F0Fu);   // low bytes of tokens 1,3,5,7
-            const uint32_t qh = lds16(qa + r * 2);
-            const uint32_t q2 = qh | (qh << 16);
-            acc02 = hfma2_bits(__byte_perm(lbe, f.x, 0x6140), q2, acc02);
-            acc13 = hfma2_bits(__byte_perm(lbo, f.x, 0x7150), q2, acc13);
-            acc46 = hfma2_bits(__byte_perm(lbe, f.y, 0x6342), q2, acc46);
-            acc57 = hfma2_bits(__byte_perm(lbo, f.y, 0x7352), q2, acc57);
+        if (p.debug & 16) {
+            const uint32_t par = (uint32_t)((i / STAGES) & 1);
+            int spins = 0;
+            while (!mbar_try_wait(mbar_a + cstage * 8, par) && ++spins < (1 << 22)) {}
         }
-        if (c == nch - 1) {  // unit finished: scale, reorder to token order, one 16-byte store per lane
-            int bh, g;
-            k_unit_coords(p, w + k * W, bh, g);
-            const int blk = g * TILES + tile;
+        __syncwarp();
+        if (i + STAGES - 1 < total) issue();
+        cp_async_commit();
+        if (p.pf_dist > 0 && p.pf_dist < 100 && fcount < total) prefetch();
+
+        const uint8_t* stp = ring + (size_t)cstage * STAGE;
+        cstage = (cstage + 1 == STAGES) ? 0 : cstage + 1;
+        const uint2* fp = reinterpret_cast<const uint2*>(stp + tile * F_TILE + li * 8);
+        const uint32_t* mp = reinterpret_cast<const uint32_t*>(stp + F_BYTES + tile * N_TILE + li * 4);
+        const uint32_t* lp = reinterpret_cast<const uint32_t*>(stp + F_BYTES + N_BYTES + tile * N_TILE + li * 4);
+        const uint4* qp = reinterpret_cast<const uint4*>(meta0 + (size_t)ck.slot * META + 64 + ck.c * (KCH * 4));
+        if (!(p.debug & 1))
+#pragma unroll
+        for (int r4 = 0; r4 < KCH / 4; ++r4) {
+            const uint4 qv = qp[r4];
+            const uint32_t q2s[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) {
+                const int r = r4 * 4 + rr;
+                const uint2 f = fp[r * 8];
+                const uint32_t M = mp[r * 8], L = lp[r * 8];
+                const uint32_t lbe = (M & 0xF0F0F0F0u) | ((L >> 4) & 0x0F0F0F0Fu);   // low bytes, tokens 0,2,4,6
+                const uint32_t lbo = ((M << 4) & 0xF0F0F0F0u) | (L & 0x0F0F0F0Fu);   // low bytes, tokens 1,3,5,7
+                acc02 = hfma2_bits(__byte_perm(lbe, f.x, 0x6140), q2s[rr], acc02);
+                acc13 = hfma2_bits(__byte_perm(lbo, f.x, 0x7150), q2s[rr], acc13);
+                acc46 = hfma2_bits(__byte_perm(lbe, f.y, 0x6342), q2s[rr], acc46);
+                acc57 = hfma2_bits(__byte_perm(lbo, f.y, 0x7352), q2s[rr], acc57);
+            }
+        }
+        const int cbh = ck.bh, cg = ck.g;
+        const bool last_chunk = (ck.c == nch - 1);
+        advance(ck);
+        if (last_chunk) {  // unit finished: scale, reorder to token order, one 16-byte store per lane
+            const int blk = cg * TILES + tile;
             if (blk < p.nb) {
                 acc02 = hmul2_bits(acc02, p.scale2);
                 acc13 = hmul2_bits(acc13, p.scale2);
@@ -193,7 +304,7 @@ __global__ void __launch_bounds__(256, 1) k_compute_kernel(const KParams p) {
                 o.y = __byte_perm(acc02, acc13, 0x7632);
                 o.z = __byte_perm(acc46, acc57, 0x5410);
                 o.w = __byte_perm(acc46, acc57, 0x7632);
-                const size_t row = (size_t)bh * (size_t)(p.nb + 1) * 64 + (size_t)blk * 64 + li * 8;
+                const size_t row = (size_t)cbh * (size_t)(p.nb + 1) * 64 + (size_t)blk * 64 + li * 8;
                 *reinterpret_cast<uint4*>(p.s + row * 2) = o;
             }
             acc02 = acc13 = acc46 = acc57 = 0;
@@ -255,41 +366,56 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     p.first8 = first8; p.mid4 = mid4; p.last4 = last4; p.kq = kq; p.kqmax = kqmax; p.q = q; p.s = s;
     p.BH = bsz * H; p.nb = nb; p.nmb = nmb; p.D = D;
     p.ngroups = (nb + TILES - 1) / TILES;
-    p.units = (long long)p.BH * p.ngroups;
+    const long long units = (long long)p.BH * p.ngroups;
+    AKV_REQUIRE(units < (1ll << 30), AKV_ERR_OVERFLOW, "k_cache_compute: too many blocks");
+    p.units = (int)units;
     const unsigned short sb = __half_as_ushort(scale);
     p.scale2 = (uint32_t)sb | ((uint32_t)sb << 16);
     p.reference = reference;
+    p.pf_dist = tuning().k_prefetch;
+    p.debug = tuning().debug;
 
-    // Pick warps per CTA (one CTA per SM) so that the last wave of units is as full as possible, then give
-    // each warp as many ring stages as the shared memory allows.
+    // One CTA per SM.  Pick the channel-chunk size, ring depth and warps per CTA (tunable), trimming the warp
+    // count so that every warp gets (nearly) the same whole number of units.
     const int sms = sm_count();
     const int budget = max_dyn_smem();
-    int best_wpc = 8;
+    const int kch = tuning().k_kch, stages = tuning().k_stages;
+    const int per_warp = stages * stage_bytes(kch) + NMETA * META + 64;
+    int wmax = budget / per_warp;
+    if (wmax > 16) wmax = 16;
+    if (tuning().k_wpc > 0 && tuning().k_wpc < wmax) wmax = tuning().k_wpc;
+    AKV_REQUIRE(wmax >= 1, AKV_ERR_CUDA, "k_cache_compute: %d bytes of shared memory are too few", budget);
+    int wpc = wmax;
     double best_eff = -1.0;
-    for (int wpc = 8; wpc >= 5; --wpc) {
+    for (int c = wmax; c >= (wmax * 3 + 3) / 4; --c) {
+        long long Wt = (long long)sms * c;
+        long long upw = (units + Wt - 1) / Wt;
+        double eff = (double)units / (double)(upw * Wt);
+        if (eff > best_eff + 0.02) { best_eff = eff; wpc = c; }
+    }
+    {
         long long Wt = (long long)sms * wpc;
-        long long waves = (p.units + Wt - 1) / Wt;
-        double eff = (double)p.units / (double)(waves * Wt);
-        if (eff > best_eff + 0.02) { best_eff = eff; best_wpc = wpc; }
+        p.upw = (int)((units + Wt - 1) / Wt);
     }
-    int wpc = best_wpc;
-    long long ctas = (p.units + wpc - 1) / wpc;
-    int grid = (int)(ctas < sms ? ctas : sms);
-    int per_warp = budget / wpc;
-    int stages = (per_warp - NMETA * META) / STAGE;
-    if (stages > 4) stages = 4;
-    AKV_REQUIRE(stages >= 3, AKV_ERR_CUDA, "k_cache_compute: %d bytes of shared memory are too few", budget);
-    size_t smem = (size_t)wpc * (stages * STAGE + NMETA * META);
-    cudaError_t e;
-    if (stages == 4) {
-        e = cudaFuncSetAttribute(k_compute_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const long long warps_needed = (units + p.upw - 1) / p.upw;
+    int grid = (int)((warps_needed + wpc - 1) / wpc);
+    size_t smem = (size_t)wpc * per_warp;
+    auto go = [&](auto kern) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_status(e, "k_cache_compute smem attribute");
-        k_compute_kernel<4><<<grid, wpc * 32, smem, st>>>(p);
-    } else {
-        e = cudaFuncSetAttribute(k_compute_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_status(e, "k_cache_compute smem attribute");
-        k_compute_kernel<3><<<grid, wpc * 32, smem, st>>>(p);
+        kern<<<grid, wpc * 32, smem, st>>>(p);
+        return AKV_OK;
+    };
+    int rc;
+    switch (kch * 10 + stages) {
+        case 83: rc = go(k_compute_kernel<8, 3>); break;
+        case 84: rc = go(k_compute_kernel<8, 4>); break;
+        case 86: rc = go(k_compute_kernel<8, 6>); break;
+        case 164: rc = go(k_compute_kernel<16, 4>); break;
+        case 165: rc = go(k_compute_kernel<16, 5>); break;
+        default: rc = go(k_compute_kernel<16, 3>); break;
     }
+    if (rc != AKV_OK) return rc;
     return cuda_status(cudaGetLastError(), "k_cache_compute launch");
 }
 

@@ -36,6 +36,12 @@ def _stream(dev: torch.device) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
+def _cuda_device_of(name: str, t: torch.Tensor) -> torch.device:
+    """Device of the tensor that anchors a call (checked before a device context is entered)."""
+    _u8(name, t)
+    return t.device
+
+
 class _CudaModule:
     """Stand-in for the pybind module `kv_cache_cuda`."""
 
@@ -45,7 +51,7 @@ class _CudaModule:
     # KV_cache_ops.cpp:5-16
     def k_cache_save(self, k_cache_first_8, k_cache_mid_4, k_cache_last_4, k_new, bsz, n_kv_heads, n_blocks,
                      n_max_blocks, d_head, d_block, start_pos, seqlen) -> None:
-        dev = k_new.device
+        dev = _cuda_device_of("k_new", k_new)
         with torch.cuda.device(dev):
             rc = self._lib.akv_k_cache_save(
                 _u8("k_cache_first_8", k_cache_first_8, dev), _u8("k_cache_mid_4", k_cache_mid_4, dev),
@@ -58,7 +64,7 @@ class _CudaModule:
     def k_cache_compute(self, k_cache_first_8, k_cache_mid_4, k_cache_last_4, k_column_max_multiply_q,
                         k_column_max_multiply_q_max, q, bsz, n_kv_heads, n_blocks, n_max_blocks, d_head, d_block,
                         seqlen, sqrt_dim, reference) -> torch.Tensor:
-        dev = q.device
+        dev = _cuda_device_of("q", q)
         # same shape and (uninitialised) allocation as extension/csrc/K_cache.cu:329-330
         s = torch.empty((bsz, n_kv_heads, 1, (n_blocks + 1) * d_block * 2), dtype=torch.uint8, device=dev)
         if n_blocks == 0:
@@ -77,7 +83,7 @@ class _CudaModule:
     # KV_cache_ops.cpp:34-43
     def v_cache_save(self, v_cache_first_8, v_cache_mid_4, v_cache_last_4, v_new, bsz, n_local_kv_heads,
                      max_seq_len, head_dim, start_pos, seq_len) -> None:
-        dev = v_new.device
+        dev = _cuda_device_of("v_new", v_new)
         with torch.cuda.device(dev):
             rc = self._lib.akv_v_cache_save(
                 _u8("v_cache_first_8", v_cache_first_8, dev), _u8("v_cache_mid_4", v_cache_mid_4, dev),
@@ -89,7 +95,7 @@ class _CudaModule:
     # KV_cache_ops.cpp:45-54
     def v_cache_test_compute(self, v_cache_first_8, v_cache_mid_4, v_cache_last_4, test_s_value, test_s_index, bsz,
                              n_local_kv_heads, max_seq_len, head_dim, top_max_k) -> torch.Tensor:
-        dev = test_s_value.device
+        dev = _cuda_device_of("test_s_value", test_s_value)
         test_o = torch.empty((bsz, n_local_kv_heads, 1, head_dim * 2), dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             rc = self._lib.akv_v_cache_test_compute(
@@ -104,7 +110,7 @@ class _CudaModule:
     def v_cache_compute(self, v_cache_first_8, v_cache_mid_4, v_cache_last_4, s, s_exp_expect_alignment_min, bsz,
                         n_local_kv_heads, max_seq_len, head_dim, s_last_dim, start_pos_add_seqlen,
                         reference) -> torch.Tensor:
-        dev = v_cache_first_8.device
+        dev = _cuda_device_of("v_cache_first_8", v_cache_first_8)
         o = torch.empty((bsz, n_local_kv_heads, 1, head_dim * 2), dtype=torch.uint8, device=dev)
         # `s` may be a sliced view (extension/v_cache_file.py:150,184): like the reference, only its base
         # pointer and the row stride passed as s_last_dim are used, so contiguity is not required here.

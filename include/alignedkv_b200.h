@@ -39,6 +39,13 @@ int akv_abi_version(void);
 const char* akv_last_error(void);
 
 /*
+ * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16, "k_prefetch" 0..64,
+ * "v_stages" 4|6|8, "v_prefetch" 0..64).
+ * Process-wide; results never depend on them.  No counterpart in the reference.
+ */
+int akv_set_tuning(const char* key, int value);
+
+/*
  * Replaces k_cache_save (extension/csrc/KV_cache_ops.cpp:5-16; extension/csrc/K_cache.cu:97-164).
  * Splits fp16 keys k_new [B,seqlen,H,D] into the three K planes.  Same dispatch as the reference:
  * start_pos==0 or seqlen%d_block==0 -> writes n_blocks blocks starting at block start_pos/d_block (nothing when
