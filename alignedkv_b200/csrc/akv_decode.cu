@@ -1,0 +1,344 @@
+// One-call decode step: everything the reference does between receiving (q, k_new, v_new) of one decode token and
+// returning the attention output (model/KVCache_AlignedKV.py:116-124), with the wrapper arithmetic of
+// extension/k_cache_file.py:97-118,132-159 and extension/v_cache_file.py:97-116,119-190 moved into a handful of
+// small kernels around the two streaming kernels:
+//   append      residual buffers, per-channel exponent maxima, alignment inputs kq / kqmax
+//   (flush)     plane writers, only when the residual buffer reaches 64 tokens
+//   q.K^T       akv_k_compute.cu
+//   softmax     residual-token scores, -inf padding, fp32 softmax -> fp16 probabilities, and the per-residue-class
+//               (token index mod 32) maximum + first position that the magnitude probe needs
+//   probe       akv_v_compute.cu, then the threshold byte per (batch, head) with the reference's [B,H,H,D] broadcast
+//   P.V         akv_v_compute.cu
+//   tail        adds the residual tokens' contribution
+#include "akv_common.cuh"
+
+namespace akv {
+
+int launch_v_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, int, int, int, int, cudaStream_t);
+int launch_k_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, int, int, int, int, int,
+                  cudaStream_t);
+int launch_k_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
+                     const uint8_t*, uint8_t*, int, int, int, int, int, int, float, int, cudaStream_t);
+int launch_v_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*,
+                     int, int, int, int, int, int, int, cudaStream_t);
+int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int,
+                   cudaStream_t);
+
+constexpr int TOPK = 32;     // residue classes of the magnitude probe (extension/v_cache_file.py:16)
+constexpr int BLK = 64;      // tokens per K block (extension/k_cache_file.py:5-6)
+
+struct Scratch {
+    uint16_t* s;         // [B,H,R] scores, then probabilities (fp16), R = (nb+1)*64
+    uint8_t* kq;         // [B,H,D]
+    uint8_t* kqmax;      // [B*H]
+    uint16_t* pval;      // [B,H,32]
+    int32_t* pidx;       // [B,H,32]
+    uint16_t* test_o;    // [B,H,D]
+    uint8_t* amin;       // [B*H]
+    uint16_t* o_main;    // [B,H,D]
+};
+
+static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static size_t carve(Scratch* sc, uint8_t* base, int B, int H, int D, int max_seq_len) {
+    const size_t R = ((size_t)(max_seq_len + BLK - 1) / BLK + 1) * BLK;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += align_up(bytes); return base ? base + o : nullptr; };
+    uint8_t* p;
+    p = take((size_t)B * H * R * 2);       if (sc) sc->s = reinterpret_cast<uint16_t*>(p);
+    p = take((size_t)B * H * D);           if (sc) sc->kq = p;
+    p = take((size_t)B * H);               if (sc) sc->kqmax = p;
+    p = take((size_t)B * H * TOPK * 2);    if (sc) sc->pval = reinterpret_cast<uint16_t*>(p);
+    p = take((size_t)B * H * TOPK * 4);    if (sc) sc->pidx = reinterpret_cast<int32_t*>(p);
+    p = take((size_t)B * H * D * 2);       if (sc) sc->test_o = reinterpret_cast<uint16_t*>(p);
+    p = take((size_t)B * H);               if (sc) sc->amin = p;
+    p = take((size_t)B * H * D * 2);       if (sc) sc->o_main = reinterpret_cast<uint16_t*>(p);
+    return off;
+}
+
+// ------------------------------------------------------------------ append
+// grid B*H, block D/2.  Thread c handles channels 2c, 2c+1.
+__global__ void __launch_bounds__(512)
+append_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, uint16_t* __restrict__ k_exp,
+              uint16_t* __restrict__ v_exp, const uint32_t* __restrict__ q, const uint32_t* __restrict__ k_new,
+              const uint32_t* __restrict__ v_new, uint16_t* __restrict__ kq, uint8_t* __restrict__ kqmax, int H, int D,
+              int rest_len) {
+    __shared__ uint32_t red[16];
+    const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
+    const int c = threadIdx.x, hd = D >> 1;
+    const size_t row = (size_t)bh * hd + c;                                  // [B,1,H,D] in words
+    const size_t rrow = (((size_t)b * BLK + rest_len) * H + h) * hd + c;     // [B,64,H,D] in words
+    const uint32_t kw = k_new[row], vw = v_new[row], qw = q[row];
+    restk[rrow] = kw;
+    restv[rrow] = vw;
+    auto exps = [](uint32_t w) { return ((w >> 10) & 0x1Fu) | (((w >> 26) & 0x1Fu) << 8); };   // two exponent bytes
+    // running per-channel maxima of the exponent fields (k_cache_file.py:98-99, v_cache_file.py:98-99)
+    const uint32_t ke2 = __vmaxu4(k_exp[row], exps(kw)) & 0xFFFFu, ve2 = __vmaxu4(v_exp[row], exps(vw)) & 0xFFFFu;
+    k_exp[row] = (uint16_t)ke2;
+    v_exp[row] = (uint16_t)ve2;
+    // exponent upper bound of every product q_d * k_{t,d} and its maximum over channels (k_cache_file.py:136-138)
+    const uint32_t kq2 = __vadd4(exps(qw), ke2) & 0xFFFFu;
+    kq[row] = (uint16_t)kq2;
+    uint32_t m = max(kq2 & 0xFFu, kq2 >> 8);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if ((c & 31) == 0) red[c >> 5] = m;
+    __syncthreads();
+    if (c == 0) {
+        for (int w = 1; w < (hd + 31) / 32; ++w) m = max(m, red[w]);
+        kqmax[bh] = (uint8_t)m;
+    }
+}
+
+// ------------------------------------------------------------------ softmax (+ residual scores, class maxima)
+// grid B*H, block 256.  Row = [0, qn) aligned scores | [qn, qn+rest) residual scores | -inf up to R.
+__global__ void __launch_bounds__(256)
+softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
+               uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, int H, int D, int R, int qn, int rest,
+               float sqrt_d) {
+    __shared__ float redf[8];
+    __shared__ uint32_t cand_v[256];
+    __shared__ int32_t cand_i[256];
+    const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint16_t* row = s + (size_t)bh * R;
+    const int len = qn + rest;
+    // residual tokens: fp32 dot product rounded to fp16, then divided by sqrt(D) and rounded again, which is
+    // what `matmul(q, restk^T) / sqrt(D)` on fp16 tensors produces (k_cache_file.py:156-157)
+    for (int r = warp; r < rest; r += 8) {
+        const __half* kr = restk + (((size_t)b * BLK + r) * H + h) * D;
+        const __half* qr = q + (size_t)bh * D;
+        float acc = 0.f;
+        for (int d = lane; d < D; d += 32) acc += __half2float(qr[d]) * __half2float(kr[d]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (lane == 0) row[qn + r] = __half_as_ushort(__float2half_rn(__half2float(__float2half_rn(acc)) / sqrt_d));
+    }
+    __syncthreads();
+    // pass 1: maximum
+    float m = -INFINITY;
+    for (int t = tid; t < len; t += 256) m = fmaxf(m, __half2float(__ushort_as_half(row[t])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane == 0) redf[warp] = m;
+    __syncthreads();
+    m = redf[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, redf[w]);
+    __syncthreads();
+    // pass 2: sum of exponentials (fp32, as F.softmax(scores.float()) does; model/KVCache_AlignedKV.py:121)
+    float sum = 0.f;
+    for (int t = tid; t < len; t += 256) sum += expf(__half2float(__ushort_as_half(row[t])) - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if (lane == 0) redf[warp] = sum;
+    __syncthreads();
+    sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sum += redf[w];
+    // pass 3: probabilities, and this thread's residue class (tid % 32): largest probability over the quantized
+    // tokens with its first position (torch.max over the group axis keeps the first maximum; v_cache_file.py:128-130)
+    uint32_t best = 0;
+    int32_t best_g = 0;
+    for (int t = tid; t < R; t += 256) {
+        uint16_t pb = 0;   // exp(-inf - m) = 0
+        if (t < len) pb = __half_as_ushort(__float2half_rn(expf(__half2float(__ushort_as_half(row[t])) - m) / sum));
+        row[t] = pb;
+        if (t < qn && pb > best) {   // probabilities are non-negative: their bit patterns order like their values
+            best = pb;
+            best_g = t >> 5;
+        }
+    }
+    cand_v[tid] = best;
+    cand_i[tid] = best_g;
+    __syncthreads();
+    if (tid < TOPK) {
+        uint32_t bv = cand_v[tid];
+        int32_t bi = cand_i[tid];
+        for (int w = 1; w < 8; ++w) {
+            const uint32_t v = cand_v[tid + 32 * w];
+            const int32_t i = cand_i[tid + 32 * w];
+            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        }
+        pval[(size_t)bh * TOPK + tid] = (uint16_t)bv;
+        pidx[(size_t)bh * TOPK + tid] = bi;
+    }
+}
+
+// ------------------------------------------------------------------ threshold byte per (batch, head)
+// amin[i] = min_d ((exp(test_o[bb, hp, d]) & 0x1E) + 15 - v_exp[bb, he, d]) mod 256 with i = b*H + h read flat from
+// the reference's [B,H,H,1] tensor: bb = i / (H*H), hp = (i / H) % H, he = i % H (v_cache_file.py:142,156-160).
+__global__ void __launch_bounds__(128)
+amin_kernel(const uint16_t* __restrict__ test_o, const uint8_t* __restrict__ v_exp, uint8_t* __restrict__ amin,
+            int BH, int H, int D) {
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= BH) return;
+    const int lane = threadIdx.x & 31;
+    const int bb = i / (H * H), hp = (i / H) % H, he = i % H;
+    uint32_t m = 255;
+    for (int d = lane; d < D; d += 32) {
+        const uint32_t e = (test_o[((size_t)bb * H + hp) * D + d] >> 10) & 0x1Eu;
+        const uint32_t a = (e + 15u - v_exp[((size_t)bb * H + he) * D + d]) & 0xFFu;
+        m = min(m, a);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane == 0) amin[i] = (uint8_t)m;
+}
+
+// ------------------------------------------------------------------ tail: residual tokens of P.V
+// out = half(o_main + half(sum_r p[qn+r] * restv[r])) (v_cache_file.py:189); grid B*H, block D/2... one thread/channel
+__global__ void __launch_bounds__(256)
+tail_kernel(const uint16_t* __restrict__ o_main, const uint16_t* __restrict__ p, const __half* __restrict__ restv,
+            __half* __restrict__ out, int H, int D, int R, int qn, int rest) {
+    const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < rest; ++r)
+            acc += __half2float(__ushort_as_half(p[(size_t)bh * R + qn + r])) *
+                   __half2float(restv[(((size_t)b * BLK + r) * H + h) * D + d]);
+        const float base = o_main ? __half2float(__ushort_as_half(o_main[(size_t)bh * D + d])) : 0.f;
+        out[(size_t)bh * D + d] = __float2half_rn(base + __half2float(__float2half_rn(acc)));
+    }
+}
+
+// ------------------------------------------------------------------ optional per-kernel timing
+struct Timing {
+    static constexpr int CAP = 4096;
+    cudaEvent_t ev[CAP][4];
+    int created = 0, used = 0;
+};
+static Timing g_timing;
+
+static cudaEvent_t* timing_slot() {
+    if (!tuning().timing) return nullptr;
+    Timing& t = g_timing;
+    if (t.used >= Timing::CAP) return nullptr;
+    if (t.used >= t.created) {
+        for (int i = 0; i < 4; ++i)
+            if (cudaEventCreate(&t.ev[t.created][i]) != cudaSuccess) return nullptr;
+        ++t.created;
+    }
+    return t.ev[t.used++];
+}
+
+}  // namespace akv
+
+using namespace akv;
+
+extern "C" {
+
+long long akv_decode_scratch_bytes(int bsz, int n_heads, int head_dim, int max_seq_len) {
+    if (bsz <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq_len <= 0) return -1;
+    return (long long)carve(nullptr, nullptr, bsz, n_heads, head_dim, max_seq_len);
+}
+
+int akv_timing_reset(void) {
+    g_timing.used = 0;
+    return AKV_OK;
+}
+
+// Mean duration (microseconds) of the q.K^T and P.V launches recorded since the last reset; the caller must have
+// synchronised the stream.  Returns the number of recorded steps.
+int akv_timing_read(double* k_us, double* v_us) {
+    double ks = 0, vs = 0;
+    int n = 0;
+    for (int i = 0; i < g_timing.used; ++i) {
+        float a = 0, b = 0;
+        if (cudaEventElapsedTime(&a, g_timing.ev[i][0], g_timing.ev[i][1]) != cudaSuccess) continue;
+        if (cudaEventElapsedTime(&b, g_timing.ev[i][2], g_timing.ev[i][3]) != cudaSuccess) continue;
+        ks += a * 1e3;
+        vs += b * 1e3;
+        ++n;
+    }
+    if (k_us) *k_us = n ? ks / n : 0;
+    if (v_us) *v_us = n ? vs / n : 0;
+    return n;
+}
+
+int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                    void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                    const void* v_new, void* out, void* scratch, long long scratch_bytes, int bsz, int n_heads,
+                    int head_dim, int max_seq_len, int rest_len, int rest_start, int reference, void* stream) {
+    set_error("");
+    const int B = bsz, H = n_heads, D = head_dim;
+    AKV_REQUIRE(k_first_8 && k_mid_4 && k_last_4 && v_first_8 && v_mid_4 && v_last_4 && k_exp_max && v_exp_max &&
+                restk && restv && q && k_new && v_new && out && scratch, AKV_ERR_NULL, "decode_step: null pointer");
+    AKV_REQUIRE(B > 0 && H > 0 && D > 0 && D % 64 == 0 && D <= 1024 && max_seq_len > 0, AKV_ERR_SHAPE,
+                "decode_step: unsupported extent (bsz %d, heads %d, head_dim %d [multiple of 64], max_seq_len %d)", B, H,
+                D, max_seq_len);
+    AKV_REQUIRE(rest_len >= 0 && rest_len < BLK && rest_start >= 0 && rest_start % BLK == 0 &&
+                rest_start + rest_len + 1 <= max_seq_len, AKV_ERR_SHAPE,
+                "decode_step: residual state (start %d, length %d) does not fit max_seq_len %d", rest_start, rest_len,
+                max_seq_len);
+    AKV_REQUIRE(scratch_bytes >= akv_decode_scratch_bytes(B, H, D, max_seq_len), AKV_ERR_SHAPE,
+                "decode_step: scratch of %lld bytes is too small", scratch_bytes);
+    AKV_REQUIRE(aligned16(scratch) && aligned16(q) && aligned16(k_new) && aligned16(v_new) && aligned16(out) &&
+                aligned16(restk) && aligned16(restv) && aligned16(k_exp_max) && aligned16(v_exp_max), AKV_ERR_ALIGN,
+                "decode_step: pointers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Scratch sc;
+    carve(&sc, static_cast<uint8_t*>(scratch), B, H, D, max_seq_len);
+    const int nmb = (max_seq_len + BLK - 1) / BLK;
+    int rc;
+
+    append_kernel<<<B * H, D / 2, 0, st>>>(static_cast<uint32_t*>(restk), static_cast<uint32_t*>(restv),
+                                          static_cast<uint16_t*>(k_exp_max), static_cast<uint16_t*>(v_exp_max),
+                                          static_cast<const uint32_t*>(q), static_cast<const uint32_t*>(k_new),
+                                          static_cast<const uint32_t*>(v_new), reinterpret_cast<uint16_t*>(sc.kq),
+                                          sc.kqmax, H, D, rest_len);
+    if ((rc = cuda_status(cudaGetLastError(), "decode_step append launch")) != AKV_OK) return rc;
+    int rest = rest_len + 1, qn = rest_start;
+    if (rest == BLK) {   // the buffered block goes to the planes (k_cache_file.py:102-118, v_cache_file.py:103-116)
+        rc = launch_k_save(static_cast<uint8_t*>(k_first_8), static_cast<uint8_t*>(k_mid_4),
+                           static_cast<uint8_t*>(k_last_4), static_cast<const uint8_t*>(restk), B, H, 1, nmb, D, BLK, qn,
+                           BLK, st);
+        if (rc != AKV_OK) return rc;
+        rc = launch_v_save(static_cast<uint8_t*>(v_first_8), static_cast<uint8_t*>(v_mid_4),
+                           static_cast<uint8_t*>(v_last_4), static_cast<const uint8_t*>(restv), B, H, max_seq_len, D, qn,
+                           BLK, BLK, st);
+        if (rc != AKV_OK) return rc;
+        qn += BLK;
+        rest = 0;
+    }
+    const int nb = qn / BLK;
+    const int R = (nb + 1) * BLK;
+    cudaEvent_t* ev = timing_slot();
+    if (nb > 0) {
+        if (ev) cudaEventRecord(ev[0], st);
+        rc = launch_k_compute(static_cast<const uint8_t*>(k_first_8), static_cast<const uint8_t*>(k_mid_4),
+                              static_cast<const uint8_t*>(k_last_4), sc.kq, sc.kqmax, static_cast<const uint8_t*>(q),
+                              reinterpret_cast<uint8_t*>(sc.s), B, H, nb, nmb, D, BLK, 1.0f / sqrtf((float)D),
+                              reference != 0, st);
+        if (ev) cudaEventRecord(ev[1], st);
+        if (rc != AKV_OK) return rc;
+    }
+    softmax_kernel<<<B * H, 256, 0, st>>>(sc.s, static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval,
+                                         sc.pidx, H, D, R, qn, rest, sqrtf((float)D));
+    if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
+    if (qn > 0) {
+        rc = launch_v_probe(static_cast<const uint8_t*>(v_first_8), reinterpret_cast<const uint8_t*>(sc.pval),
+                            reinterpret_cast<const uint8_t*>(sc.pidx), reinterpret_cast<uint8_t*>(sc.test_o), B, H,
+                            max_seq_len, D, TOPK, st);
+        if (rc != AKV_OK) return rc;
+        amin_kernel<<<(B * H + 3) / 4, 128, 0, st>>>(sc.test_o, static_cast<const uint8_t*>(v_exp_max), sc.amin, B * H, H,
+                                                    D);
+        if ((rc = cuda_status(cudaGetLastError(), "decode_step threshold launch")) != AKV_OK) return rc;
+        if (ev) cudaEventRecord(ev[2], st);
+        rc = launch_v_compute(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                              static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
+                              reinterpret_cast<uint8_t*>(rest ? (void*)sc.o_main : out), B, H, max_seq_len, D, R, qn,
+                              reference != 0, st);
+        if (ev) cudaEventRecord(ev[3], st);
+        if (rc != AKV_OK) return rc;
+    }
+    if (rest > 0 || qn == 0) {
+        tail_kernel<<<B * H, D < 256 ? ((D + 31) / 32) * 32 : 256, 0, st>>>(
+            qn > 0 ? sc.o_main : nullptr, sc.s, static_cast<const __half*>(restv), static_cast<__half*>(out), H, D, R, qn,
+            rest);
+        if ((rc = cuda_status(cudaGetLastError(), "decode_step tail launch")) != AKV_OK) return rc;
+    }
+    return AKV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,168 @@
+"""`DecodeLayer`: one layer's AlignedKV cache driven through the one-call decode step of the C ABI.
+
+State and arithmetic are those of the reference's K_Cache_Class / V_Cache_Class pair (extension/k_cache_file.py,
+extension/v_cache_file.py) plus the decode branch of QuantizedCache_AlignedKV (model/KVCache_AlignedKV.py:116-124);
+the difference is mechanical: the ~35 small tensor operations the reference wrappers run per step are folded into
+kernels behind `akv_decode_step`, so a step is a single library call.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from .extension._planes import cdiv, column_block, exponent_field
+from .extension.KV_cache_cpp_extention import cuda_module
+
+__all__ = ["DecodeLayer"]
+
+
+class DecodeLayer:
+    # DRAM bytes per launch from the committed ncu capture of the bench workload (profiles/), by kernel
+    NCU_TRAFFIC = {}
+
+    def __init__(self, bsz: int, max_seq_len: int, n_heads: int, head_dim: int, device):
+        self.lib = _lib.load()
+        self.B, self.L, self.H, self.D = bsz, max_seq_len, n_heads, head_dim
+        self.device = torch.device(device)
+        nmb = cdiv(max_seq_len, column_block)
+        z = lambda *shape: torch.zeros(shape, dtype=torch.uint8, device=self.device)  # noqa: E731
+        self.k_first_8 = z(bsz, n_heads, nmb, head_dim, column_block)
+        self.k_mid_4 = z(bsz, n_heads, nmb, head_dim, column_block // 2)
+        self.k_last_4 = z(bsz, n_heads, nmb, head_dim, column_block // 2)
+        self.v_first_8 = z(bsz, n_heads, max_seq_len, head_dim)
+        self.v_mid_4 = z(bsz, n_heads, max_seq_len, head_dim // 2)
+        self.v_last_4 = z(bsz, n_heads, max_seq_len, head_dim // 2)
+        self.k_exp_max = z(bsz, 1, n_heads, head_dim)
+        self.v_exp_max = z(bsz, 1, n_heads, head_dim)
+        self.restk = torch.zeros((bsz, column_block, n_heads, head_dim), dtype=torch.half, device=self.device)
+        self.restv = torch.zeros_like(self.restk)
+        self.rest_len = 0
+        self.rest_start = 0
+        self.cache_len = 0
+        self.reference = False
+        nbytes = self.lib.akv_decode_scratch_bytes(bsz, n_heads, head_dim, max_seq_len)
+        if nbytes < 0:
+            raise ValueError("bad extents")
+        self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.launches = 0
+
+    # ------------------------------------------------------------------ prompt
+    def prefill(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Write a prompt [B,S,H,D] to the planes (whole 64-token blocks) and the residual buffers (the tail);
+        bookkeeping of extension/k_cache_file.py:76-96 and extension/v_cache_file.py:79-96."""
+        B, H, D = self.B, self.H, self.D
+        S = k.shape[1]
+        assert self.cache_len == 0 and k.shape == (B, S, H, D) and v.shape == (B, S, H, D) and S <= self.L
+        self.k_exp_max.copy_(exponent_field(torch.max(k, dim=1, keepdim=True).values))
+        self.v_exp_max.copy_(exponent_field(torch.max(v, dim=1, keepdim=True).values))
+        cuda_module.k_cache_save(self.k_first_8, self.k_mid_4, self.k_last_4, k.view(torch.uint8), B, H,
+                                 S // column_block, cdiv(self.L, column_block), D, column_block, 0, S)
+        full = S - S % column_block
+        cuda_module.v_cache_save(self.v_first_8, self.v_mid_4, self.v_last_4, v.view(torch.uint8), B, H, self.L, D, 0,
+                                 full)
+        self.launches += 2 if full else 0
+        self.rest_len = S % column_block
+        self.rest_start = full
+        self.restk[:, :self.rest_len] = k[:, full:]
+        self.restv[:, :self.rest_len] = v[:, full:]
+        self.cache_len = S
+
+    # ------------------------------------------------------------------ one decode token
+    def decode(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """Append (k, v) of one token per sequence and return the attention output [B,1,H,D] (fp16)."""
+        B, H, D = self.B, self.H, self.D
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            if t.shape != (B, 1, H, D) or t.dtype != torch.half or not t.is_cuda or not t.is_contiguous():
+                raise RuntimeError(f"{name}: expected a contiguous CUDA fp16 tensor of shape {(B, 1, H, D)}")
+        if self.cache_len + 1 > self.L:
+            raise RuntimeError(f"cache is full ({self.L} tokens)")
+        out = torch.empty((B, 1, H, D), dtype=torch.half, device=self.device)
+        with torch.cuda.device(self.device):
+            rc = self.lib.akv_decode_step(
+                self.k_first_8.data_ptr(), self.k_mid_4.data_ptr(), self.k_last_4.data_ptr(),
+                self.v_first_8.data_ptr(), self.v_mid_4.data_ptr(), self.v_last_4.data_ptr(),
+                self.k_exp_max.data_ptr(), self.v_exp_max.data_ptr(), self.restk.data_ptr(), self.restv.data_ptr(),
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), self.scratch.data_ptr(),
+                self.scratch.numel(), B, H, D, self.L, self.rest_len, self.rest_start, int(self.reference),
+                torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check("decode_step", rc)
+        flush = self.rest_len + 1 == column_block
+        qn = self.rest_start + (column_block if flush else 0)
+        rest = 0 if flush else self.rest_len + 1
+        # kernels of this library launched by the call: append, (2 flush), q.K^T, softmax, probe, threshold, P.V, tail
+        self.launches += 1 + (2 if flush else 0) + (1 if qn else 0) + 1 + (3 if qn else 0) + (1 if rest or not qn else 0)
+        self.rest_len, self.rest_start = rest, qn
+        self.cache_len += 1
+        return out
+
+    # ------------------------------------------------------------------ benchmark helpers
+    def snapshot(self):
+        """Everything a decode step mutates, so that the same step can be replayed."""
+        return dict(rest_len=self.rest_len, rest_start=self.rest_start, cache_len=self.cache_len,
+                    restk=self.restk.clone(), restv=self.restv.clone(), k_exp=self.k_exp_max.clone(),
+                    v_exp=self.v_exp_max.clone())
+
+    def restore(self, snap) -> None:
+        """Rewind to a snapshot taken at most one block earlier.  The K nibble planes of blocks written since are
+        zeroed because the K writer accumulates nibbles (extension/csrc/K_cache.cu:52-56)."""
+        first_blk = snap["rest_start"] // column_block
+        last_blk = cdiv(self.cache_len, column_block)
+        if last_blk > first_blk:
+            self.k_mid_4[:, :, first_blk:last_blk].zero_()
+            self.k_last_4[:, :, first_blk:last_blk].zero_()
+        self.restk.copy_(snap["restk"])
+        self.restv.copy_(snap["restv"])
+        self.k_exp_max.copy_(snap["k_exp"])
+        self.v_exp_max.copy_(snap["v_exp"])
+        self.rest_len, self.rest_start, self.cache_len = snap["rest_len"], snap["rest_start"], snap["cache_len"]
+
+    def reset_counters(self) -> None:
+        self.launches = 0
+        self.lib.akv_set_tuning(b"timing", 1)
+        self.lib.akv_timing_reset()
+
+    def kernel_times(self):
+        """Mean CUDA-event duration of the two streaming kernels over the steps since reset_counters()."""
+        torch.cuda.synchronize(self.device)
+        k_us, v_us = ctypes.c_double(0), ctypes.c_double(0)
+        n = self.lib.akv_timing_read(ctypes.byref(k_us), ctypes.byref(v_us))
+        self.lib.akv_set_tuning(b"timing", 0)
+        if n == 0:
+            return {}
+        return {"k_compute": {"us": k_us.value, "launches": n}, "v_compute": {"us": v_us.value, "launches": n}}
+
+    def bytes_accounting(self, q: torch.Tensor):
+        """Algorithmic plane bytes of the LAST decode step under its read decisions (mid plane iff code < 2, low
+        plane iff code < 1), from the state the step left behind, plus the dense fp16 equivalent."""
+        B, H, D = self.B, self.H, self.D
+        qn = self.rest_start
+        kq = exponent_field(q) + self.k_exp_max
+        diff = (kq.max(dim=3, keepdim=True).values - kq)
+        k_rows = float(B * H * D) + 0.5 * float((diff < 8).sum()) + 0.5 * float((diff < 4).sum())
+        k_bytes = qn * k_rows
+        R = (qn // column_block + 1) * column_block
+        p = self.scratch[:B * H * R * 2].view(torch.half).view(B, H, R)[..., :qn]
+        amin_off = self._scratch_offset("amin")
+        amin = self.scratch[amin_off:amin_off + B * H].to(torch.int32).view(B, H, 1)
+        d = ((((amin << 10) & 0xFFFF) - p.view(torch.int16).to(torch.int32)) << 16) >> 16
+        v_rows = float(B * H * qn) + 0.5 * float((d < 0x800).sum()) + 0.5 * float((d < 0x400).sum())
+        v_bytes = D * v_rows
+        rest = 4.0 * (self.cache_len - qn) * D * B * H
+        dense = 4.0 * B * H * self.cache_len * D
+        return {"k_compute": k_bytes, "v_compute": v_bytes, "read": k_bytes + v_bytes + rest, "dense": dense}
+
+    def _scratch_offset(self, name: str) -> int:
+        B, H, D = self.B, self.H, self.D
+        R = (cdiv(self.L, column_block) + 1) * column_block
+        up = lambda x: (x + 255) & ~255  # noqa: E731
+        sizes = [("s", B * H * R * 2), ("kq", B * H * D), ("kqmax", B * H), ("pval", B * H * 32 * 2),
+                 ("pidx", B * H * 32 * 4), ("test_o", B * H * D * 2), ("amin", B * H), ("o_main", B * H * D * 2)]
+        off = 0
+        for n, sz in sizes:
+            if n == name:
+                return off
+            off += up(sz)
+        raise KeyError(name)

@@ -1,0 +1,281 @@
+#!/usr/bin/env python
+"""Benchmark of the AlignedKV decode hot path on B200: one layer of Llama-2-7B-shaped decode attention.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step = rewind the cache to 4095 cached tokens, append token 4096 of every sequence (which flushes a 64-token
+block through the plane-writer kernels), then one decode step (aligned q.K^T, softmax, probe, aligned P.V).
+At N > 1 (launched with torchrun, one rank per GPU) every rank owns an independent shard of (batch, head) units of
+the same size - no collective is on the data path - so the job processes N x batch sequences per step.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the reference's CPU path (its torch dense attention,
+restated in oracle/pipeline.py) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Llama-2-7B-shaped decode attention, one layer (the configuration the metric is quoted on)
+WORKLOAD = dict(name="llama2-7b-layer-decode", batch=8, heads=32, head_dim=128, cache_len=4096)
+OUTLIER_CHANNELS = (3, 34, 65, 96)
+METRIC = "decode_attention_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------- CPU baseline
+def cpu_dense_baseline(seed: int, budget_s: float = 12.0):
+    """The reference's torch dense-attention path on the host cores, on a bounded sample of the workload:
+    one batch row (all heads, full cache length), repeated while the time budget lasts."""
+    import torch
+    from oracle.pipeline import dense_attention_torch_cpu
+    H, D, L = WORKLOAD["heads"], WORKLOAD["head_dim"], WORKLOAD["cache_len"]
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(1, L, H, D, generator=g)
+    k[..., list(OUTLIER_CHANNELS)] *= 20
+    k = k.half()
+    v = torch.randn(1, L, H, D, generator=g).half()
+    q = torch.randn(1, 1, H, D, generator=g).half()
+    cores = torch.get_num_threads()
+    dense_attention_torch_cpu(q, k, v)  # warm-up
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < 5 or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        dense_attention_torch_cpu(q, k, v)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"value": 1.0 / med, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"1 of {WORKLOAD['batch']} batch rows (32 heads x 4096 cached tokens), median of {len(times)} "
+                      f"runs of the reference's fp16 torch dense attention on CPU"}, med
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, med = cpu_dense_baseline(args.seed, budget_s=20.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": med * 1e3 * WORKLOAD["batch"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], **{k: v for k, v in WORKLOAD.items() if k != "name"},
+                   "note": "reference's torch dense fp16 attention on the host cores; per-step time extrapolated "
+                           "from one batch row"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for ln in self.proc.stdout:
+            self.lines.append((time.perf_counter(), ln.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return None
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [ln.split(", ") for t, ln in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or \
+               [ln.split(", ") for _, ln in self.lines[-3:]]
+        sm, reasons, mx = [], set(), None
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: alignedkv_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from alignedkv_b200 import _lib
+    from alignedkv_b200.decode import DecodeLayer
+    _lib.load()
+
+    B, H, D, L = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["head_dim"], WORKLOAD["cache_len"]
+    g = torch.Generator(device=dev).manual_seed(args.seed + 1000 * rank)
+    k = torch.randn(B, L, H, D, device=dev, generator=g)
+    k[..., list(OUTLIER_CHANNELS)] *= 20
+    k = k.half()
+    v = torch.randn(B, L, H, D, device=dev, generator=g).half()
+    q = torch.randn(B, 1, H, D, device=dev, generator=g).half()
+
+    layer = DecodeLayer(B, L, H, D, dev)
+    layer.prefill(k[:, :L - 1].contiguous(), v[:, :L - 1].contiguous())
+    snap = layer.snapshot()                                # state with 4095 cached tokens (63 in the residual)
+    k_tok, v_tok = k[:, L - 1:].contiguous(), v[:, L - 1:].contiguous()
+    del k, v
+
+    def step_resident():
+        layer.restore(snap)
+        return layer.decode(q, k_tok, v_tok)
+
+    # host-side buffers for the end-to-end number (pinned), device staging buffers, pinned result
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k_tok, v_tok))
+    dq, dk, dv = (torch.empty_like(t) for t in (q, k_tok, v_tok))
+    hout = torch.empty((B, 1, H, D), dtype=torch.half).pin_memory()
+
+    def step_e2e():
+        layer.restore(snap)
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        out = layer.decode(dq, dk, dv)
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # the caller reads the result on the host
+        return hout
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, sampler=None):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        ms = e0.elapsed_time(e1)
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, t0, t1
+
+    warm = max(args.warmup, 3)
+    sampler = ClockSampler(local) if rank == 0 else None
+    layer.reset_counters()
+    if sampler:
+        sampler.start()
+    ms, t0, t1 = timed(step_resident, args.steps, warm)
+    clocks = sampler.stop(t0, t1) if sampler else None
+    launches = layer.launches // (args.steps + warm)       # kernels of this library per step
+    kern = layer.kernel_times()                            # per-kernel CUDA-event durations inside the timed region
+    ms_e2e, _, _ = timed(step_e2e, args.steps, warm)
+
+    if rank == 0:
+        ms_step = ms / args.steps
+        tokens = B * world
+        acct = layer.bytes_accounting(q)                   # algorithmic bytes under this step's read decisions
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        dom = max(kern, key=lambda n: kern[n]["us"]) if kern else None
+        roofline = None
+        if dom:
+            a = acct[dom] / (kern[dom]["us"] * 1e-6) / 1e9
+            roofline = {"bound": "hbm", "kernel": dom, "achieved": a, "peak": peak, "unit": "GB/s", "frac": a / peak,
+                        "peak_source": "measured" if peaks else "fallback",
+                        "traffic": layer.NCU_TRAFFIC.get(dom), "us_per_launch": kern[dom]["us"],
+                        "algorithmic_bytes": acct[dom]}
+        line = {
+            "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD["name"], **{k_: v_ for k_, v_ in WORKLOAD.items() if k_ != "name"},
+                       "per_gpu_batch": B, "global_batch": tokens, "sharding": "(batch, kv-head) units, no collective",
+                       "step": "rewind to 4095 tokens -> append token 4096 (flushes a 64-token block through the "
+                               "plane writers) -> decode",
+                       "l2": "inputs larger than L2 (planes 512 MiB, ~0.3 GB read per step)"},
+            "effective_hbm_gbs": acct["dense"] * world / (ms_step * 1e-3) / 1e9,
+            "achieved_hbm_gbs": acct["read"] * world / (ms_step * 1e-3) / 1e9,
+            "bytes_read_over_dense": acct["read"] / acct["dense"],
+            "kernels_us": {n: round(kv_["us"], 2) for n, kv_ in kern.items()},
+            "roofline": roofline,
+            "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int(3 * q.numel() * 2), "d2h_bytes_per_step": int(hout.numel() * 2),
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = cpu_dense_baseline(args.seed)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -40,7 +40,7 @@ const char* akv_last_error(void);
 
 /*
  * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16, "k_prefetch" 0..64,
- * "v_stages" 4|6|8, "v_prefetch" 0..64).
+ * "v_stages" 4|6|8, "v_prefetch" 0..64, "timing" 0|1).
  * Process-wide; results never depend on them.  No counterpart in the reference.
  */
 int akv_set_tuning(const char* key, int value);
@@ -100,6 +100,39 @@ int akv_v_cache_compute(const void* v_first_8, const void* v_mid_4, const void* 
                         const void* s, const void* amin, void* o_out,
                         int bsz, int n_local_kv_heads, int max_seq_len, int head_dim, int s_last_dim,
                         int start_pos_add_seqlen, int reference, void* stream);
+
+/*
+ * One decode step of one layer in a single call: what the reference does between receiving (q, k_new, v_new) of a
+ * decode token and returning the attention output - K_Cache_Class.save + decoding_compute
+ * (extension/k_cache_file.py:97-118,132-159), the fp32 softmax (model/KVCache_AlignedKV.py:119-121, no mask) and
+ * V_Cache_Class.save + decoding_compute (extension/v_cache_file.py:97-116,119-190) - with the wrapper's small
+ * tensor operations folded into kernels.  All pointers are device pointers:
+ *   planes as above; k_exp_max / v_exp_max [B,1,H,D] u8 (updated in place); restk / restv [B,64,H,D] fp16 residual
+ *   buffers (the new token is written at row rest_len); q, k_new, v_new [B,1,H,D] fp16; out [B,1,H,D] fp16;
+ *   scratch: workspace of at least akv_decode_scratch_bytes() bytes, 16-byte aligned, owned by the caller.
+ * rest_len / rest_start are the residual fill count and first buffered position BEFORE this token
+ * (the reference's restklen / reststartpos).  After the call the caller advances them: rest_len + 1, or
+ * (0, rest_start + 64) when rest_len was 63 (this call then also wrote that block to the planes).
+ * head_dim must be a multiple of 64.  Plane bytes and read decisions equal the operator-by-operator path; the
+ * softmax and the residual-token dot products are fp32 like torch's but may differ from it in the last bit.
+ */
+int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                    void* k_exp_max, void* v_exp_max, void* restk, void* restv,
+                    const void* q, const void* k_new, const void* v_new, void* out,
+                    void* scratch, long long scratch_bytes,
+                    int bsz, int n_heads, int head_dim, int max_seq_len, int rest_len, int rest_start,
+                    int reference, void* stream);
+
+/* Bytes of workspace akv_decode_step needs for these extents (-1 on bad extents). */
+long long akv_decode_scratch_bytes(int bsz, int n_heads, int head_dim, int max_seq_len);
+
+/*
+ * Benchmark instrumentation (no counterpart in the reference): with akv_set_tuning("timing", 1), akv_decode_step
+ * records CUDA events around its q.K^T and P.V launches.  akv_timing_read returns how many steps were recorded
+ * since akv_timing_reset and their mean launch durations in microseconds; synchronise the stream first.
+ */
+int akv_timing_reset(void);
+int akv_timing_read(double* k_us, double* v_us);
 
 #ifdef __cplusplus
 }
