@@ -22,6 +22,7 @@ SIGNATURES = {
     "akv_v_cache_test_compute": (_I, [_P] * 6 + [_I] * 5 + [_P]),
     "akv_v_cache_compute": (_I, [_P] * 6 + [_I] * 7 + [_P]),
     "akv_decode_step": (_I, [_P] * 15 + [ctypes.c_longlong] + [_I] * 7 + [_P]),
+    "akv_decode_step_noalloc": (_I, [_P] * 14 + [_I] * 7 + [_P]),
     "akv_decode_scratch_bytes": (ctypes.c_longlong, [_I] * 4),
     "akv_timing_reset": (_I, []),
     "akv_timing_read": (_I, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),

@@ -341,4 +341,57 @@ int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_firs
     return AKV_OK;
 }
 
+
+// ------------------------------------------------------------------ decode step without any allocation
+// Some callers may not allocate device memory at all: a serving process whose memory pool was carved up at start-up
+// and whose allocator is locked afterwards, a plugin that runs inside somebody else's stream callback or real-time
+// loop where cudaMalloc (which synchronises the device) is forbidden, or code that only holds raw pointers handed
+// to it.  For them the workspace of the decode step lives in this library image instead: a fixed array in device
+// global memory that every GPU loading the library reserves until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[AKV_NOALLOC_SCRATCH_BYTES];
+
+namespace akv {
+// Device address of g_noalloc_scratch per device ordinal.  In host code the array's name is only a handle for
+// the runtime, not an address a kernel could use, so the address is looked up once per device (with that device
+// current) and cached.
+static void* g_noalloc_ptr[64] = {nullptr};
+
+static int noalloc_workspace(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e, "decode_step_noalloc: cudaGetDevice");
+    AKV_REQUIRE(dev >= 0 && dev < 64, AKV_ERR_SHAPE, "decode_step_noalloc: device ordinal %d is not supported", dev);
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_status(e, "decode_step_noalloc: cudaGetSymbolAddress");
+        AKV_REQUIRE(p != nullptr, AKV_ERR_CUDA, "decode_step_noalloc: the workspace symbol has no device address");
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return AKV_OK;
+}
+}  // namespace akv
+
+int akv_decode_step_noalloc(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4,
+                            void* v_last_4, void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q,
+                            const void* k_new, const void* v_new, void* out, int bsz, int n_heads, int head_dim,
+                            int max_seq_len, int rest_len, int rest_start, int reference, void* stream) {
+    set_error("");
+    const long long need = akv_decode_scratch_bytes(bsz, n_heads, head_dim, max_seq_len);
+    AKV_REQUIRE(need >= 0, AKV_ERR_SHAPE, "decode_step_noalloc: bad extent (bsz %d, heads %d, head_dim %d, "
+                "max_seq_len %d)", bsz, n_heads, head_dim, max_seq_len);
+    AKV_REQUIRE(need <= (long long)AKV_NOALLOC_SCRATCH_BYTES, AKV_ERR_SHAPE,
+                "decode_step_noalloc: these extents need a %lld-byte workspace but the built-in one holds %lld bytes; "
+                "use akv_decode_step with a caller-provided workspace", need, (long long)AKV_NOALLOC_SCRATCH_BYTES);
+    AKV_REQUIRE(!tuning().timing, AKV_ERR_SHAPE,
+                "decode_step_noalloc: the \"timing\" knob creates CUDA events, which allocates; switch it off");
+    void* ws = nullptr;
+    const int rc = noalloc_workspace(&ws);
+    if (rc != AKV_OK) return rc;
+    return akv_decode_step(k_first_8, k_mid_4, k_last_4, v_first_8, v_mid_4, v_last_4, k_exp_max, v_exp_max, restk, restv,
+                           q, k_new, v_new, out, ws, (long long)AKV_NOALLOC_SCRATCH_BYTES, bsz, n_heads, head_dim,
+                           max_seq_len, rest_len, rest_start, reference, stream);
+}
+
 }  // extern "C"

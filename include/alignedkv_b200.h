@@ -127,6 +127,28 @@ int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_firs
 long long akv_decode_scratch_bytes(int bsz, int n_heads, int head_dim, int max_seq_len);
 
 /*
+ * akv_decode_step for callers that cannot allocate device memory (no counterpart in the reference).
+ * Same arguments and results as akv_decode_step, minus the workspace: it lives in a fixed array of
+ * AKV_NOALLOC_SCRATCH_BYTES bytes of device global memory inside the library image, which every GPU that loads the
+ * library keeps reserved until the process exits.  The call itself performs no cudaMalloc / cudaFree and calls no
+ * allocating library routine.  Meant for hosts whose device memory was handed out once at start-up and is locked
+ * afterwards, and for code that runs where an allocation (which synchronises the device) is not allowed.
+ *  - Extents whose workspace (akv_decode_scratch_bytes) exceeds AKV_NOALLOC_SCRATCH_BYTES are rejected with
+ *    AKV_ERR_SHAPE; so is a call while the "timing" knob is on (creating events allocates).
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *    current); make that first call before any stream capture begins.
+ *  - All calls on a device share the one array and find the previous call's bytes in it.  Nothing in it has to
+ *    start at zero (every region is fully written before it is read within a call), but two calls that overlap on
+ *    the GPU - different streams, or different caches on one stream without ordering - race on it: serialise them.
+ */
+#define AKV_NOALLOC_SCRATCH_BYTES (8u << 20)
+int akv_decode_step_noalloc(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4,
+                            void* v_last_4, void* k_exp_max, void* v_exp_max, void* restk, void* restv,
+                            const void* q, const void* k_new, const void* v_new, void* out,
+                            int bsz, int n_heads, int head_dim, int max_seq_len, int rest_len, int rest_start,
+                            int reference, void* stream);
+
+/*
  * Benchmark instrumentation (no counterpart in the reference): with akv_set_tuning("timing", 1), akv_decode_step
  * records CUDA events around its q.K^T and P.V launches.  akv_timing_read returns how many steps were recorded
  * since akv_timing_reset and their mean launch durations in microseconds; synchronise the stream first.
