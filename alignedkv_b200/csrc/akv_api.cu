@@ -79,7 +79,7 @@ int akv_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "k_stages") && value >= 3 && value <= 6) t.k_stages = value;
     else if (!strcmp(key, "k_prefetch") && value >= 0 && value <= 101) t.k_prefetch = value;
     else if (!strcmp(key, "timing") && (value == 0 || value == 1)) t.timing = value;
-    else if (!strcmp(key, "debug") && value >= 0 && value <= 31) t.debug = value;
+    else if (!strcmp(key, "debug") && value >= 0 && value <= 255) t.debug = value;
     else if (!strcmp(key, "v_prefetch") && value >= 0 && value <= 64) t.v_prefetch = value;
     else if (!strcmp(key, "k_wpc") && value >= 0 && value <= 16) t.k_wpc = value;
     else if (!strcmp(key, "v_stages") && (value == 4 || value == 6 || value == 8)) t.v_stages = value;

@@ -5,12 +5,19 @@
 // fused-multiply-add chain over tokens 0..n-1 in order, skipped nibble planes are replaced by the reference's
 // constants (V_cache.cu:198-202,250-253).
 //
-// Design (B200): one CTA of 64 threads per (batch, head) - thread c owns channels 2c, 2c+1 and their serial
-// chains.  What the reference leaves latency-bound (every token waits for four dependent byte loads) is
-// decoupled here: the CTA streams 64-token stages of the high-byte plane through a deep ring of shared memory
-// with 16-byte asynchronous copies, thread t decides from the probability bits of token t whether that token's
-// 64-byte mid / low rows are fetched at all, and the consumer loop runs from shared memory at FMA latency.
-// Runs of 8 tokens that need no nibble plane (the common case) take a 3-instruction-per-token path.
+// Design (B200): the exact token order leaves only B*H*D/2 independent chains - two warps per (batch, head) -
+// and those warps are bound by their own instruction stream, so the kernel is organised around keeping that
+// stream minimal and never letting it wait for memory.  One CTA per (batch, head), two roles:
+//   chain warps (64 threads, thread c owns channels 2c, 2c+1): per token one 2-byte shared load, one byte permute
+//     and one FMA; the loads and permutes of 32 tokens are issued before their dependent chain starts.
+//   loader warps (64 threads, thread t owns token t of every 64-token stage): take the token's probability from a
+//     register pipeline fetched four stages ahead, decide from its bit pattern which of the token's 64-byte nibble
+//     rows are needed, and issue 16-byte asynchronous copies: the 8 KB of high bytes into a deep ring of
+//     high-byte-only stages, and - only for a run of 32 tokens in which some token needs a nibble plane - the
+//     rows into a small side ring (rows that are not read get the reference's substitute constants).  Completion
+//     is tracked by shared-memory mbarriers that the copies arrive on by themselves, so a loader never waits for
+//     data, only for a free slot.
+// Every wait is a bounded spin; a wait that gives up raises a flag the host can read (akv_device_error_flag).
 #include "akv_common.cuh"
 
 namespace akv {
@@ -27,244 +34,220 @@ struct VParams {
     const uint8_t* amin;
     uint16_t* o;
     int max_seq_len, D, s_last_dim, n, reference;
-    int pf_dist;   // L2 prefetch distance in stages (0 = off)
     int debug;
 };
 
 __device__ __forceinline__ void st_shared_row16(uint32_t a, uint32_t v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(a), "r"(v) : "memory");
 }
-// Named barriers (ids 1..15): producers and consumers hand stages over without spinning.
-__device__ __forceinline__ void bar_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+
+// ---- shared-memory barriers (mbarrier) with bounded waits
+static __device__ unsigned int g_v_wait_gave_up = 0;   // set when a bounded wait ran out (never expected)
+
+__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(count) : "memory");
 }
-__device__ __forceinline__ void bar_arrive(int id, int count) {
-    asm volatile("bar.arrive %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint32_t a) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(a) : "memory");
+}
+// arrives (without raising the pending count) once all earlier async copies of this thread have landed
+__device__ __forceinline__ void mbar_arrive_on_copies(uint32_t a) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(a) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity) {
+    for (int spin = 0; spin < (1 << 22); ++spin) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    atomicOr(&g_v_wait_gave_up, 1u);
+    return false;
 }
 
 // Shared-memory plan of one CTA.
-//   raw ring   RAW stages of [F: 64*D][M: 64*D/2][L: 64*D/2]                 filled by 16-byte async copies
-//   ready ring RDY stages of [kv: 64 tokens x D/2 fp16x2 words][s2: 64 words]   filled by the unpackers
-//   s ring     8 chunks of 64 probabilities, copied SA stages before the stage that needs them, so that the
-//              plane-read decision of a token never waits for a global load
-//   meta       per raw stage: the 64 probability words and two "lean" flags (one per 32 tokens)
-template <int D, int RAW, int RDY>
+//   F ring     NS stages of 64 tokens x D high bytes, filled by 16-byte async copies
+//   meta       per stage: 64 probability words (both halves equal) and, per run of 32 tokens, the side-ring slot
+//              that holds its nibble rows (-1: the run needs none)
+//   side ring  per loader warp NML slots of [32 tokens x D/2 mid bytes][32 tokens x D/2 low bytes]
+//   barriers   full / empty per stage, empty per side-ring slot
+template <int D, int NS, int NML>
 struct VPlan {
     static constexpr int TOK = vc::TOK;
     static constexpr int HD = D / 2;
     static constexpr int F_BYTES = TOK * D;
-    static constexpr int N_BYTES = TOK * HD;
-    static constexpr int RAW_BYTES = F_BYTES + 2 * N_BYTES;
-    static constexpr int KV_BYTES = TOK * HD * 4;
-    static constexpr int RDY_BYTES = KV_BYTES + TOK * 4;
-    static constexpr int RDY_OFF = RAW * RAW_BYTES;
-    static constexpr int SRING = 8;
-    static constexpr int S_OFF = RDY_OFF + RDY * RDY_BYTES;
-    static constexpr int META_OFF = S_OFF + SRING * TOK * 2;
+    static constexpr int META_OFF = NS * F_BYTES;
     static constexpr int META_BYTES = TOK * 4 + 16;
-    static constexpr int BYTES = META_OFF + RAW * META_BYTES;
+    static constexpr int ML_OFF = META_OFF + NS * META_BYTES;
+    static constexpr int ML_BYTES = 32 * HD * 2;
+    static constexpr int BAR_OFF = ML_OFF + 2 * NML * ML_BYTES;
+    static constexpr int BYTES = BAR_OFF + (2 * NS + 2 * NML) * 8;
 };
 
-// Threads [0, D/2): chain warps - thread c owns channels 2c, 2c+1 and runs their serial fp16 chains from the
-// ready ring (per token: one shared load and one FMA, nothing else).
-// Threads [D/2, D/2 + 32*NSTG): staging warps - they issue the async copies of a stage, decide from the
-// probability bits of each token which nibble rows are fetched (staging thread t < 64 owns token t), and
-// reassemble landed stages into fp16x2 words for the chain warps.
-template <int RAW, int RDY, int D, int NSTG>
-__global__ void __launch_bounds__(D / 2 + 32 * NSTG) v_compute_kernel(const VParams p) {
-    using P = VPlan<D, RAW, RDY>;
+template <int NS, int NML, int D>
+__global__ void __launch_bounds__(D) v_compute_kernel(const VParams p) {
+    using P = VPlan<D, NS, NML>;
     constexpr int TOK = P::TOK;
-    constexpr int NC = D / 2;                      // chain threads
-    constexpr int NS = 32 * NSTG;                  // staging threads
-    constexpr int NT = NC + NS;
-    constexpr int HD = P::HD;
-    constexpr int F_OPS = (P::F_BYTES / 16 + NS - 1) / NS;   // 16-byte copies per staging thread, high-byte plane
-    constexpr int ROW_OPS = HD / 16;                          // 16-byte copies per nibble row
-    constexpr int ITEMS = TOK * (D / 8) / NS;                 // (token, 8-channel) pieces per staging thread
-    constexpr int SA = 4;                          // probability chunks run SA stages ahead of the plane copies
-    static_assert(NC == TOK, "one chain thread per staged token is assumed by the ready-stage layout");
-    static_assert(NS >= TOK && (TOK * (D / 8)) % NS == 0, "staging thread count");
-    static_assert(SA >= RAW - 1 && SA + RAW <= P::SRING, "s ring depth");
-    static_assert(RDY >= 2 && 2 * RDY + 1 <= 15, "named barriers");
+    constexpr int NC = D / 2;                      // chain threads; thread c owns channels 2c, 2c+1
+    constexpr int NL = TOK;                        // loader threads; thread t owns token t of a stage
+    constexpr int HD = P::HD;                      // nibble row bytes
+    constexpr int F_OPS = P::F_BYTES / 16 / NL;    // 16-byte copies per loader thread for the high-byte plane
+    constexpr int ROW_OPS = HD / 16;               // 16-byte copies per nibble row
+    static_assert(NC == 64 && NL == 64, "two chain warps and two loader warps");
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x;
     const long long bh = blockIdx.x;
     const int n = p.n;
     const int nst = (n + TOK - 1) / TOK;
     const uint32_t base = smem_u32(smem);
-    // barrier ids: 1 = staging warps only; 2+2r = ready slot r full; 3+2r = ready slot r empty
+    const uint32_t bar_full = base + P::BAR_OFF, bar_empty = bar_full + NS * 8, bar_ml = bar_empty + NS * 8;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(bar_full + s * 8, 2 * NL);    // per loader thread: one arrival by its copies, one by itself
+            mbar_init(bar_empty + s * 8, NC);
+        }
+        for (int s = 0; s < 2 * NML; ++s) mbar_init(bar_ml + s * 8, NC);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
 
     if (tid < NC) {
         // ------------------------------------------------------------------ chain warps
-        const int c = tid;
         uint32_t acc = 0;
-        for (int i = 0; i < nst; ++i) {
-            const int slot = i % RDY;
-            bar_sync(2 + 2 * slot, NT);
-            const uint32_t ra = base + P::RDY_OFF + (uint32_t)slot * P::RDY_BYTES;
-            const uint32_t kva = ra + c * 4;              // + t * NC * 4
-            const uint32_t sa = ra + P::KV_BYTES;         // + t * 4 (probability in both halves)
+        int slot = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int i = 0; i < nst && alive; ++i) {
+            alive = mbar_wait(bar_full + slot * 8, phase);
+            const uint32_t fa = base + (uint32_t)slot * P::F_BYTES + tid * 2;            // + t * D
+            const uint32_t ma = base + P::META_OFF + (uint32_t)slot * P::META_BYTES;     // s2 words, then 2 slot ids
             const int cnt = (n - i * TOK) < TOK ? (n - i * TOK) : TOK;
-            if (cnt == TOK && !(p.debug & 1)) {
-                uint32_t cur[16], nxt[16];
-                uint4 cs[4], ns[4];
+            if (!(p.debug & 1)) {
 #pragma unroll
-                for (int u = 0; u < 16; ++u) cur[u] = lds32(kva + u * NC * 4);
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int tb = hf * 32;
+                    const int ms = (int)lds32(ma + TOK * 4 + hf * 4);
+                    if (ms < 0) {
+                        // 32 tokens, high byte only: k~ = [0x80, f_even, 0x80, f_odd]
+                        uint32_t f[32];
+                        uint4 sv[8];
 #pragma unroll
-                for (int v = 0; v < 4; ++v) cs[v] = lds128(sa + v * 16);
+                        for (int u = 0; u < 32; ++u) f[u] = lds16(fa + (tb + u) * D);
 #pragma unroll
-                for (int b = 0; b < TOK / 16; ++b) {
+                        for (int v = 0; v < 8; ++v) sv[v] = lds128(ma + (tb + 4 * v) * 4);
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        if (b + 1 < TOK / 16) {   // next batch's loads ride between the dependent FMAs
-                            ns[v] = lds128(sa + ((b + 1) * 4 + v) * 16);
+                        for (int u = 0; u < 32; ++u) f[u] = __byte_perm(f[u], 0x80u, 0x1404);
 #pragma unroll
-                            for (int w = 0; w < 4; ++w) nxt[4 * v + w] = lds32(kva + ((b + 1) * 16 + 4 * v + w) * NC * 4);
+                        for (int v = 0; v < 8; ++v) {
+                            acc = hfma2_bits(f[4 * v], sv[v].x, acc);
+                            acc = hfma2_bits(f[4 * v + 1], sv[v].y, acc);
+                            acc = hfma2_bits(f[4 * v + 2], sv[v].z, acc);
+                            acc = hfma2_bits(f[4 * v + 3], sv[v].w, acc);
                         }
-                        acc = hfma2_bits(cur[4 * v], cs[v].x, acc);
-                        acc = hfma2_bits(cur[4 * v + 1], cs[v].y, acc);
-                        acc = hfma2_bits(cur[4 * v + 2], cs[v].z, acc);
-                        acc = hfma2_bits(cur[4 * v + 3], cs[v].w, acc);
+                    } else {
+                        const uint32_t mla = base + P::ML_OFF + (uint32_t)(hf * NML + ms) * P::ML_BYTES + tid;
+                        const int end = cnt < tb + 32 ? cnt : tb + 32;
+                        for (int t0 = tb; t0 < end; t0 += 8) {
+                            uint32_t f[8], mb[8], lb[8], s2[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int t = t0 + u;   // rows past the stage's tokens hold stale bytes; not used
+                                f[u] = lds16(fa + t * D);
+                                mb[u] = lds8(mla + (t - tb) * HD);
+                                lb[u] = lds8(mla + 32 * HD + (t - tb) * HD);
+                                s2[u] = lds32(ma + t * 4);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                if (t0 + u < end) {
+                                    const uint32_t lo_e = (mb[u] & 0xF0u) | (lb[u] >> 4);            // even channel
+                                    const uint32_t lo_o = ((mb[u] << 4) & 0xF0u) | (lb[u] & 0x0Fu);  // odd channel
+                                    acc = hfma2_bits(__byte_perm(f[u], lo_e | (lo_o << 8), 0x1504), s2[u], acc);
+                                }
+                            }
+                        }
+                        mbar_arrive(bar_ml + (hf * NML + ms) * 8);   // the side-ring slot may be refilled
                     }
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) cs[v] = ns[v];
                 }
-            } else if (!(p.debug & 1)) {
-                for (int t = 0; t < cnt; ++t) acc = hfma2_bits(lds32(kva + t * NC * 4), lds32(sa + t * 4), acc);
             }
-            if (i + RDY < nst) bar_arrive(3 + 2 * slot, NT);   // hand the slot back if it is needed again
+            mbar_arrive(bar_empty + slot * 8);
+            if (++slot == NS) { slot = 0; phase ^= 1; }
         }
-        reinterpret_cast<uint32_t*>(p.o)[(size_t)bh * NC + c] = acc;
+        reinterpret_cast<uint32_t*>(p.o)[(size_t)bh * NC + tid] = acc;
         return;
     }
 
-    // ---------------------------------------------------------------------- staging warps
-    const int pt = tid - NC;                     // staging thread index; pt < 64 owns token pt of every stage
+    // ---------------------------------------------------------------------- loader warps
+    const int pt = tid - NC, lane = pt & 31, pw = pt >> 5;
     const uint8_t* F = p.first8 + (size_t)bh * p.max_seq_len * D;
     const uint8_t* M = p.mid4 + (size_t)bh * p.max_seq_len * HD;
     const uint8_t* L = p.last4 + (size_t)bh * p.max_seq_len * HD;
     const uint16_t* s_row = p.s + (size_t)bh * p.s_last_dim;
     const uint32_t A = ((uint32_t)p.amin[bh] << 10) & 0xFFFFu;
-
-    // chunk of 64 probabilities for stage j -> s ring (8 threads x 16 bytes); beyond n nothing is copied and
-    // the decision code below treats those tokens as absent
-    auto stage_s = [&](int j) {
-        const int t0 = j * TOK + pt * 8;
-        if (pt < 8 && t0 < n)
-            cp_async16(base + P::S_OFF + (uint32_t)(j % P::SRING) * (TOK * 2) + pt * 16, s_row + t0);
+    auto load_s = [&](int j) -> uint32_t {   // probability of this thread's token of stage j (0 beyond n)
+        const int t = j * TOK + pt;
+        return (t < n) ? (uint32_t)__ldg(s_row + t) : 0u;
     };
+    int slot = 0, ml_used = 0;          // stage slot; side-ring slots this warp has handed out so far
+    uint32_t phase = 0;
+    bool alive = true;
 
-    auto issue = [&](int j, int rslot) {
-        const uint32_t st = base + (uint32_t)rslot * P::RAW_BYTES;
+    auto stage = [&](int j, uint32_t sb) {
+        if (j >= NS) alive = alive && mbar_wait(bar_empty + slot * 8, phase ^ 1);   // stage j-NS has been consumed
+        const uint32_t st = base + (uint32_t)slot * P::F_BYTES;
         const int t0 = j * TOK;
         const int cnt = (n - t0) < TOK ? (n - t0) : TOK;
         const int fbytes = cnt * D;  // high-byte plane: cnt*D contiguous bytes
         if (!(p.debug & 2)) {
 #pragma unroll
             for (int it = 0; it < F_OPS; ++it) {
-                const int off = (it * NS + pt) << 4;
+                const int off = (it * NL + pt) << 4;
                 if (off < fbytes) cp_async16(st + off, F + (size_t)t0 * D + off);
             }
         }
-        stage_s(j + SA);
-        if (pt < TOK) {
-            const uint32_t sb = (pt < cnt) ? lds16(base + P::S_OFF + (uint32_t)(j % P::SRING) * (TOK * 2) + pt * 2) : 0u;
-            // decision from the bit patterns (V_cache.cu:211,250-251): 16-bit wrap-around, signed compare
-            const int diff = (int)(int16_t)(uint16_t)(A - sb);
-            int code = p.reference ? 0 : (diff >= 0x0800 ? 2 : (diff >= 0x0400 ? 1 : 0));
-            if (pt >= cnt) code = 2;
-            // 32 tokens are "lean" when all of them exist and none reads a nibble plane
-            const bool lean = __all_sync(0xFFFFFFFFu, code == 2) && (t0 + (pt & 32) + 32 <= n);
-            const uint32_t ma = base + P::META_OFF + (uint32_t)rslot * P::META_BYTES;
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(ma + pt * 4), "r"(sb | (sb << 16)) : "memory");
-            if ((pt & 31) == 0)
-                asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(ma + TOK * 4 + (pt >> 5) * 4), "r"((uint32_t)lean)
-                             : "memory");
-            if (!lean) {
-                // rows the rule reads are fetched; the others get the reference's substitute bytes (mid 0x88 /
-                // low 0x00 when neither is read, low 0x88 when only mid is read): unpacking needs no branch
-                const size_t src = (size_t)(t0 + pt) * HD;
-                const uint32_t dm = st + P::F_BYTES + pt * HD, dl = dm + P::N_BYTES;
+        // decision from the bit patterns (V_cache.cu:211,250-251): 16-bit wrap-around, signed compare
+        const int diff = (int)(int16_t)(uint16_t)(A - sb);
+        int code = p.reference ? 0 : (diff >= 0x0800 ? 2 : (diff >= 0x0400 ? 1 : 0));
+        if (pt >= cnt) code = 2;
+        // this warp's 32 tokens are "lean" when all of them exist and none reads a nibble plane
+        const bool lean = __all_sync(0xFFFFFFFFu, code == 2) && (t0 + pw * 32 + 32 <= n);
+        const uint32_t ma = base + P::META_OFF + (uint32_t)slot * P::META_BYTES;
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(ma + pt * 4), "r"(sb | (sb << 16)) : "memory");
+        int ms = -1;
+        if (!lean) {
+            ms = ml_used % NML;
+            if (ml_used >= NML) alive = alive && mbar_wait(bar_ml + (pw * NML + ms) * 8, ((ml_used / NML) & 1) ^ 1);
+            ++ml_used;
+            // rows the rule reads are fetched; the others get the reference's substitute bytes (mid 0x88 / low 0x00
+            // when neither is read, low 0x88 when only mid is read), so the consumer has no per-token branch
+            const size_t src = (size_t)(t0 + pt) * HD;
+            const uint32_t dm = base + P::ML_OFF + (uint32_t)(pw * NML + ms) * P::ML_BYTES + lane * HD;
+            const uint32_t dl = dm + 32 * HD;
 #pragma unroll
-                for (int v = 0; v < ROW_OPS; ++v) {
-                    if (code < 2) cp_async16(dm + v * 16, M + src + v * 16);
-                    else st_shared_row16(dm + v * 16, 0x88888888u);
-                    if (code == 0) cp_async16(dl + v * 16, L + src + v * 16);
-                    else st_shared_row16(dl + v * 16, code == 1 ? 0x88888888u : 0u);
-                }
+            for (int v = 0; v < ROW_OPS; ++v) {
+                if (code < 2) cp_async16(dm + v * 16, M + src + v * 16);
+                else st_shared_row16(dm + v * 16, 0x88888888u);
+                if (code == 0) cp_async16(dl + v * 16, L + src + v * 16);
+                else st_shared_row16(dl + v * 16, code == 1 ? 0x88888888u : 0u);
             }
         }
+        if (lane == 0) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(ma + TOK * 4 + pw * 4), "r"(ms) : "memory");
+        mbar_arrive_on_copies(bar_full + slot * 8);   // fires when this thread's copies (all of them) have landed
+        mbar_arrive(bar_full + slot * 8);             // publishes this thread's plain stores
+        if (++slot == NS) { slot = 0; phase ^= 1; }
     };
 
-    // Reassemble raw stage rslot into ready slot dslot: token rows of D/2 fp16x2 words [lo_e, f_e, lo_o, f_o].
-    // Piece = (token, 8 channels): 8 raw bytes in, 16 ready bytes out; consecutive threads take consecutive
-    // pieces, so neither side has bank conflicts.
-    auto unpack = [&](int rslot, int dslot) {
-        const uint32_t raw = base + (uint32_t)rslot * P::RAW_BYTES;
-        const uint32_t rdy = base + P::RDY_OFF + (uint32_t)dslot * P::RDY_BYTES;
-        const uint32_t ma = base + P::META_OFF + (uint32_t)rslot * P::META_BYTES;
-        if (pt < TOK) {
-            const uint32_t s2 = lds32(ma + pt * 4);
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(rdy + P::KV_BYTES + pt * 4), "r"(s2) : "memory");
-        }
-        uint2 f[ITEMS];
-        uint32_t lean[ITEMS], m[ITEMS], l[ITEMS];
-#pragma unroll
-        for (int k = 0; k < ITEMS; ++k) {
-            const int item = k * NS + pt;
-            const int t = item / (D / 8);
-            f[k] = lds64(raw + item * 8);
-            lean[k] = lds32(ma + TOK * 4 + (t >> 5) * 4);     // warp-uniform: a warp's 32 pieces span 2 tokens
-        }
-#pragma unroll
-        for (int k = 0; k < ITEMS; ++k) {
-            const int item = k * NS + pt;
-            m[k] = 0x88888888u;
-            l[k] = 0u;
-            if (!lean[k]) {
-                m[k] = lds32(raw + P::F_BYTES + item * 4);
-                l[k] = lds32(raw + P::F_BYTES + P::N_BYTES + item * 4);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < ITEMS; ++k) {
-            const int item = k * NS + pt;
-            // byte j of le / lo: low byte of the even / odd channel of pair j
-            const uint32_t le = (m[k] & 0xF0F0F0F0u) | ((l[k] >> 4) & 0x0F0F0F0Fu);
-            const uint32_t lo = ((m[k] << 4) & 0xF0F0F0F0u) | (l[k] & 0x0F0F0F0Fu);
-            const uint32_t a0 = __byte_perm(le, lo, 0x5140), a1 = __byte_perm(le, lo, 0x7362);  // [le,lo] x2
-            const uint32_t w0 = __byte_perm(a0, f[k].x, 0x5140), w1 = __byte_perm(a0, f[k].x, 0x7362);
-            const uint32_t w2 = __byte_perm(a1, f[k].y, 0x5140), w3 = __byte_perm(a1, f[k].y, 0x7362);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(rdy + item * 16), "r"(w0), "r"(w1), "r"(w2),
-                         "r"(w3) : "memory");
-        }
-    };
-
-    for (int j = 0; j < SA && j < nst; ++j) stage_s(j);
+    uint32_t s0 = load_s(0), s1 = load_s(1), s2 = load_s(2), s3 = load_s(3);
+    for (int j0 = 0; j0 < nst && alive; j0 += 4) {
+        stage(j0, s0);
+        s0 = load_s(j0 + 4);
+        if (j0 + 1 < nst) { stage(j0 + 1, s1); s1 = load_s(j0 + 5); }
+        if (j0 + 2 < nst) { stage(j0 + 2, s2); s2 = load_s(j0 + 6); }
+        if (j0 + 3 < nst) { stage(j0 + 3, s3); s3 = load_s(j0 + 7); }
+    }
     cp_async_commit();
-    cp_async_wait<0>();
-    bar_sync(1, NS);
-    for (int j = 0; j < RAW - 1; ++j) {
-        if (j < nst) issue(j, j);
-        cp_async_commit();
-    }
-    int rslot = 0;
-    for (int i = 0; i < nst; ++i) {
-        cp_async_wait<RAW - 2>();
-        bar_sync(1, NS);   // every staging thread's copies of stage i have landed; stage i-1 is fully unpacked
-        const int jr = (rslot == 0) ? RAW - 1 : rslot - 1;
-        if (i + RAW - 1 < nst) issue(i + RAW - 1, jr);
-        cp_async_commit();
-        const int dslot = i % RDY;
-        if (i >= RDY) bar_sync(3 + 2 * dslot, NT);   // chain warps are done with this ready slot
-        if (!(p.debug & 4)) unpack(rslot, dslot);
-        __threadfence_block();
-        bar_arrive(2 + 2 * dslot, NT);
-        rslot = (rslot + 1 == RAW) ? 0 : rslot + 1;
-    }
-    cp_async_wait<0>();
+    cp_async_wait<0>();   // this thread's copies must have landed before its shared memory goes away
 }
 
 // Any even head_dim: one thread per channel pair, planes read straight from global memory.
@@ -298,13 +281,13 @@ v_compute_generic_kernel(const VParams p, int bh_count) {
     }
 }
 
-template <int RAW, int RDY, int D, int NSTG>
+template <int NS, int NML, int D>
 static int launch_v_fast(const VParams& p, int BH, cudaStream_t st) {
-    size_t smem = (size_t)VPlan<D, RAW, RDY>::BYTES;
-    cudaError_t e = cudaFuncSetAttribute(v_compute_kernel<RAW, RDY, D, NSTG>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    size_t smem = (size_t)VPlan<D, NS, NML>::BYTES;
+    cudaError_t e = cudaFuncSetAttribute(v_compute_kernel<NS, NML, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
     if (e != cudaSuccess) return cuda_status(e, "v_cache_compute smem attribute");
-    v_compute_kernel<RAW, RDY, D, NSTG><<<BH, D / 2 + 32 * NSTG, smem, st>>>(p);
+    v_compute_kernel<NS, NML, D><<<BH, D, smem, st>>>(p);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
 }
 
@@ -317,7 +300,6 @@ int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     p.amin = amin;
     p.o = reinterpret_cast<uint16_t*>(o);
     p.max_seq_len = max_seq_len; p.D = D; p.s_last_dim = s_last_dim; p.n = n; p.reference = reference;
-    p.pf_dist = tuning().v_prefetch;
     p.debug = tuning().debug;
     const int BH = bsz * H;
     const bool fast = D == 128 && aligned16(first8) && aligned16(mid4) && aligned16(last4) &&
@@ -325,9 +307,9 @@ int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
                       ((reinterpret_cast<uintptr_t>(o) & 3u) == 0);
     if (fast) {
         const int stages = tuning().v_stages;
-        if (stages == 4) return launch_v_fast<4, 2, 128, 4>(p, BH, st);
-        if (stages == 8) return launch_v_fast<3, 2, 128, 8>(p, BH, st);
-        return launch_v_fast<4, 2, 128, 8>(p, BH, st);
+        if (stages == 4) return launch_v_fast<6, 2, 128>(p, BH, st);
+        if (stages == 8) return launch_v_fast<8, 2, 128>(p, BH, st);
+        return launch_v_fast<10, 2, 128>(p, BH, st);
     }
     long long total = (long long)BH * (D >> 1);
     long long want = (total + 127) / 128;
@@ -384,3 +366,12 @@ int launch_v_probe(const uint8_t* first8, const uint8_t* s_val, const uint8_t* s
 }
 
 }  // namespace akv
+
+extern "C" int akv_device_error_flag(void) {
+    // Non-zero once a bounded wait inside a kernel of this library gave up (never expected; the kernel then
+    // returned early and its output is invalid).  Reading the flag synchronises the device.
+    unsigned int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, akv::g_v_wait_gave_up, sizeof(v));
+    if (e != cudaSuccess) return akv::cuda_status(e, "device_error_flag");
+    return (int)v;
+}

@@ -39,6 +39,13 @@ int akv_abi_version(void);
 const char* akv_last_error(void);
 
 /*
+ * Device-side health flag (no counterpart in the reference): non-zero once a bounded wait inside a kernel of this
+ * library gave up - the kernel then returned early and its output is invalid.  Never expected in a healthy run.
+ * Reading it copies a word from the device, i.e. synchronises; negative values are AKV_ERR_* codes.
+ */
+int akv_device_error_flag(void);
+
+/*
  * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16, "k_prefetch" 0..64,
  * "v_stages" 4|6|8, "v_prefetch" 0..64, "timing" 0|1).
  * Process-wide; results never depend on them.  No counterpart in the reference.

@@ -110,6 +110,11 @@ def test_decode_step_rejects_bad_state(built):
     torch.cuda.synchronize()
 
 
+def test_no_kernel_wait_gave_up(built):
+    """Every in-kernel wait is bounded; the flag that a wait ran out must still be clear after the tests above."""
+    assert built.akv_device_error_flag() == 0
+
+
 def test_smoke_entry(built):
     import __graft_entry__
     __graft_entry__.smoke()
