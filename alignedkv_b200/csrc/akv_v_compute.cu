@@ -11,7 +11,7 @@
 //   chain warps (64 threads, thread c owns channels 2c, 2c+1): per token one 2-byte shared load, one byte permute
 //     and one FMA; the loads and permutes of 32 tokens are issued before their dependent chain starts.
 //   loader warps (64 threads, thread t owns token t of every 64-token stage): take the token's probability from a
-//     register pipeline fetched four stages ahead, decide from its bit pattern which of the token's 64-byte nibble
+//     shared buffer that is copied a whole 32-stage chunk ahead, decide from its bit pattern which of the token's 64-byte nibble
 //     rows are needed, and issue 16-byte asynchronous copies: the 8 KB of high bytes into a deep ring of
 //     high-byte-only stages, and - only for a run of 32 tokens in which some token needs a nibble plane - the
 //     rows into a small side ring (rows that are not read get the reference's substitute constants).  Completion
@@ -35,6 +35,7 @@ struct VParams {
     uint16_t* o;
     int max_seq_len, D, s_last_dim, n, reference;
     int debug;
+    unsigned long long* trace;   // experiments only
 };
 
 __device__ __forceinline__ void st_shared_row16(uint32_t a, uint32_t v) {
@@ -70,18 +71,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity) {
 //   meta       per stage: 64 probability words (both halves equal) and, per run of 32 tokens, the side-ring slot
 //              that holds its nibble rows (-1: the run needs none)
 //   side ring  per loader warp NML slots of [32 tokens x D/2 mid bytes][32 tokens x D/2 low bytes]
-//   barriers   full / empty per stage, empty per side-ring slot
+//   s chunks   per loader warp two buffers of 32 stages x 32 probabilities (that warp's tokens), copied a whole
+//              chunk ahead so that no global-load latency sits on the staging loop
+//   barriers   full / empty per stage, empty per side-ring slot, landed per probability buffer
 template <int D, int NS, int NML>
 struct VPlan {
     static constexpr int TOK = vc::TOK;
     static constexpr int HD = D / 2;
     static constexpr int F_BYTES = TOK * D;
     static constexpr int META_OFF = NS * F_BYTES;
-    static constexpr int META_BYTES = TOK * 4 + 16;
+    static constexpr int META_BYTES = TOK * 4 + 32;   // + per run of 32 tokens: side slot, mid mask, low mask, pad
     static constexpr int ML_OFF = META_OFF + NS * META_BYTES;
     static constexpr int ML_BYTES = 32 * HD * 2;
-    static constexpr int BAR_OFF = ML_OFF + 2 * NML * ML_BYTES;
-    static constexpr int BYTES = BAR_OFF + (2 * NS + 2 * NML) * 8;
+    static constexpr int SCH = 32;                               // stages per probability chunk
+    static constexpr int S_OFF = ML_OFF + 2 * NML * ML_BYTES;    // per loader warp: 2 chunks x 32 stages x 32 fp16
+    static constexpr int S_BYTES = 2 * SCH * 32 * 2;
+    static constexpr int BAR_OFF = S_OFF + 2 * S_BYTES;
+    static constexpr int BYTES = BAR_OFF + (2 * NS + 2 * NML + 4) * 8;
 };
 
 template <int NS, int NML, int D>
@@ -101,6 +107,7 @@ __global__ void __launch_bounds__(D) v_compute_kernel(const VParams p) {
     const int nst = (n + TOK - 1) / TOK;
     const uint32_t base = smem_u32(smem);
     const uint32_t bar_full = base + P::BAR_OFF, bar_empty = bar_full + NS * 8, bar_ml = bar_empty + NS * 8;
+    const uint32_t bar_s = bar_ml + 2 * NML * 8;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -108,6 +115,7 @@ __global__ void __launch_bounds__(D) v_compute_kernel(const VParams p) {
             mbar_init(bar_empty + s * 8, NC);
         }
         for (int s = 0; s < 2 * NML; ++s) mbar_init(bar_ml + s * 8, NC);
+        for (int s = 0; s < 4; ++s) mbar_init(bar_s + s * 8, 32);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
@@ -118,62 +126,83 @@ __global__ void __launch_bounds__(D) v_compute_kernel(const VParams p) {
         int slot = 0;
         uint32_t phase = 0;
         bool alive = true;
+        // One run of 32 tokens: K_[u] holds k~ = [0x80, f_even, 0x80, f_odd] of token u; tokens whose bit is set in
+        // the run's mid mask take their low bytes from the side ring instead (warp-uniform, rare branch).
+#define AKV_V_RUN(K_, S_, MM_, LM_, MLA_)                                                              \
+        _Pragma("unroll") for (int v_ = 0; v_ < 8; ++v_) {                                             \
+            _Pragma("unroll") for (int w_ = 0; w_ < 4; ++w_) {                                         \
+                const int u_ = 4 * v_ + w_;                                                            \
+                uint32_t k_ = K_[u_];                                                                  \
+                if ((MM_ >> u_) & 1u) {                                                                \
+                    const uint32_t mb_ = lds8(MLA_ + u_ * HD);                                         \
+                    const uint32_t lb_ = ((LM_ >> u_) & 1u) ? lds8(MLA_ + 32 * HD + u_ * HD) : 0x88u;  \
+                    const uint32_t lo_e_ = (mb_ & 0xF0u) | (lb_ >> 4);                                 \
+                    const uint32_t lo_o_ = ((mb_ << 4) & 0xF0u) | (lb_ & 0x0Fu);                       \
+                    k_ = (k_ & 0xFF00FF00u) | lo_e_ | (lo_o_ << 16);                                   \
+                }                                                                                      \
+                const uint32_t s_ = (w_ == 0) ? S_[v_].x : (w_ == 1) ? S_[v_].y : (w_ == 2) ? S_[v_].z : S_[v_].w; \
+                acc = hfma2_bits(k_, s_, acc);                                                         \
+            }                                                                                          \
+        }
+        // The common run: no token reads a nibble plane, so the chain is 32 back-to-back FMAs.
+#define AKV_V_RUN_LEAN(K_, S_)                                   \
+        _Pragma("unroll") for (int v_ = 0; v_ < 8; ++v_) {       \
+            acc = hfma2_bits(K_[4 * v_], S_[v_].x, acc);         \
+            acc = hfma2_bits(K_[4 * v_ + 1], S_[v_].y, acc);     \
+            acc = hfma2_bits(K_[4 * v_ + 2], S_[v_].z, acc);     \
+            acc = hfma2_bits(K_[4 * v_ + 3], S_[v_].w, acc);     \
+        }
         for (int i = 0; i < nst && alive; ++i) {
+            if (p.trace && bh == 0 && tid == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); p.trace[i * 4 + 0] = t; }
             alive = mbar_wait(bar_full + slot * 8, phase);
+            if (p.trace && bh == 0 && tid == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); p.trace[i * 4 + 1] = t; }
             const uint32_t fa = base + (uint32_t)slot * P::F_BYTES + tid * 2;            // + t * D
-            const uint32_t ma = base + P::META_OFF + (uint32_t)slot * P::META_BYTES;     // s2 words, then 2 slot ids
+            const uint32_t ma = base + P::META_OFF + (uint32_t)slot * P::META_BYTES;     // s2 words, then run records
             const int cnt = (n - i * TOK) < TOK ? (n - i * TOK) : TOK;
-            if (!(p.debug & 1)) {
+            const uint4 r0 = lds128(ma + TOK * 4), r1 = lds128(ma + TOK * 4 + 16);       // {slot, mid mask, low mask, -}
+            const uint32_t mla0 = base + P::ML_OFF + (uint32_t)(0 * NML + (int)r0.x) * P::ML_BYTES + tid;
+            const uint32_t mla1 = base + P::ML_OFF + (uint32_t)(1 * NML + (int)r1.x) * P::ML_BYTES + tid;
+            if (p.debug & 1) {
+            } else if (cnt == TOK) {
+                uint32_t k0[32], k1[32];
+                uint4 s0[8], s1[8];
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const int tb = hf * 32;
-                    const int ms = (int)lds32(ma + TOK * 4 + hf * 4);
-                    if (ms < 0) {
-                        // 32 tokens, high byte only: k~ = [0x80, f_even, 0x80, f_odd]
-                        uint32_t f[32];
-                        uint4 sv[8];
+                for (int u = 0; u < 32; ++u) k0[u] = lds16(fa + u * D);
 #pragma unroll
-                        for (int u = 0; u < 32; ++u) f[u] = lds16(fa + (tb + u) * D);
+                for (int v = 0; v < 8; ++v) s0[v] = lds128(ma + 4 * v * 4);
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) sv[v] = lds128(ma + (tb + 4 * v) * 4);
+                for (int u = 0; u < 32; ++u) k1[u] = lds16(fa + (32 + u) * D);     // second run's loads are in
 #pragma unroll
-                        for (int u = 0; u < 32; ++u) f[u] = __byte_perm(f[u], 0x80u, 0x1404);
+                for (int v = 0; v < 8; ++v) s1[v] = lds128(ma + (32 + 4 * v) * 4); // flight during the first chain
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            acc = hfma2_bits(f[4 * v], sv[v].x, acc);
-                            acc = hfma2_bits(f[4 * v + 1], sv[v].y, acc);
-                            acc = hfma2_bits(f[4 * v + 2], sv[v].z, acc);
-                            acc = hfma2_bits(f[4 * v + 3], sv[v].w, acc);
-                        }
-                    } else {
-                        const uint32_t mla = base + P::ML_OFF + (uint32_t)(hf * NML + ms) * P::ML_BYTES + tid;
-                        const int end = cnt < tb + 32 ? cnt : tb + 32;
-                        for (int t0 = tb; t0 < end; t0 += 8) {
-                            uint32_t f[8], mb[8], lb[8], s2[8];
+                for (int u = 0; u < 32; ++u) k0[u] = __byte_perm(k0[u], 0x80u, 0x1404);
+                if (r0.y == 0) { AKV_V_RUN_LEAN(k0, s0) } else { AKV_V_RUN(k0, s0, r0.y, r0.z, mla0) }
 #pragma unroll
-                            for (int u = 0; u < 8; ++u) {
-                                const int t = t0 + u;   // rows past the stage's tokens hold stale bytes; not used
-                                f[u] = lds16(fa + t * D);
-                                mb[u] = lds8(mla + (t - tb) * HD);
-                                lb[u] = lds8(mla + 32 * HD + (t - tb) * HD);
-                                s2[u] = lds32(ma + t * 4);
-                            }
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) {
-                                if (t0 + u < end) {
-                                    const uint32_t lo_e = (mb[u] & 0xF0u) | (lb[u] >> 4);            // even channel
-                                    const uint32_t lo_o = ((mb[u] << 4) & 0xF0u) | (lb[u] & 0x0Fu);  // odd channel
-                                    acc = hfma2_bits(__byte_perm(f[u], lo_e | (lo_o << 8), 0x1504), s2[u], acc);
-                                }
-                            }
-                        }
-                        mbar_arrive(bar_ml + (hf * NML + ms) * 8);   // the side-ring slot may be refilled
+                for (int u = 0; u < 32; ++u) k1[u] = __byte_perm(k1[u], 0x80u, 0x1404);
+                if (r1.y == 0) { AKV_V_RUN_LEAN(k1, s1) } else { AKV_V_RUN(k1, s1, r1.y, r1.z, mla1) }
+            } else {
+                // last, partial stage: token by token; rows past cnt hold stale bytes and must not be touched
+                for (int t = 0; t < cnt; ++t) {
+                    const uint4 r = (t < 32) ? r0 : r1;
+                    const uint32_t mla = (t < 32) ? mla0 : mla1;
+                    const int u = t & 31;
+                    uint32_t k = __byte_perm(lds16(fa + t * D), 0x80u, 0x1404);
+                    if ((r.y >> u) & 1u) {
+                        const uint32_t mb = lds8(mla + u * HD);
+                        const uint32_t lb = ((r.z >> u) & 1u) ? lds8(mla + 32 * HD + u * HD) : 0x88u;
+                        k = (k & 0xFF00FF00u) | ((mb & 0xF0u) | (lb >> 4)) | ((((mb << 4) & 0xF0u) | (lb & 0x0Fu)) << 16);
                     }
+                    acc = hfma2_bits(k, lds32(ma + t * 4), acc);
                 }
             }
+            if ((int)r0.x >= 0) mbar_arrive(bar_ml + (0 * NML + (int)r0.x) * 8);   // side-ring slots may be refilled
+            if ((int)r1.x >= 0) mbar_arrive(bar_ml + (1 * NML + (int)r1.x) * 8);
+            if (p.trace && bh == 0 && tid == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); p.trace[i * 4 + 2] = t; }
             mbar_arrive(bar_empty + slot * 8);
             if (++slot == NS) { slot = 0; phase ^= 1; }
         }
+#undef AKV_V_RUN
+#undef AKV_V_RUN_LEAN
         reinterpret_cast<uint32_t*>(p.o)[(size_t)bh * NC + tid] = acc;
         return;
     }
@@ -185,15 +214,24 @@ __global__ void __launch_bounds__(D) v_compute_kernel(const VParams p) {
     const uint8_t* L = p.last4 + (size_t)bh * p.max_seq_len * HD;
     const uint16_t* s_row = p.s + (size_t)bh * p.s_last_dim;
     const uint32_t A = ((uint32_t)p.amin[bh] << 10) & 0xFFFFu;
-    auto load_s = [&](int j) -> uint32_t {   // probability of this thread's token of stage j (0 beyond n)
-        const int t = j * TOK + pt;
-        return (t < n) ? (uint32_t)__ldg(s_row + t) : 0u;
+    // Probability chunk c (stages 32c .. 32c+31, this warp's 32 tokens of each) -> this warp's buffer c & 1.
+    // 4 x 16 bytes per stage; the barrier of the buffer completes when every lane's copies have landed.
+    const uint32_t sbuf = base + P::S_OFF + (uint32_t)pw * P::S_BYTES;
+    auto request_s = [&](int c) {
+        const uint32_t dst = sbuf + (uint32_t)(c & 1) * (P::SCH * 64);
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int op = it * 32 + lane;              // 128 pieces: stage (op >> 2), 8 tokens (op & 3)
+            const int t = (c * P::SCH + (op >> 2)) * TOK + pw * 32 + (op & 3) * 8;
+            if (t < n) cp_async16(dst + (op >> 2) * 64 + (op & 3) * 16, s_row + t);
+        }
+        mbar_arrive_on_copies(bar_s + (pw * 2 + (c & 1)) * 8);
     };
     int slot = 0, ml_used = 0;          // stage slot; side-ring slots this warp has handed out so far
     uint32_t phase = 0;
     bool alive = true;
 
-    auto stage = [&](int j, uint32_t sb) {
+    auto stage = [&](int j) {
         if (j >= NS) alive = alive && mbar_wait(bar_empty + slot * 8, phase ^ 1);   // stage j-NS has been consumed
         const uint32_t st = base + (uint32_t)slot * P::F_BYTES;
         const int t0 = j * TOK;
@@ -206,46 +244,49 @@ __global__ void __launch_bounds__(D) v_compute_kernel(const VParams p) {
                 if (off < fbytes) cp_async16(st + off, F + (size_t)t0 * D + off);
             }
         }
+        const int c = j / P::SCH, js = j - c * P::SCH;
+        if (js == 0) {   // entering chunk c: ask for the next one, make sure this one has landed
+            if ((c + 1) * P::SCH < nst) request_s(c + 1);
+            alive = alive && mbar_wait(bar_s + (pw * 2 + (c & 1)) * 8, (uint32_t)(c >> 1) & 1u);
+        }
+        const uint32_t sb = (pt < cnt) ? lds16(sbuf + (uint32_t)(c & 1) * (P::SCH * 64) + js * 64 + lane * 2) : 0u;
         // decision from the bit patterns (V_cache.cu:211,250-251): 16-bit wrap-around, signed compare
         const int diff = (int)(int16_t)(uint16_t)(A - sb);
         int code = p.reference ? 0 : (diff >= 0x0800 ? 2 : (diff >= 0x0400 ? 1 : 0));
         if (pt >= cnt) code = 2;
-        // this warp's 32 tokens are "lean" when all of them exist and none reads a nibble plane
-        const bool lean = __all_sync(0xFFFFFFFFu, code == 2) && (t0 + pw * 32 + 32 <= n);
+        // which of this warp's 32 tokens read the mid plane / the low plane
+        const uint32_t mmask = __ballot_sync(0xFFFFFFFFu, code < 2), lmask = __ballot_sync(0xFFFFFFFFu, code == 0);
         const uint32_t ma = base + P::META_OFF + (uint32_t)slot * P::META_BYTES;
         asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(ma + pt * 4), "r"(sb | (sb << 16)) : "memory");
         int ms = -1;
-        if (!lean) {
+        if (mmask) {
+            // their 64-byte rows go to a slot of this warp's side ring; rows of other tokens are not touched
             ms = ml_used % NML;
             if (ml_used >= NML) alive = alive && mbar_wait(bar_ml + (pw * NML + ms) * 8, ((ml_used / NML) & 1) ^ 1);
             ++ml_used;
-            // rows the rule reads are fetched; the others get the reference's substitute bytes (mid 0x88 / low 0x00
-            // when neither is read, low 0x88 when only mid is read), so the consumer has no per-token branch
             const size_t src = (size_t)(t0 + pt) * HD;
             const uint32_t dm = base + P::ML_OFF + (uint32_t)(pw * NML + ms) * P::ML_BYTES + lane * HD;
             const uint32_t dl = dm + 32 * HD;
+            if (code < 2) {
 #pragma unroll
-            for (int v = 0; v < ROW_OPS; ++v) {
-                if (code < 2) cp_async16(dm + v * 16, M + src + v * 16);
-                else st_shared_row16(dm + v * 16, 0x88888888u);
-                if (code == 0) cp_async16(dl + v * 16, L + src + v * 16);
-                else st_shared_row16(dl + v * 16, code == 1 ? 0x88888888u : 0u);
+                for (int v = 0; v < ROW_OPS; ++v) cp_async16(dm + v * 16, M + src + v * 16);
+            }
+            if (code == 0) {
+#pragma unroll
+                for (int v = 0; v < ROW_OPS; ++v) cp_async16(dl + v * 16, L + src + v * 16);
             }
         }
-        if (lane == 0) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(ma + TOK * 4 + pw * 4), "r"(ms) : "memory");
+        if (lane == 0)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(ma + TOK * 4 + pw * 16), "r"(ms), "r"(mmask),
+                         "r"(lmask), "r"(0) : "memory");
+        if (p.trace && bh == 0 && pt == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); p.trace[j * 4 + 3] = t; }
         mbar_arrive_on_copies(bar_full + slot * 8);   // fires when this thread's copies (all of them) have landed
         mbar_arrive(bar_full + slot * 8);             // publishes this thread's plain stores
         if (++slot == NS) { slot = 0; phase ^= 1; }
     };
 
-    uint32_t s0 = load_s(0), s1 = load_s(1), s2 = load_s(2), s3 = load_s(3);
-    for (int j0 = 0; j0 < nst && alive; j0 += 4) {
-        stage(j0, s0);
-        s0 = load_s(j0 + 4);
-        if (j0 + 1 < nst) { stage(j0 + 1, s1); s1 = load_s(j0 + 5); }
-        if (j0 + 2 < nst) { stage(j0 + 2, s2); s2 = load_s(j0 + 6); }
-        if (j0 + 3 < nst) { stage(j0 + 3, s3); s3 = load_s(j0 + 7); }
-    }
+    request_s(0);
+    for (int j = 0; j < nst && alive; ++j) stage(j);
     cp_async_commit();
     cp_async_wait<0>();   // this thread's copies must have landed before its shared memory goes away
 }
@@ -301,6 +342,7 @@ int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     p.o = reinterpret_cast<uint16_t*>(o);
     p.max_seq_len = max_seq_len; p.D = D; p.s_last_dim = s_last_dim; p.n = n; p.reference = reference;
     p.debug = tuning().debug;
+    p.trace = reinterpret_cast<unsigned long long*>(((unsigned long long)(unsigned)tuning().trace_hi << 32) | (unsigned)tuning().trace_lo);
     const int BH = bsz * H;
     const bool fast = D == 128 && aligned16(first8) && aligned16(mid4) && aligned16(last4) &&
                       (n == 0 || (aligned16(s) && s_last_dim % 8 == 0)) &&
