@@ -49,7 +49,7 @@ int launch_k_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, i
 int launch_k_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
                      const uint8_t*, uint8_t*, int, int, int, int, int, int, float, int, cudaStream_t);
 int launch_v_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*,
-                     int, int, int, int, int, int, int, cudaStream_t);
+                     int, int, int, int, int, int, int, int, cudaStream_t);
 int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int,
                    cudaStream_t);
 
@@ -78,13 +78,9 @@ int akv_set_tuning(const char* key, int value) {
     if (!strcmp(key, "k_kch") && (value == 8 || value == 16)) t.k_kch = value;
     else if (!strcmp(key, "k_stages") && value >= 3 && value <= 6) t.k_stages = value;
     else if (!strcmp(key, "k_prefetch") && value >= 0 && value <= 101) t.k_prefetch = value;
-    else if (!strcmp(key, "trace_lo")) t.trace_lo = value;
-    else if (!strcmp(key, "trace_hi")) t.trace_hi = value;
     else if (!strcmp(key, "timing") && (value == 0 || value == 1)) t.timing = value;
     else if (!strcmp(key, "debug") && value >= 0 && value <= 255) t.debug = value;
-    else if (!strcmp(key, "v_prefetch") && value >= 0 && value <= 64) t.v_prefetch = value;
     else if (!strcmp(key, "k_wpc") && value >= 0 && value <= 16) t.k_wpc = value;
-    else if (!strcmp(key, "v_stages") && (value == 4 || value == 6 || value == 8)) t.v_stages = value;
     else {
         set_error("set_tuning: unknown key or value out of range (%s = %d)", key, value);
         return AKV_ERR_SHAPE;
@@ -187,7 +183,7 @@ int akv_v_cache_compute(const void* f8, const void* m4, const void* l4, const vo
                 "v_cache_compute: tensor extent overflows");
     AKV_REQUIRE((reinterpret_cast<uintptr_t>(s) & 1u) == 0 && (reinterpret_cast<uintptr_t>(o_out) & 3u) == 0 &&
                 (reinterpret_cast<uintptr_t>(f8) & 1u) == 0, AKV_ERR_ALIGN, "v_cache_compute: misaligned pointer");
-    return launch_v_compute(CU8(f8), CU8(m4), CU8(l4), CU8(s), CU8(amin), U8(o_out), bsz, H, max_seq_len, D,
+    return launch_v_compute(CU8(f8), CU8(m4), CU8(l4), CU8(s), CU8(amin), U8(o_out), bsz, H, 1, max_seq_len, D,
                             s_last_dim, n, reference != 0, static_cast<cudaStream_t>(stream));
 }
 

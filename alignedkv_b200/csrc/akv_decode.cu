@@ -20,7 +20,7 @@ int launch_k_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, i
 int launch_k_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
                      const uint8_t*, uint8_t*, int, int, int, int, int, int, float, int, cudaStream_t);
 int launch_v_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*,
-                     int, int, int, int, int, int, int, cudaStream_t);
+                     int, int, int, int, int, int, int, int, cudaStream_t);
 int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int,
                    cudaStream_t);
 
@@ -327,7 +327,7 @@ int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_firs
         if (ev) cudaEventRecord(ev[2], st);
         rc = launch_v_compute(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
                               static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
-                              reinterpret_cast<uint8_t*>(rest ? (void*)sc.o_main : out), B, H, max_seq_len, D, R, qn,
+                              reinterpret_cast<uint8_t*>(rest ? (void*)sc.o_main : out), B, H, 1, max_seq_len, D, R, qn,
                               reference != 0, st);
         if (ev) cudaEventRecord(ev[3], st);
         if (rc != AKV_OK) return rc;

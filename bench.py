@@ -26,7 +26,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # Llama-2-7B-shaped decode attention, one layer (the configuration the metric is quoted on)
-WORKLOAD = dict(name="llama2-7b-layer-decode", batch=8, heads=32, head_dim=128, cache_len=4096)
+WORKLOADS = {
+    "llama2-7b-layer-decode": dict(batch=8, heads=32, head_dim=128, cache_len=4096),
+    # a quarter of the batch: same kernels and per-(batch, head) work, planes still larger than L2; sized for profiler
+    # captures that replay every launch many times
+    "llama2-7b-layer-decode-b2": dict(batch=2, heads=32, head_dim=128, cache_len=4096),
+}
+WORKLOAD = dict(name="llama2-7b-layer-decode", **WORKLOADS["llama2-7b-layer-decode"])
 OUTLIER_CHANNELS = (3, 34, 65, 96)
 METRIC = "decode_attention_tokens_per_s"
 UNIT = "tokens/s"
@@ -40,7 +46,11 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
-    return ap.parse_args()
+    ap.add_argument("--workload", default="llama2-7b-layer-decode", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    WORKLOAD.clear()
+    WORKLOAD.update(name=args.workload, **WORKLOADS[args.workload])
+    return args
 
 
 # ---------------------------------------------------------------------------------------------- CPU baseline
