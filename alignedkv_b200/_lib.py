@@ -25,6 +25,12 @@ SIGNATURES = {
     "akv_decode_step": (_I, [_P] * 15 + [ctypes.c_longlong] + [_I] * 7 + [_P]),
     "akv_decode_step_noalloc": (_I, [_P] * 14 + [_I] * 7 + [_P]),
     "akv_decode_scratch_bytes": (ctypes.c_longlong, [_I] * 4),
+    "akv_k_cache_compute_gqa": (_I, [_P] * 7 + [_I] * 8 + [_F, _I, _P]),
+    "akv_v_cache_compute_gqa": (_I, [_P] * 7 + [ctypes.c_longlong] + [_I] * 8 + [_P]),
+    "akv_v_cache_compute_scratch_bytes": (ctypes.c_longlong, [_I] * 4),
+    "akv_decode_step_ex": (_I, [_P] * 16 + [ctypes.c_longlong] + [_I] * 8 + [_P]),
+    "akv_decode_scratch_bytes_ex": (ctypes.c_longlong, [_I] * 6),
+    "akv_lse_merge": (_I, [_P] * 2 + [_I] * 3 + [_P]),
     "akv_timing_reset": (_I, []),
     "akv_timing_read": (_I, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
 }

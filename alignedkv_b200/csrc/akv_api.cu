@@ -47,10 +47,13 @@ int launch_v_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, i
 int launch_k_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, int, int, int, int, int,
                   cudaStream_t);
 int launch_k_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
-                     const uint8_t*, uint8_t*, int, int, int, int, int, int, float, int, cudaStream_t);
+                     const uint8_t*, uint8_t*, int, int, int, int, int, int, int, float, int, cudaStream_t);
+int launch_v_split(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, float*,
+                   float*, int, int, int, int, int, int, int, int, cudaStream_t);
+long long v_split_scratch_bytes(int, int, int, int);
 int launch_v_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*,
                      int, int, int, int, int, int, int, int, cudaStream_t);
-int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int,
+int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int, int,
                    cudaStream_t);
 
 static bool fits_i64(long long a, long long b, long long c = 1, long long d = 1, long long e = 1) {
@@ -113,22 +116,30 @@ int akv_k_cache_save(void* f8, void* m4, void* l4, const void* k_new, int bsz, i
 int akv_k_cache_compute(const void* f8, const void* m4, const void* l4, const void* kq, const void* kqmax,
                         const void* q, void* s_out, int bsz, int H, int n_blocks, int n_max_blocks, int D,
                         int d_block, int seqlen, float sqrt_dim, int reference, void* stream) {
+    return akv_k_cache_compute_gqa(f8, m4, l4, kq, kqmax, q, s_out, bsz, H, 1, n_blocks, n_max_blocks, D, d_block,
+                                   seqlen, sqrt_dim, reference, stream);
+}
+
+int akv_k_cache_compute_gqa(const void* f8, const void* m4, const void* l4, const void* kq, const void* kqmax,
+                            const void* q, void* s_out, int bsz, int H, int group, int n_blocks, int n_max_blocks,
+                            int D, int d_block, int seqlen, float sqrt_dim, int reference, void* stream) {
     (void)seqlen;  // carried for signature parity; the reference ignores it too
     g_err[0] = 0;
-    AKV_REQUIRE(bsz > 0 && H > 0 && D > 0 && n_max_blocks > 0 && n_blocks >= 0, AKV_ERR_SHAPE,
-                "k_cache_compute: bad extent (bsz %d, heads %d, d_head %d, n_max_blocks %d, n_blocks %d)", bsz, H, D,
-                n_max_blocks, n_blocks);
+    AKV_REQUIRE(bsz > 0 && H > 0 && group > 0 && D > 0 && n_max_blocks > 0 && n_blocks >= 0, AKV_ERR_SHAPE,
+                "k_cache_compute: bad extent (bsz %d, heads %d x %d, d_head %d, n_max_blocks %d, n_blocks %d)", bsz, H,
+                group, D, n_max_blocks, n_blocks);
     AKV_REQUIRE(d_block >= 2 && d_block % 2 == 0, AKV_ERR_SHAPE, "k_cache_compute: d_block %d must be even",
                 d_block);
     AKV_REQUIRE(n_blocks <= n_max_blocks, AKV_ERR_SHAPE, "k_cache_compute: n_blocks %d > n_max_blocks %d", n_blocks,
                 n_max_blocks);
     if (n_blocks == 0) return AKV_OK;  // the reference returns its uninitialised buffer untouched
     AKV_REQUIRE(f8 && m4 && l4 && kq && kqmax && q && s_out, AKV_ERR_NULL, "k_cache_compute: null pointer");
-    AKV_REQUIRE(fits_i64(bsz, H, n_max_blocks, D, d_block) && fits_i64(bsz, H, (long long)n_blocks + 1, d_block, 2),
+    AKV_REQUIRE(fits_i64(bsz, H, n_max_blocks, D, d_block) &&
+                fits_i64(bsz, (long long)H * group, (long long)n_blocks + 1, d_block, 2),
                 AKV_ERR_OVERFLOW, "k_cache_compute: tensor extent overflows");
     AKV_REQUIRE((reinterpret_cast<uintptr_t>(q) & 1u) == 0 && (reinterpret_cast<uintptr_t>(s_out) & 1u) == 0,
                 AKV_ERR_ALIGN, "k_cache_compute: q and s must be 2-byte aligned");
-    return launch_k_compute(CU8(f8), CU8(m4), CU8(l4), CU8(kq), CU8(kqmax), CU8(q), U8(s_out), bsz, H, n_blocks,
+    return launch_k_compute(CU8(f8), CU8(m4), CU8(l4), CU8(kq), CU8(kqmax), CU8(q), U8(s_out), bsz, H, group, n_blocks,
                             n_max_blocks, D, d_block, sqrt_dim, reference != 0, static_cast<cudaStream_t>(stream));
 }
 
@@ -164,27 +175,48 @@ int akv_v_cache_test_compute(const void* f8, const void* m4, const void* l4, con
     AKV_REQUIRE((reinterpret_cast<uintptr_t>(s_idx) & 3u) == 0 && (reinterpret_cast<uintptr_t>(test_o) & 3u) == 0 &&
                 (reinterpret_cast<uintptr_t>(s_val) & 1u) == 0 && (reinterpret_cast<uintptr_t>(f8) & 1u) == 0,
                 AKV_ERR_ALIGN, "v_cache_test_compute: misaligned pointer");
-    return launch_v_probe(CU8(f8), CU8(s_val), CU8(s_idx), U8(test_o), bsz, H, max_seq_len, D, top_max_k,
+    return launch_v_probe(CU8(f8), CU8(s_val), CU8(s_idx), U8(test_o), bsz, H, 1, max_seq_len, D, top_max_k,
                           static_cast<cudaStream_t>(stream));
 }
 
 int akv_v_cache_compute(const void* f8, const void* m4, const void* l4, const void* s, const void* amin,
                         void* o_out, int bsz, int H, int max_seq_len, int D, int s_last_dim, int n, int reference,
                         void* stream) {
+    return akv_v_cache_compute_gqa(f8, m4, l4, s, amin, o_out, nullptr, 0, bsz, H, 1, max_seq_len, D, s_last_dim, n,
+                                   reference ? AKV_STEP_REFERENCE : 0, stream);
+}
+
+long long akv_v_cache_compute_scratch_bytes(int bsz, int n_kv_heads, int group, int n) {
+    if (bsz <= 0 || n_kv_heads <= 0 || group <= 0 || n < 0) return -1;
+    return v_split_scratch_bytes(bsz, n_kv_heads, group, n);
+}
+
+int akv_v_cache_compute_gqa(const void* f8, const void* m4, const void* l4, const void* s, const void* amin,
+                            void* o_out, void* scratch, long long scratch_bytes, int bsz, int H, int group,
+                            int max_seq_len, int D, int s_last_dim, int n, int flags, void* stream) {
     g_err[0] = 0;
+    const bool reference = (flags & AKV_STEP_REFERENCE) != 0, order_free = (flags & AKV_STEP_ORDER_FREE) != 0;
     AKV_REQUIRE(f8 && m4 && l4 && amin && o_out && (s || n == 0), AKV_ERR_NULL, "v_cache_compute: null pointer");
-    AKV_REQUIRE(bsz > 0 && H > 0 && D > 0 && D % 2 == 0 && max_seq_len > 0 && n >= 0 && s_last_dim >= 0,
-                AKV_ERR_SHAPE, "v_cache_compute: bad extent (bsz %d, heads %d, head_dim %d, max_seq_len %d, "
-                "s_last_dim %d, tokens %d)", bsz, H, D, max_seq_len, s_last_dim, n);
+    AKV_REQUIRE(bsz > 0 && H > 0 && group > 0 && D > 0 && D % 2 == 0 && max_seq_len > 0 && n >= 0 && s_last_dim >= 0,
+                AKV_ERR_SHAPE, "v_cache_compute: bad extent (bsz %d, heads %d x %d, head_dim %d, max_seq_len %d, "
+                "s_last_dim %d, tokens %d)", bsz, H, group, D, max_seq_len, s_last_dim, n);
     AKV_REQUIRE(n <= max_seq_len, AKV_ERR_SHAPE, "v_cache_compute: %d tokens exceed max_seq_len %d", n, max_seq_len);
-    AKV_REQUIRE(n <= s_last_dim || bsz * H == 1, AKV_ERR_SHAPE,
+    AKV_REQUIRE(n <= s_last_dim || bsz * H * group == 1, AKV_ERR_SHAPE,
                 "v_cache_compute: %d tokens exceed the score row stride %d", n, s_last_dim);
-    AKV_REQUIRE(fits_i64(bsz, H, max_seq_len, D) && fits_i64(bsz, H, s_last_dim, 2), AKV_ERR_OVERFLOW,
-                "v_cache_compute: tensor extent overflows");
+    AKV_REQUIRE(fits_i64(bsz, H, max_seq_len, D) && fits_i64(bsz, (long long)H * group, s_last_dim, 2),
+                AKV_ERR_OVERFLOW, "v_cache_compute: tensor extent overflows");
     AKV_REQUIRE((reinterpret_cast<uintptr_t>(s) & 1u) == 0 && (reinterpret_cast<uintptr_t>(o_out) & 3u) == 0 &&
                 (reinterpret_cast<uintptr_t>(f8) & 1u) == 0, AKV_ERR_ALIGN, "v_cache_compute: misaligned pointer");
-    return launch_v_compute(CU8(f8), CU8(m4), CU8(l4), CU8(s), CU8(amin), U8(o_out), bsz, H, 1, max_seq_len, D,
-                            s_last_dim, n, reference != 0, static_cast<cudaStream_t>(stream));
+    if (order_free) {
+        AKV_REQUIRE(scratch && scratch_bytes >= v_split_scratch_bytes(bsz, H, group, n), AKV_ERR_SHAPE,
+                    "v_cache_compute (order-free): workspace of %lld bytes is too small", scratch_bytes);
+        AKV_REQUIRE(n <= s_last_dim, AKV_ERR_SHAPE, "v_cache_compute (order-free): %d tokens exceed the row stride", n);
+        return launch_v_split(CU8(f8), CU8(m4), CU8(l4), CU8(s), CU8(amin), U8(o_out), nullptr,
+                              static_cast<float*>(scratch), bsz, H, group, max_seq_len, D, s_last_dim, n, reference,
+                              static_cast<cudaStream_t>(stream));
+    }
+    return launch_v_compute(CU8(f8), CU8(m4), CU8(l4), CU8(s), CU8(amin), U8(o_out), bsz, H, group, max_seq_len, D,
+                            s_last_dim, n, reference, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

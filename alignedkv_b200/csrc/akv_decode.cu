@@ -18,96 +18,122 @@ int launch_v_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, i
 int launch_k_save(uint8_t*, uint8_t*, uint8_t*, const uint8_t*, int, int, int, int, int, int, int, int,
                   cudaStream_t);
 int launch_k_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
-                     const uint8_t*, uint8_t*, int, int, int, int, int, int, float, int, cudaStream_t);
+                     const uint8_t*, uint8_t*, int, int, int, int, int, int, int, float, int, cudaStream_t);
 int launch_v_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*,
                      int, int, int, int, int, int, int, int, cudaStream_t);
-int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int,
+int launch_v_split(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, float*,
+                   float*, int, int, int, int, int, int, int, int, cudaStream_t);
+long long v_split_scratch_bytes(int, int, int, int);
+int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int, int,
                    cudaStream_t);
+int launch_lse_merge(const float*, uint8_t*, int, int, int, cudaStream_t);
 
 constexpr int TOPK = 32;     // residue classes of the magnitude probe (extension/v_cache_file.py:16)
 constexpr int BLK = 64;      // tokens per K block (extension/k_cache_file.py:5-6)
 
+// Workspace of one decode step.  H = KV heads, Hq = query heads.
 struct Scratch {
-    uint16_t* s;         // [B,H,R] scores, then probabilities (fp16), R = (nb+1)*64
-    uint8_t* kq;         // [B,H,D]
-    uint8_t* kqmax;      // [B*H]
-    uint16_t* pval;      // [B,H,32]
-    int32_t* pidx;       // [B,H,32]
-    uint16_t* test_o;    // [B,H,D]
-    uint8_t* amin;       // [B*H]
-    uint16_t* o_main;    // [B,H,D]
+    uint16_t* s;         // [B,Hq,R] scores, then probabilities (fp16), R = (nb+1)*64
+    uint8_t* kq;         // [B,Hq,D]
+    uint8_t* kqmax;      // [B*Hq]
+    uint16_t* pval;      // [B,Hq,32]
+    int32_t* pidx;       // [B,Hq,32]
+    uint16_t* test_o;    // [B,Hq,D]
+    uint8_t* amin;       // [B*Hq]
+    uint16_t* o_main;    // [B,Hq,D] fp16 result of the exact P.V kernel over the quantized tokens
+    float* stats;        // [B*Hq,2] maximum score and sum of exponentials of the softmax
+    float* o_main32;     // [B,Hq,D] fp32 result of the order-free P.V kernel
+    float* partial;      // chunk partials of the order-free P.V kernel
 };
 
 static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
-static size_t carve(Scratch* sc, uint8_t* base, int B, int H, int D, int max_seq_len) {
+static size_t carve(Scratch* sc, uint8_t* base, int B, int H, int G, int D, int max_seq_len, bool order_free) {
     const size_t R = ((size_t)(max_seq_len + BLK - 1) / BLK + 1) * BLK;
+    const size_t Q = (size_t)B * H * G;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align_up(bytes); return base ? base + o : nullptr; };
     uint8_t* p;
-    p = take((size_t)B * H * R * 2);       if (sc) sc->s = reinterpret_cast<uint16_t*>(p);
-    p = take((size_t)B * H * D);           if (sc) sc->kq = p;
-    p = take((size_t)B * H);               if (sc) sc->kqmax = p;
-    p = take((size_t)B * H * TOPK * 2);    if (sc) sc->pval = reinterpret_cast<uint16_t*>(p);
-    p = take((size_t)B * H * TOPK * 4);    if (sc) sc->pidx = reinterpret_cast<int32_t*>(p);
-    p = take((size_t)B * H * D * 2);       if (sc) sc->test_o = reinterpret_cast<uint16_t*>(p);
-    p = take((size_t)B * H);               if (sc) sc->amin = p;
-    p = take((size_t)B * H * D * 2);       if (sc) sc->o_main = reinterpret_cast<uint16_t*>(p);
+    p = take(Q * R * 2);        if (sc) sc->s = reinterpret_cast<uint16_t*>(p);
+    p = take(Q * D);            if (sc) sc->kq = p;
+    p = take(Q);                if (sc) sc->kqmax = p;
+    p = take(Q * TOPK * 2);     if (sc) sc->pval = reinterpret_cast<uint16_t*>(p);
+    p = take(Q * TOPK * 4);     if (sc) sc->pidx = reinterpret_cast<int32_t*>(p);
+    p = take(Q * D * 2);        if (sc) sc->test_o = reinterpret_cast<uint16_t*>(p);
+    p = take(Q);                if (sc) sc->amin = p;
+    p = take(Q * D * 2);        if (sc) sc->o_main = reinterpret_cast<uint16_t*>(p);
+    p = take(Q * 2 * 4);        if (sc) sc->stats = reinterpret_cast<float*>(p);
+    if (order_free) {
+        p = take(Q * D * 4);    if (sc) sc->o_main32 = reinterpret_cast<float*>(p);
+        p = take((size_t)v_split_scratch_bytes(B, H, G, max_seq_len));
+        if (sc) sc->partial = reinterpret_cast<float*>(p);
+    } else if (sc) {
+        sc->o_main32 = nullptr;
+        sc->partial = nullptr;
+    }
     return off;
 }
 
 // ------------------------------------------------------------------ append
-// grid B*H, block D/2.  Thread c handles channels 2c, 2c+1.
+// grid B*H (KV heads), block D/2.  Thread c handles channels 2c, 2c+1.  With append == 0 nothing is stored (the
+// token belongs to another shard of the sequence) and only the alignment inputs of the G query heads are built.
 __global__ void __launch_bounds__(512)
 append_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, uint16_t* __restrict__ k_exp,
               uint16_t* __restrict__ v_exp, const uint32_t* __restrict__ q, const uint32_t* __restrict__ k_new,
-              const uint32_t* __restrict__ v_new, uint16_t* __restrict__ kq, uint8_t* __restrict__ kqmax, int H, int D,
-              int rest_len) {
+              const uint32_t* __restrict__ v_new, uint16_t* __restrict__ kq, uint8_t* __restrict__ kqmax, int H, int G,
+              int D, int rest_len, int append) {
     __shared__ uint32_t red[16];
     const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
     const int c = threadIdx.x, hd = D >> 1;
     const size_t row = (size_t)bh * hd + c;                                  // [B,1,H,D] in words
-    const size_t rrow = (((size_t)b * BLK + rest_len) * H + h) * hd + c;     // [B,64,H,D] in words
-    const uint32_t kw = k_new[row], vw = v_new[row], qw = q[row];
-    restk[rrow] = kw;
-    restv[rrow] = vw;
     auto exps = [](uint32_t w) { return ((w >> 10) & 0x1Fu) | (((w >> 26) & 0x1Fu) << 8); };   // two exponent bytes
-    // running per-channel maxima of the exponent fields (k_cache_file.py:98-99, v_cache_file.py:98-99)
-    const uint32_t ke2 = __vmaxu4(k_exp[row], exps(kw)) & 0xFFFFu, ve2 = __vmaxu4(v_exp[row], exps(vw)) & 0xFFFFu;
-    k_exp[row] = (uint16_t)ke2;
-    v_exp[row] = (uint16_t)ve2;
+    uint32_t ke2 = k_exp[row];
+    if (append) {
+        const size_t rrow = (((size_t)b * BLK + rest_len) * H + h) * hd + c;     // [B,64,H,D] in words
+        const uint32_t kw = k_new[row], vw = v_new[row];
+        restk[rrow] = kw;
+        restv[rrow] = vw;
+        // running per-channel maxima of the exponent fields (k_cache_file.py:98-99, v_cache_file.py:98-99)
+        ke2 = __vmaxu4(ke2, exps(kw)) & 0xFFFFu;
+        k_exp[row] = (uint16_t)ke2;
+        v_exp[row] = (uint16_t)(__vmaxu4(v_exp[row], exps(vw)) & 0xFFFFu);
+    }
     // exponent upper bound of every product q_d * k_{t,d} and its maximum over channels (k_cache_file.py:136-138)
-    const uint32_t kq2 = __vadd4(exps(qw), ke2) & 0xFFFFu;
-    kq[row] = (uint16_t)kq2;
-    uint32_t m = max(kq2 & 0xFFu, kq2 >> 8);
+    for (int g = 0; g < G; ++g) {
+        const size_t qrow = ((size_t)bh * G + g) * hd + c;
+        const uint32_t kq2 = __vadd4(exps(q[qrow]), ke2) & 0xFFFFu;
+        kq[qrow] = (uint16_t)kq2;
+        uint32_t m = max(kq2 & 0xFFu, kq2 >> 8);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if ((c & 31) == 0) red[c >> 5] = m;
-    __syncthreads();
-    if (c == 0) {
-        for (int w = 1; w < (hd + 31) / 32; ++w) m = max(m, red[w]);
-        kqmax[bh] = (uint8_t)m;
+        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        __syncthreads();
+        if ((c & 31) == 0) red[c >> 5] = m;
+        __syncthreads();
+        if (c == 0) {
+            for (int w = 1; w < (hd + 31) / 32; ++w) m = max(m, red[w]);
+            kqmax[(size_t)bh * G + g] = (uint8_t)m;
+        }
     }
 }
 
 // ------------------------------------------------------------------ softmax (+ residual scores, class maxima)
-// grid B*H, block 256.  Row = [0, qn) aligned scores | [qn, qn+rest) residual scores | -inf up to R.
+// grid B*Hq, block 256.  Row = [0, qn) aligned scores | [qn, qn+rest) residual scores | -inf up to R.
 __global__ void __launch_bounds__(256)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
-               uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, int H, int D, int R, int qn, int rest,
-               float sqrt_d) {
+               uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats, int H, int G, int D,
+               int R, int qn, int rest, float sqrt_d) {
     __shared__ float redf[8];
     __shared__ uint32_t cand_v[256];
     __shared__ int32_t cand_i[256];
-    const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
+    const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint16_t* row = s + (size_t)bh * R;
+    uint16_t* row = s + (size_t)bhq * R;
     const int len = qn + rest;
     // residual tokens: fp32 dot product rounded to fp16, then divided by sqrt(D) and rounded again, which is
     // what `matmul(q, restk^T) / sqrt(D)` on fp16 tensors produces (k_cache_file.py:156-157)
     for (int r = warp; r < rest; r += 8) {
         const __half* kr = restk + (((size_t)b * BLK + r) * H + h) * D;
-        const __half* qr = q + (size_t)bh * D;
+        const __half* qr = q + (size_t)bhq * D;
         float acc = 0.f;
         for (int d = lane; d < D; d += 32) acc += __half2float(qr[d]) * __half2float(kr[d]);
 #pragma unroll
@@ -136,6 +162,10 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     sum = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) sum += redf[w];
+    if (tid == 0) {
+        stats[(size_t)bhq * 2] = m;
+        stats[(size_t)bhq * 2 + 1] = sum;
+    }
     // pass 3: probabilities, and this thread's residue class (tid % 32): largest probability over the quantized
     // tokens with its first position (torch.max over the group axis keeps the first maximum; v_cache_file.py:128-130)
     uint32_t best = 0;
@@ -160,25 +190,27 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
             const int32_t i = cand_i[tid + 32 * w];
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
         }
-        pval[(size_t)bh * TOPK + tid] = (uint16_t)bv;
-        pidx[(size_t)bh * TOPK + tid] = bi;
+        pval[(size_t)bhq * TOPK + tid] = (uint16_t)bv;
+        pidx[(size_t)bhq * TOPK + tid] = bi;
     }
 }
 
-// ------------------------------------------------------------------ threshold byte per (batch, head)
-// amin[i] = min_d ((exp(test_o[bb, hp, d]) & 0x1E) + 15 - v_exp[bb, he, d]) mod 256 with i = b*H + h read flat from
-// the reference's [B,H,H,1] tensor: bb = i / (H*H), hp = (i / H) % H, he = i % H (v_cache_file.py:142,156-160).
+// ------------------------------------------------------------------ threshold byte per (batch, query head)
+// amin[i] = min_d ((exp(test_o[bb, hp, d]) & 0x1E) + 15 - v_exp[bb, he, d]) mod 256 with i = b*Hq + h read flat from
+// the reference's [B,Hq,Hq,1] tensor: bb = i / (Hq*Hq), hp = (i / Hq) % Hq, he = i % Hq (v_cache_file.py:142,156-160).
+// The exponent maxima are stored per KV head; query head he belongs to KV head he / G (for G > 1 this is the
+// reference's rule applied to the cache with its KV heads repeated G times).
 __global__ void __launch_bounds__(128)
 amin_kernel(const uint16_t* __restrict__ test_o, const uint8_t* __restrict__ v_exp, uint8_t* __restrict__ amin,
-            int BH, int H, int D) {
+            int BHq, int H, int G, int D) {
     const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (i >= BH) return;
-    const int lane = threadIdx.x & 31;
-    const int bb = i / (H * H), hp = (i / H) % H, he = i % H;
+    if (i >= BHq) return;
+    const int lane = threadIdx.x & 31, Hq = H * G;
+    const int bb = i / (Hq * Hq), hp = (i / Hq) % Hq, he = i % Hq;
     uint32_t m = 255;
     for (int d = lane; d < D; d += 32) {
-        const uint32_t e = (test_o[((size_t)bb * H + hp) * D + d] >> 10) & 0x1Eu;
-        const uint32_t a = (e + 15u - v_exp[((size_t)bb * H + he) * D + d]) & 0xFFu;
+        const uint32_t e = (test_o[((size_t)bb * Hq + hp) * D + d] >> 10) & 0x1Eu;
+        const uint32_t a = (e + 15u - v_exp[((size_t)bb * H + he / G) * D + d]) & 0xFFu;
         m = min(m, a);
     }
 #pragma unroll
@@ -186,19 +218,31 @@ amin_kernel(const uint16_t* __restrict__ test_o, const uint8_t* __restrict__ v_e
     if (lane == 0) amin[i] = (uint8_t)m;
 }
 
-// ------------------------------------------------------------------ tail: residual tokens of P.V
-// out = half(o_main + half(sum_r p[qn+r] * restv[r])) (v_cache_file.py:189); grid B*H, block D/2... one thread/channel
+// ------------------------------------------------------------------ tail: residual tokens of P.V, final outputs
+// out = half(o_main + half(sum_r p[qn+r] * restv[r])) (v_cache_file.py:189); grid B*Hq.  With an fp32 main result
+// (order-free P.V) the residual sum is added in fp32 and rounded once.  packed (optional): one row
+// (max score, sum of exponentials, output[0..D-1]) in fp32 per (batch, query head), the record ranks exchange when
+// the sequence is sharded.
 __global__ void __launch_bounds__(256)
-tail_kernel(const uint16_t* __restrict__ o_main, const uint16_t* __restrict__ p, const __half* __restrict__ restv,
-            __half* __restrict__ out, int H, int D, int R, int qn, int rest) {
-    const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
+tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_main32, const uint16_t* __restrict__ p,
+            const __half* __restrict__ restv, __half* __restrict__ out, const float* __restrict__ stats,
+            float* __restrict__ packed, int H, int G, int D, int R, int qn, int rest) {
+    const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f;
         for (int r = 0; r < rest; ++r)
-            acc += __half2float(__ushort_as_half(p[(size_t)bh * R + qn + r])) *
+            acc += __half2float(__ushort_as_half(p[(size_t)bhq * R + qn + r])) *
                    __half2float(restv[(((size_t)b * BLK + r) * H + h) * D + d]);
-        const float base = o_main ? __half2float(__ushort_as_half(o_main[(size_t)bh * D + d])) : 0.f;
-        out[(size_t)bh * D + d] = __float2half_rn(base + __half2float(__float2half_rn(acc)));
+        float v;
+        if (o_main32) v = o_main32[(size_t)bhq * D + d] + acc;
+        else v = (o_main ? __half2float(__ushort_as_half(o_main[(size_t)bhq * D + d])) : 0.f) +
+                 __half2float(__float2half_rn(acc));
+        if (out) out[(size_t)bhq * D + d] = __float2half_rn(v);
+        if (packed) packed[(size_t)bhq * (D + 2) + 2 + d] = o_main32 ? v : __half2float(__float2half_rn(v));
+    }
+    if (packed && threadIdx.x == 0) {
+        packed[(size_t)bhq * (D + 2)] = stats[(size_t)bhq * 2];
+        packed[(size_t)bhq * (D + 2) + 1] = stats[(size_t)bhq * 2 + 1];
     }
 }
 
@@ -228,9 +272,14 @@ using namespace akv;
 
 extern "C" {
 
+long long akv_decode_scratch_bytes_ex(int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int flags) {
+    if (bsz <= 0 || n_kv_heads <= 0 || group <= 0 || head_dim <= 0 || max_seq_len <= 0) return -1;
+    return (long long)carve(nullptr, nullptr, bsz, n_kv_heads, group, head_dim, max_seq_len,
+                            (flags & AKV_STEP_ORDER_FREE) != 0);
+}
+
 long long akv_decode_scratch_bytes(int bsz, int n_heads, int head_dim, int max_seq_len) {
-    if (bsz <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq_len <= 0) return -1;
-    return (long long)carve(nullptr, nullptr, bsz, n_heads, head_dim, max_seq_len);
+    return akv_decode_scratch_bytes_ex(bsz, n_heads, 1, head_dim, max_seq_len, 0);
 }
 
 int akv_timing_reset(void) {
@@ -238,47 +287,64 @@ int akv_timing_reset(void) {
     return AKV_OK;
 }
 
-// Mean duration (microseconds) of the q.K^T and P.V launches recorded since the last reset; the caller must have
+// Median duration (microseconds) of the q.K^T and P.V launches recorded since the last reset (the median, so that a
+// step that was held up by something else on the machine does not move the figure); the caller must have
 // synchronised the stream.  Returns the number of recorded steps.
 int akv_timing_read(double* k_us, double* v_us) {
-    double ks = 0, vs = 0;
+    static float ks[Timing::CAP], vs[Timing::CAP];
     int n = 0;
     for (int i = 0; i < g_timing.used; ++i) {
         float a = 0, b = 0;
         if (cudaEventElapsedTime(&a, g_timing.ev[i][0], g_timing.ev[i][1]) != cudaSuccess) continue;
         if (cudaEventElapsedTime(&b, g_timing.ev[i][2], g_timing.ev[i][3]) != cudaSuccess) continue;
-        ks += a * 1e3;
-        vs += b * 1e3;
+        ks[n] = a * 1e3f;
+        vs[n] = b * 1e3f;
         ++n;
     }
-    if (k_us) *k_us = n ? ks / n : 0;
-    if (v_us) *v_us = n ? vs / n : 0;
+    auto median = [](float* x, int m) -> double {
+        if (m == 0) return 0.0;
+        for (int i = 1; i < m; ++i) {   // insertion sort: at most a few thousand entries, off the hot path
+            float v = x[i];
+            int j = i - 1;
+            for (; j >= 0 && x[j] > v; --j) x[j + 1] = x[j];
+            x[j + 1] = v;
+        }
+        return (m & 1) ? x[m / 2] : 0.5 * (x[m / 2 - 1] + x[m / 2]);
+    };
+    if (k_us) *k_us = median(ks, n);
+    if (v_us) *v_us = median(vs, n);
     return n;
 }
 
-int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
-                    void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
-                    const void* v_new, void* out, void* scratch, long long scratch_bytes, int bsz, int n_heads,
-                    int head_dim, int max_seq_len, int rest_len, int rest_start, int reference, void* stream) {
+int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                       void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                       const void* v_new, void* out, void* packed_out, void* scratch, long long scratch_bytes, int bsz,
+                       int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
+                       int flags, void* stream) {
     set_error("");
-    const int B = bsz, H = n_heads, D = head_dim;
+    const int B = bsz, H = n_kv_heads, G = group, D = head_dim;
+    const bool reference = (flags & AKV_STEP_REFERENCE) != 0, order_free = (flags & AKV_STEP_ORDER_FREE) != 0;
+    const bool append = (flags & AKV_STEP_NO_APPEND) == 0;
     AKV_REQUIRE(k_first_8 && k_mid_4 && k_last_4 && v_first_8 && v_mid_4 && v_last_4 && k_exp_max && v_exp_max &&
-                restk && restv && q && k_new && v_new && out && scratch, AKV_ERR_NULL, "decode_step: null pointer");
-    AKV_REQUIRE(B > 0 && H > 0 && D > 0 && D % 64 == 0 && D <= 1024 && max_seq_len > 0, AKV_ERR_SHAPE,
-                "decode_step: unsupported extent (bsz %d, heads %d, head_dim %d [multiple of 64], max_seq_len %d)", B, H,
-                D, max_seq_len);
+                restk && restv && q && (out || packed_out) && scratch && (!append || (k_new && v_new)), AKV_ERR_NULL,
+                "decode_step: null pointer");
+    AKV_REQUIRE(B > 0 && H > 0 && G > 0 && G <= 64 && D > 0 && D % 64 == 0 && D <= 1024 && max_seq_len > 0,
+                AKV_ERR_SHAPE, "decode_step: unsupported extent (bsz %d, kv heads %d, group %d, head_dim %d [multiple "
+                "of 64], max_seq_len %d)", B, H, G, D, max_seq_len);
     AKV_REQUIRE(rest_len >= 0 && rest_len < BLK && rest_start >= 0 && rest_start % BLK == 0 &&
-                rest_start + rest_len + 1 <= max_seq_len, AKV_ERR_SHAPE,
+                rest_start + rest_len + (append ? 1 : 0) <= max_seq_len, AKV_ERR_SHAPE,
                 "decode_step: residual state (start %d, length %d) does not fit max_seq_len %d", rest_start, rest_len,
                 max_seq_len);
-    AKV_REQUIRE(scratch_bytes >= akv_decode_scratch_bytes(B, H, D, max_seq_len), AKV_ERR_SHAPE,
+    AKV_REQUIRE(!order_free || D == 128, AKV_ERR_SHAPE, "decode_step: the order-free P.V kernel needs head_dim 128");
+    AKV_REQUIRE(scratch_bytes >= akv_decode_scratch_bytes_ex(B, H, G, D, max_seq_len, flags), AKV_ERR_SHAPE,
                 "decode_step: scratch of %lld bytes is too small", scratch_bytes);
-    AKV_REQUIRE(aligned16(scratch) && aligned16(q) && aligned16(k_new) && aligned16(v_new) && aligned16(out) &&
-                aligned16(restk) && aligned16(restv) && aligned16(k_exp_max) && aligned16(v_exp_max), AKV_ERR_ALIGN,
+    AKV_REQUIRE(aligned16(scratch) && aligned16(q) && (!append || (aligned16(k_new) && aligned16(v_new))) &&
+                (!out || aligned16(out)) && (!packed_out || aligned16(packed_out)) && aligned16(restk) &&
+                aligned16(restv) && aligned16(k_exp_max) && aligned16(v_exp_max), AKV_ERR_ALIGN,
                 "decode_step: pointers must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Scratch sc;
-    carve(&sc, static_cast<uint8_t*>(scratch), B, H, D, max_seq_len);
+    carve(&sc, static_cast<uint8_t*>(scratch), B, H, G, D, max_seq_len, order_free);
     const int nmb = (max_seq_len + BLK - 1) / BLK;
     int rc;
 
@@ -286,9 +352,9 @@ int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_firs
                                           static_cast<uint16_t*>(k_exp_max), static_cast<uint16_t*>(v_exp_max),
                                           static_cast<const uint32_t*>(q), static_cast<const uint32_t*>(k_new),
                                           static_cast<const uint32_t*>(v_new), reinterpret_cast<uint16_t*>(sc.kq),
-                                          sc.kqmax, H, D, rest_len);
+                                          sc.kqmax, H, G, D, rest_len, append ? 1 : 0);
     if ((rc = cuda_status(cudaGetLastError(), "decode_step append launch")) != AKV_OK) return rc;
-    int rest = rest_len + 1, qn = rest_start;
+    int rest = rest_len + (append ? 1 : 0), qn = rest_start;
     if (rest == BLK) {   // the buffered block goes to the planes (k_cache_file.py:102-118, v_cache_file.py:103-116)
         rc = launch_k_save(static_cast<uint8_t*>(k_first_8), static_cast<uint8_t*>(k_mid_4),
                            static_cast<uint8_t*>(k_last_4), static_cast<const uint8_t*>(restk), B, H, 1, nmb, D, BLK, qn,
@@ -308,37 +374,67 @@ int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_firs
         if (ev) cudaEventRecord(ev[0], st);
         rc = launch_k_compute(static_cast<const uint8_t*>(k_first_8), static_cast<const uint8_t*>(k_mid_4),
                               static_cast<const uint8_t*>(k_last_4), sc.kq, sc.kqmax, static_cast<const uint8_t*>(q),
-                              reinterpret_cast<uint8_t*>(sc.s), B, H, nb, nmb, D, BLK, 1.0f / sqrtf((float)D),
-                              reference != 0, st);
+                              reinterpret_cast<uint8_t*>(sc.s), B, H, G, nb, nmb, D, BLK, 1.0f / sqrtf((float)D),
+                              reference, st);
         if (ev) cudaEventRecord(ev[1], st);
         if (rc != AKV_OK) return rc;
     }
-    softmax_kernel<<<B * H, 256, 0, st>>>(sc.s, static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval,
-                                         sc.pidx, H, D, R, qn, rest, sqrtf((float)D));
+    softmax_kernel<<<B * H * G, 256, 0, st>>>(sc.s, static_cast<const __half*>(q), static_cast<const __half*>(restk),
+                                             sc.pval, sc.pidx, sc.stats, H, G, D, R, qn, rest, sqrtf((float)D));
     if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
+    const bool need_tail = rest > 0 || qn == 0 || packed_out != nullptr || order_free;
     if (qn > 0) {
         rc = launch_v_probe(static_cast<const uint8_t*>(v_first_8), reinterpret_cast<const uint8_t*>(sc.pval),
-                            reinterpret_cast<const uint8_t*>(sc.pidx), reinterpret_cast<uint8_t*>(sc.test_o), B, H,
+                            reinterpret_cast<const uint8_t*>(sc.pidx), reinterpret_cast<uint8_t*>(sc.test_o), B, H, G,
                             max_seq_len, D, TOPK, st);
         if (rc != AKV_OK) return rc;
-        amin_kernel<<<(B * H + 3) / 4, 128, 0, st>>>(sc.test_o, static_cast<const uint8_t*>(v_exp_max), sc.amin, B * H, H,
-                                                    D);
+        amin_kernel<<<(B * H * G + 3) / 4, 128, 0, st>>>(sc.test_o, static_cast<const uint8_t*>(v_exp_max), sc.amin,
+                                                        B * H * G, H, G, D);
         if ((rc = cuda_status(cudaGetLastError(), "decode_step threshold launch")) != AKV_OK) return rc;
         if (ev) cudaEventRecord(ev[2], st);
-        rc = launch_v_compute(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
-                              static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
-                              reinterpret_cast<uint8_t*>(rest ? (void*)sc.o_main : out), B, H, 1, max_seq_len, D, R, qn,
-                              reference != 0, st);
+        if (order_free)
+            rc = launch_v_split(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                                static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
+                                nullptr, sc.o_main32, sc.partial, B, H, G, max_seq_len, D, R, qn, reference, st);
+        else
+            rc = launch_v_compute(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                                  static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
+                                  reinterpret_cast<uint8_t*>(need_tail ? (void*)sc.o_main : out), B, H, G, max_seq_len,
+                                  D, R, qn, reference, st);
         if (ev) cudaEventRecord(ev[3], st);
         if (rc != AKV_OK) return rc;
+    } else if (order_free) {
+        rc = cuda_status(cudaMemsetAsync(sc.o_main32, 0, (size_t)B * H * G * D * sizeof(float), st),
+                         "decode_step clear");
+        if (rc != AKV_OK) return rc;
     }
-    if (rest > 0 || qn == 0) {
-        tail_kernel<<<B * H, D < 256 ? ((D + 31) / 32) * 32 : 256, 0, st>>>(
-            qn > 0 ? sc.o_main : nullptr, sc.s, static_cast<const __half*>(restv), static_cast<__half*>(out), H, D, R, qn,
-            rest);
+    if (need_tail) {
+        tail_kernel<<<B * H * G, D < 256 ? ((D + 31) / 32) * 32 : 256, 0, st>>>(
+            (qn > 0 && !order_free) ? sc.o_main : nullptr, order_free ? sc.o_main32 : nullptr, sc.s,
+            static_cast<const __half*>(restv), static_cast<__half*>(out), sc.stats, static_cast<float*>(packed_out), H, G,
+            D, R, qn, rest);
         if ((rc = cuda_status(cudaGetLastError(), "decode_step tail launch")) != AKV_OK) return rc;
     }
     return AKV_OK;
+}
+
+int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                    void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                    const void* v_new, void* out, void* scratch, long long scratch_bytes, int bsz, int n_heads,
+                    int head_dim, int max_seq_len, int rest_len, int rest_start, int reference, void* stream) {
+    AKV_REQUIRE(out && k_new && v_new, AKV_ERR_NULL, "decode_step: null pointer");
+    return akv_decode_step_ex(k_first_8, k_mid_4, k_last_4, v_first_8, v_mid_4, v_last_4, k_exp_max, v_exp_max, restk,
+                              restv, q, k_new, v_new, out, nullptr, scratch, scratch_bytes, bsz, n_heads, 1, head_dim,
+                              max_seq_len, rest_len, rest_start, reference ? AKV_STEP_REFERENCE : 0, stream);
+}
+
+int akv_lse_merge(const void* packed, void* out, int n_ranks, int rows, int head_dim, void* stream) {
+    set_error("");
+    AKV_REQUIRE(packed && out, AKV_ERR_NULL, "lse_merge: null pointer");
+    AKV_REQUIRE(n_ranks > 0 && rows > 0 && head_dim > 0, AKV_ERR_SHAPE, "lse_merge: bad extent (%d ranks, %d rows, "
+                "head_dim %d)", n_ranks, rows, head_dim);
+    return launch_lse_merge(static_cast<const float*>(packed), static_cast<uint8_t*>(out), n_ranks, rows, head_dim,
+                            static_cast<cudaStream_t>(stream));
 }
 
 

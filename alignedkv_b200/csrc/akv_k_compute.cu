@@ -13,8 +13,8 @@
 // from memory; the producer writes the substitute constants into their slots so that the consumer is
 // branch-free).  Lane (tile, i) owns tokens 8i..8i+7 of its tile and keeps four fp16x2 accumulators: one 8-byte
 // and two 4-byte shared loads feed four FMAs, and no cross-lane reduction exists, which is what keeps the
-// channel-order fp16 sum exact.  Because a B200 needs well over 100 KB in flight per SM to saturate HBM and the
-// rings cannot hold that much, the producer also issues L2 prefetches a few stages ahead of the copies.
+// channel-order fp16 sum exact.  Grouped-query attention (G query heads per KV head) runs the G passes over a
+// unit's tiles back to back on the same warp, so that only the first pass reads HBM.
 #include "akv_common.cuh"
 
 namespace akv {
@@ -38,41 +38,22 @@ struct KParams {
     const uint8_t* q;
     uint8_t* s;
     int BH, nb, nmb, D, ngroups;
+    int G;                // query heads per KV head; kq, kqmax, q and s are per (batch, query head)
     int units, upw;       // total units, units per warp (contiguous run)
-    int pf_dist;          // L2 prefetch distance in stages (0 = off)
     uint32_t scale2;      // half(sqrt_dim) in both halves
     int reference;
-    int debug;
 };
 
 __device__ __forceinline__ void st_shared_v4(uint32_t a, uint32_t v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(a), "r"(v) : "memory");
 }
-__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p), "r"(bytes) : "memory");
-}
 
-__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(a), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t a, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar) : "memory");
-}
-
-// Position of a stream of stages (unit, channel chunk) inside one warp's run of units.
+// Position of a stream of stages (unit, channel chunk) inside one warp's run of units.  Units are ordered
+// (batch, KV head) -> group of 4 blocks -> query head of the group, so the G passes over the same tiles (one per
+// query head) run back to back on the same warp and all but the first are served by L2.
 struct KCursor {
-    int u, g, bh, c;          // absolute unit, group inside (batch, head), (batch, head), channel chunk
-    int slot;                 // metadata slot of the current (batch, head)
+    int u, g, bh, gq, c;      // absolute unit, block group inside (batch, KV head), (batch, KV head), query head, chunk
+    int slot;                 // metadata slot of the current (batch, query head)
     size_t row;               // plane row index of (tile 0 of the unit, first channel of the chunk)
 };
 
@@ -95,33 +76,40 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     const int nch = p.D / KCH;
     const int total = (u_end - u_begin) * nch;
     const size_t tile_f = (size_t)p.D * 64, tile_n = (size_t)p.D * 32;
+    const int G = p.G;
 
-    uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META + 64);
-    const uint32_t mbar_a = smem_u32(ring + STAGES * STAGE + NMETA * META);
-    if (lane == 0) for (int i = 0; i < STAGES; ++i) mbar_init(mbar_a + i * 8, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    __syncwarp();
+    uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META);
     uint8_t* meta0 = ring + STAGES * STAGE;
     const uint32_t ring_a = smem_u32(ring);
 
     auto cursor_at = [&](int u) {
         KCursor k;
         k.u = u;
-        k.bh = u / p.ngroups;
-        k.g = u - k.bh * p.ngroups;
+        k.gq = u % G;
+        const int ug = u / G;
+        k.bh = ug / p.ngroups;
+        k.g = ug - k.bh * p.ngroups;
         k.c = 0;
         k.slot = 0;
         k.row = ((size_t)k.bh * p.nmb + (size_t)k.g * TILES) * p.D;
         return k;
     };
-    auto advance = [&](KCursor& k) {   // next stage; returns true when a new (batch, head) starts
+    auto advance = [&](KCursor& k) {   // next stage; returns true when a new (batch, query head) starts
         k.row += KCH;
         if (++k.c < nch) return false;
         k.c = 0;
         ++k.u;
+        if (++k.gq < G) {                                 // same tiles again for the next query head of the group
+            k.row -= (size_t)p.D;
+            k.slot = (k.slot + 1 == NMETA) ? 0 : k.slot + 1;
+            return true;
+        }
+        k.gq = 0;
         if (++k.g < p.ngroups) {
-            k.row += (size_t)(TILES - 1) * p.D;          // next 4 tiles of the same (batch, head)
-            return false;
+            k.row += (size_t)(TILES - 1) * p.D;          // next 4 tiles of the same (batch, KV head)
+            if (G == 1) return false;
+            k.slot = (k.slot + 1 == NMETA) ? 0 : k.slot + 1;
+            return true;
         }
         k.g = 0;
         ++k.bh;
@@ -129,18 +117,18 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
         k.row = (size_t)k.bh * p.nmb * p.D;
         return true;
     };
-    // Per (batch, head): plane-read masks (bit d set = row d of that plane is read: mid iff
+    // Per (batch, query head): plane-read masks (bit d set = row d of that plane is read: mid iff
     // (u8)(kqmax - kq[d]) < 8, low iff < 4; K_cache.cu:211,249-250) and q as fp16x2 words with both halves equal.
-    auto load_meta = [&](int bh, int slot) {
+    auto load_meta = [&](long long bhq, int slot) {
         uint32_t* masks = reinterpret_cast<uint32_t*>(meta0 + (size_t)slot * META);
         uint32_t* q2 = masks + 16;
-        const uint32_t top = __ldg(p.kqmax + bh);
+        const uint32_t top = __ldg(p.kqmax + bhq);
         for (int r = 0; r < (p.D + 31) / 32; ++r) {
             const int d = r * 32 + lane;
             uint32_t diff = 0, qh = 0;
             if (d < p.D) {
-                diff = (top - (uint32_t)__ldg(p.kq + (size_t)bh * p.D + d)) & 0xFFu;
-                qh = __ldg(reinterpret_cast<const uint16_t*>(p.q) + (size_t)bh * p.D + d);
+                diff = (top - (uint32_t)__ldg(p.kq + (size_t)bhq * p.D + d)) & 0xFFu;
+                qh = __ldg(reinterpret_cast<const uint16_t*>(p.q) + (size_t)bhq * p.D + d);
                 q2[d] = qh | (qh << 16);
             }
             const uint32_t mm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 8);
@@ -166,24 +154,11 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
         const uint32_t st = ring_a + (uint32_t)pstage * STAGE;
         const int ptiles = p.nb - pk.g * TILES;
         const uint8_t* pf = p.first8 + pk.row * 64 + lane * 16;
-        if (p.debug & 16) {
-            if (lane == 0) {
-                const int nt = ptiles < TILES ? ptiles : TILES;
-                mbar_expect_tx(mbar_a + pstage * 8, nt * KCH * 64);
-                const uint8_t* src = p.first8 + pk.row * 64;
-                for (int t = 0; t < nt; ++t)
-                    bulk_g2s(st + t * F_TILE, (p.debug & 8) ? src + (size_t)t * KCH * 64 : src + t * tile_f, KCH * 64,
-                             mbar_a + pstage * 8);
-            }
-        } else if (!(p.debug & 2)) {
-            const size_t tf = (p.debug & 8) ? (size_t)KCH * 64 : tile_f;
 #pragma unroll
         for (int it = 0; it < TILES * F_IT; ++it) {      // high-byte plane: KCH*64 contiguous bytes per tile
             const int t = it / F_IT, v = it % F_IT;
-            if (t < ptiles) cp_async16(st + t * F_TILE + v * 512 + lane * 16, pf + t * tf + v * 512);
+            if (t < ptiles) cp_async16(st + t * F_TILE + v * 512 + lane * 16, pf + t * tile_f + v * 512);
         }
-        }
-        if (!(p.debug & 4)) {
         const size_t pn = (pk.row + nrow) * 32 + nhalf;
         const uint32_t nd = st + F_BYTES + nrow * 32 + nhalf;
 #pragma unroll
@@ -197,53 +172,12 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
                 else st_shared_v4(dl, need_m ? 0x88888888u : 0u);  // low plane not read: low nibble becomes 8
             }
         }
-        }
-        if (p.pf_dist >= 100 && pk.c == 0 && pk.u + 1 < u_end) {
-            // whole next unit, tile by tile: DRAM sees 8 KB / 4 KB contiguous requests
-            const int nu = pk.u + 1;
-            const int nbh = nu / p.ngroups, ng = nu - nbh * p.ngroups;
-            const size_t nrow0 = ((size_t)nbh * p.nmb + (size_t)ng * TILES) * p.D;
-            const int nt = p.nb - ng * TILES;
-            if (lane < TILES && lane < nt) l2_prefetch(p.first8 + (nrow0 + (size_t)lane * p.D) * 64, p.D * 64);
-            if (p.pf_dist >= 101 && lane >= 4 && lane < 4 + TILES && lane - 4 < nt)
-                l2_prefetch(p.mid4 + (nrow0 + (size_t)(lane - 4) * p.D) * 32, p.D * 32);
-        }
         pstage = (pstage + 1 == STAGES) ? 0 : pstage + 1;
-        if (advance(pk) && pk.u < u_end) load_meta(pk.bh, pk.slot);
-    };
-
-    // ---- L2 prefetch stream, pf_dist stages ahead of the copies (high-byte rows always; nibble rows when the
-    //      stage belongs to the (batch, head) whose masks are loaded)
-    KCursor fk = cursor_at(u_begin);
-    int fcount = 0;   // stages prefetched so far
-    auto prefetch = [&]() {
-        const int ptiles = p.nb - fk.g * TILES;
-        if (lane < TILES && lane < ptiles) l2_prefetch(p.first8 + (fk.row + (size_t)lane * p.D) * 64, KCH * 64);
-        if (fk.bh == pk.bh) {
-            const uint32_t* masks = reinterpret_cast<const uint32_t*>(meta0 + (size_t)pk.slot * META);
-            const int sh = ((fk.c * KCH) & 31) + nrow, wi = (fk.c * KCH) >> 5;
-            const bool need_m = (masks[wi] >> sh) & 1u;
-            const bool need_l = (masks[8 + wi] >> sh) & 1u;
-            if (nhalf == 0) {
-#pragma unroll
-                for (int it = 0; it < TILES / TILES_PER_IT; ++it) {
-                    const int t = it * TILES_PER_IT + ntsub;
-                    if (t < ptiles) {
-                        const size_t off = (fk.row + nrow) * 32 + t * tile_n;
-                        if (need_m) l2_prefetch(p.mid4 + off, 32);
-                        if (need_l) l2_prefetch(p.last4 + off, 32);
-                    }
-                }
-            }
-        }
-        ++fcount;
-        advance(fk);
+        if (advance(pk) && pk.u < u_end) load_meta((long long)pk.bh * G + pk.gq, pk.slot);
     };
 
     // ---- prologue
-    load_meta(pk.bh, 0);
-    if (p.pf_dist > 0 && p.pf_dist < 100)
-        for (int j = 0; j < p.pf_dist + STAGES - 1 && j < total; ++j) prefetch();
+    load_meta((long long)pk.bh * G + pk.gq, 0);
     for (int j = 0; j < STAGES - 1; ++j) {
         if (j < total) issue();
         cp_async_commit();
@@ -255,15 +189,9 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     int cstage = 0;
     for (int i = 0; i < total; ++i) {
         cp_async_wait<STAGES - 2>();
-        if (p.debug & 16) {
-            const uint32_t par = (uint32_t)((i / STAGES) & 1);
-            int spins = 0;
-            while (!mbar_try_wait(mbar_a + cstage * 8, par) && ++spins < (1 << 22)) {}
-        }
         __syncwarp();
         if (i + STAGES - 1 < total) issue();
         cp_async_commit();
-        if (p.pf_dist > 0 && p.pf_dist < 100 && fcount < total) prefetch();
 
         const uint8_t* stp = ring + (size_t)cstage * STAGE;
         cstage = (cstage + 1 == STAGES) ? 0 : cstage + 1;
@@ -271,7 +199,6 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
         const uint32_t* mp = reinterpret_cast<const uint32_t*>(stp + F_BYTES + tile * N_TILE + li * 4);
         const uint32_t* lp = reinterpret_cast<const uint32_t*>(stp + F_BYTES + N_BYTES + tile * N_TILE + li * 4);
         const uint4* qp = reinterpret_cast<const uint4*>(meta0 + (size_t)ck.slot * META + 64 + ck.c * (KCH * 4));
-        if (!(p.debug & 1))
 #pragma unroll
         for (int r4 = 0; r4 < KCH / 4; ++r4) {
             const uint4 qv = qp[r4];
@@ -289,7 +216,8 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
                 acc57 = hfma2_bits(__byte_perm(lbo, f.y, 0x7352), q2s[rr], acc57);
             }
         }
-        const int cbh = ck.bh, cg = ck.g;
+        const long long cbhq = (long long)ck.bh * G + ck.gq;
+        const int cg = ck.g;
         const bool last_chunk = (ck.c == nch - 1);
         advance(ck);
         if (last_chunk) {  // unit finished: scale, reorder to token order, one 16-byte store per lane
@@ -304,7 +232,7 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
                 o.y = __byte_perm(acc02, acc13, 0x7632);
                 o.z = __byte_perm(acc46, acc57, 0x5410);
                 o.w = __byte_perm(acc46, acc57, 0x7632);
-                const size_t row = (size_t)cbh * (size_t)(p.nb + 1) * 64 + (size_t)blk * 64 + li * 8;
+                const size_t row = (size_t)cbhq * (size_t)(p.nb + 1) * 64 + (size_t)blk * 64 + li * 8;
                 *reinterpret_cast<uint4*>(p.s + row * 2) = o;
             }
             acc02 = acc13 = acc46 = acc57 = 0;
@@ -318,19 +246,20 @@ __global__ void __launch_bounds__(128)
 k_compute_generic_kernel(const uint8_t* __restrict__ first8, const uint8_t* __restrict__ mid4,
                          const uint8_t* __restrict__ last4, const uint8_t* __restrict__ kq,
                          const uint8_t* __restrict__ kqmax, const __half* __restrict__ q, __half* __restrict__ s,
-                         int nb, int nmb, int D, int d_block, __half scale, int reference, long long total) {
+                         int nb, int nmb, int D, int d_block, int G, __half scale, int reference, long long total) {
     const int hb = d_block >> 1;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         int t = (int)(i % d_block);
         long long r = i / d_block;
         int z = (int)(r % nb);
-        long long bh = r / nb;
+        long long bh = r / nb;            // (batch, query head)
+        const long long bkv = bh / G;     // (batch, KV head)
         const uint32_t top = kqmax[bh];
         __half acc = __ushort_as_half(0);
         for (int d = 0; d < D; ++d) {
             uint32_t diff = (top - (uint32_t)kq[bh * D + d]) & 0xFFu;
-            long long row = ((bh * nmb + z) * D + d) * hb;
+            long long row = ((bkv * nmb + z) * D + d) * hb;
             uint32_t f = first8[2 * row + t];
             uint32_t mb = 0x88u, lb = 0x00u;
             if (reference || diff < 8) {
@@ -345,42 +274,43 @@ k_compute_generic_kernel(const uint8_t* __restrict__ first8, const uint8_t* __re
     }
 }
 
+// q.K^T over nb quantized blocks.  H = KV heads, group = query heads per KV head; kq, kqmax, q and the score rows are
+// per (batch, query head) with query head = KV head * group + g.
 int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* kq,
-                     const uint8_t* kqmax, const uint8_t* q, uint8_t* s, int bsz, int H, int nb, int nmb, int D,
-                     int d_block, float sqrt_dim, int reference, cudaStream_t st) {
+                     const uint8_t* kqmax, const uint8_t* q, uint8_t* s, int bsz, int H, int group, int nb, int nmb,
+                     int D, int d_block, float sqrt_dim, int reference, cudaStream_t st) {
     using namespace kc;
     const __half scale = __float2half_rn(sqrt_dim);
     const bool fast = d_block == 64 && D % 16 == 0 && D >= 64 && D <= MAX_D && aligned16(first8) &&
                       aligned16(mid4) && aligned16(last4) && aligned16(kq) && aligned16(q) && aligned16(s);
     if (!fast) {
-        long long total = (long long)bsz * H * nb * d_block;
+        long long total = (long long)bsz * H * group * nb * d_block;
         long long want = (total + 127) / 128;
         int grid = (int)(want < (long long)sm_count() * 16 ? want : (long long)sm_count() * 16);
         k_compute_generic_kernel<<<grid, 128, 0, st>>>(first8, mid4, last4, kq, kqmax,
                                                        reinterpret_cast<const __half*>(q),
-                                                       reinterpret_cast<__half*>(s), nb, nmb, D, d_block, scale,
-                                                       reference, total);
+                                                       reinterpret_cast<__half*>(s), nb, nmb, D, d_block, group,
+                                                       scale, reference, total);
         return cuda_status(cudaGetLastError(), "k_cache_compute launch");
     }
     KParams p;
     p.first8 = first8; p.mid4 = mid4; p.last4 = last4; p.kq = kq; p.kqmax = kqmax; p.q = q; p.s = s;
     p.BH = bsz * H; p.nb = nb; p.nmb = nmb; p.D = D;
     p.ngroups = (nb + TILES - 1) / TILES;
-    const long long units = (long long)p.BH * p.ngroups;
+    p.G = group;
+    const long long units = (long long)p.BH * p.ngroups * group;
     AKV_REQUIRE(units < (1ll << 30), AKV_ERR_OVERFLOW, "k_cache_compute: too many blocks");
     p.units = (int)units;
     const unsigned short sb = __half_as_ushort(scale);
     p.scale2 = (uint32_t)sb | ((uint32_t)sb << 16);
     p.reference = reference;
-    p.pf_dist = tuning().k_prefetch;
-    p.debug = tuning().debug;
 
     // One CTA per SM.  Pick the channel-chunk size, ring depth and warps per CTA (tunable), trimming the warp
     // count so that every warp gets (nearly) the same whole number of units.
     const int sms = sm_count();
     const int budget = max_dyn_smem();
     const int kch = tuning().k_kch, stages = tuning().k_stages;
-    const int per_warp = stages * stage_bytes(kch) + NMETA * META + 64;
+    const int per_warp = stages * stage_bytes(kch) + NMETA * META;
     int wmax = budget / per_warp;
     if (wmax > 16) wmax = 16;
     if (tuning().k_wpc > 0 && tuning().k_wpc < wmax) wmax = tuning().k_wpc;

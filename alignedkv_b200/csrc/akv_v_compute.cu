@@ -449,7 +449,7 @@ int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     p.group = group;
     const int BH = bsz * H;
     const bool fast = D == 128 && aligned16(first8) && aligned16(mid4) && aligned16(last4) &&
-                      (n == 0 || (aligned16(s) && s_last_dim % 8 == 0)) &&
+                      (n == 0 || (aligned16(s) && s_last_dim % 8 == 0 && ((n + 7) & ~7) <= s_last_dim)) &&
                       ((reinterpret_cast<uintptr_t>(o) & 3u) == 0);
     if (fast && group == 1) return launch_v_fast<1, 10, 2>(p, BH, st);
     if (fast && group == 2) return launch_v_fast<2, 10, 2>(p, BH, st);
@@ -468,9 +468,9 @@ int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
 template <int KMAX>
 __global__ void __launch_bounds__(128)
 v_probe_kernel(const uint8_t* __restrict__ first8, const uint16_t* __restrict__ s_val,
-               const int32_t* __restrict__ s_idx, uint16_t* __restrict__ out, int max_seq_len, int D, int K) {
-    const long long bh = blockIdx.x;
-    const uint8_t* F = first8 + (size_t)bh * max_seq_len * D;
+               const int32_t* __restrict__ s_idx, uint16_t* __restrict__ out, int max_seq_len, int D, int K, int G) {
+    const long long bh = blockIdx.x;                                    // (batch, query head)
+    const uint8_t* F = first8 + (size_t)(bh / G) * max_seq_len * D;     // planes of its KV head
     for (int c = threadIdx.x; c < (D >> 1); c += blockDim.x) {
         uint32_t acc = 0;
         for (int j0 = 0; j0 < K; j0 += KMAX) {
@@ -500,11 +500,11 @@ v_probe_kernel(const uint8_t* __restrict__ first8, const uint16_t* __restrict__ 
 }
 
 int launch_v_probe(const uint8_t* first8, const uint8_t* s_val, const uint8_t* s_idx, uint8_t* out, int bsz, int H,
-                   int max_seq_len, int D, int K, cudaStream_t st) {
+                   int group, int max_seq_len, int D, int K, cudaStream_t st) {
     int threads = (D >> 1) < 128 ? (((D >> 1) + 31) / 32) * 32 : 128;
-    v_probe_kernel<32><<<bsz * H, threads, 0, st>>>(first8, reinterpret_cast<const uint16_t*>(s_val),
-                                                    reinterpret_cast<const int32_t*>(s_idx),
-                                                    reinterpret_cast<uint16_t*>(out), max_seq_len, D, K);
+    v_probe_kernel<32><<<bsz * H * group, threads, 0, st>>>(first8, reinterpret_cast<const uint16_t*>(s_val),
+                                                            reinterpret_cast<const int32_t*>(s_idx),
+                                                            reinterpret_cast<uint16_t*>(out), max_seq_len, D, K, group);
     return cuda_status(cudaGetLastError(), "v_cache_test_compute launch");
 }
 

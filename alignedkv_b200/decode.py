@@ -19,13 +19,29 @@ from .extension.KV_cache_cpp_extention import cuda_module
 __all__ = ["DecodeLayer"]
 
 
+AKV_STEP_REFERENCE, AKV_STEP_ORDER_FREE, AKV_STEP_NO_APPEND = 1, 2, 4
+
+
 class DecodeLayer:
+    """One layer's planes, residual buffers and exponent maxima, driven by `akv_decode_step_ex`.
+
+    n_heads is the number of KV heads; n_q_heads (default: the same) may be a multiple of it (grouped-query
+    attention; query head i reads KV head i // group).  v_mode "exact" runs P.V in the reference's token order
+    (bit-identical to its kernel), "order_free" splits the token axis and accumulates in fp32."""
     # DRAM bytes per launch from the committed ncu capture of the bench workload (profiles/), by kernel
     NCU_TRAFFIC = {}
 
-    def __init__(self, bsz: int, max_seq_len: int, n_heads: int, head_dim: int, device):
+    def __init__(self, bsz: int, max_seq_len: int, n_heads: int, head_dim: int, device, n_q_heads: int | None = None,
+                 v_mode: str = "exact"):
         self.lib = _lib.load()
         self.B, self.L, self.H, self.D = bsz, max_seq_len, n_heads, head_dim
+        self.Hq = n_heads if n_q_heads is None else n_q_heads
+        if self.Hq % n_heads:
+            raise ValueError("n_q_heads must be a multiple of n_heads")
+        self.G = self.Hq // n_heads
+        if v_mode not in ("exact", "order_free"):
+            raise ValueError("v_mode must be 'exact' or 'order_free'")
+        self.v_mode = v_mode
         self.device = torch.device(device)
         nmb = cdiv(max_seq_len, column_block)
         z = lambda *shape: torch.zeros(shape, dtype=torch.uint8, device=self.device)  # noqa: E731
@@ -43,11 +59,15 @@ class DecodeLayer:
         self.rest_start = 0
         self.cache_len = 0
         self.reference = False
-        nbytes = self.lib.akv_decode_scratch_bytes(bsz, n_heads, head_dim, max_seq_len)
+        nbytes = self.lib.akv_decode_scratch_bytes_ex(bsz, n_heads, self.G, head_dim, max_seq_len, self._flags())
         if nbytes < 0:
             raise ValueError("bad extents")
         self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.launches = 0
+
+    def _flags(self, append: bool = True) -> int:
+        return (AKV_STEP_REFERENCE if getattr(self, "reference", False) else 0) | \
+               (AKV_STEP_ORDER_FREE if self.v_mode == "order_free" else 0) | (0 if append else AKV_STEP_NO_APPEND)
 
     # ------------------------------------------------------------------ prompt
     def prefill(self, k: torch.Tensor, v: torch.Tensor) -> None:
@@ -71,32 +91,45 @@ class DecodeLayer:
         self.cache_len = S
 
     # ------------------------------------------------------------------ one decode token
-    def decode(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-        """Append (k, v) of one token per sequence and return the attention output [B,1,H,D] (fp16)."""
-        B, H, D = self.B, self.H, self.D
-        for name, t in (("q", q), ("k", k), ("v", v)):
-            if t.shape != (B, 1, H, D) or t.dtype != torch.half or not t.is_cuda or not t.is_contiguous():
-                raise RuntimeError(f"{name}: expected a contiguous CUDA fp16 tensor of shape {(B, 1, H, D)}")
-        if self.cache_len + 1 > self.L:
+    def decode(self, q: torch.Tensor, k: torch.Tensor | None = None, v: torch.Tensor | None = None, *,
+               append: bool = True, packed: bool = False):
+        """Append (k, v) of one token per sequence and return the attention output [B,1,Hq,D] (fp16).
+
+        append=False leaves the cache as it is (the token belongs to another shard of the sequence).  packed=True
+        returns instead the fp32 record [B*Hq, D+2] = (max score, sum of exponentials, output) over this cache's
+        tokens, which `akv_lse_merge` combines across the shards of a sequence."""
+        B, H, Hq, D = self.B, self.H, self.Hq, self.D
+        checks = [("q", q, Hq)] + ([("k", k, H), ("v", v, H)] if append else [])
+        for name, t, heads in checks:
+            if t is None or t.shape != (B, 1, heads, D) or t.dtype != torch.half or not t.is_cuda or \
+                    not t.is_contiguous():
+                raise RuntimeError(f"{name}: expected a contiguous CUDA fp16 tensor of shape {(B, 1, heads, D)}")
+        if append and self.cache_len + 1 > self.L:
             raise RuntimeError(f"cache is full ({self.L} tokens)")
-        out = torch.empty((B, 1, H, D), dtype=torch.half, device=self.device)
+        out = None if packed else torch.empty((B, 1, Hq, D), dtype=torch.half, device=self.device)
+        rec = torch.empty((B * Hq, D + 2), dtype=torch.float32, device=self.device) if packed else None
         with torch.cuda.device(self.device):
-            rc = self.lib.akv_decode_step(
+            rc = self.lib.akv_decode_step_ex(
                 self.k_first_8.data_ptr(), self.k_mid_4.data_ptr(), self.k_last_4.data_ptr(),
                 self.v_first_8.data_ptr(), self.v_mid_4.data_ptr(), self.v_last_4.data_ptr(),
                 self.k_exp_max.data_ptr(), self.v_exp_max.data_ptr(), self.restk.data_ptr(), self.restv.data_ptr(),
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), self.scratch.data_ptr(),
-                self.scratch.numel(), B, H, D, self.L, self.rest_len, self.rest_start, int(self.reference),
-                torch.cuda.current_stream(self.device).cuda_stream)
+                q.data_ptr(), k.data_ptr() if append else None, v.data_ptr() if append else None,
+                out.data_ptr() if out is not None else None, rec.data_ptr() if rec is not None else None,
+                self.scratch.data_ptr(), self.scratch.numel(), B, H, self.G, D, self.L, self.rest_len, self.rest_start,
+                self._flags(append), torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check("decode_step", rc)
-        flush = self.rest_len + 1 == column_block
+        flush = append and self.rest_len + 1 == column_block
         qn = self.rest_start + (column_block if flush else 0)
-        rest = 0 if flush else self.rest_len + 1
-        # kernels of this library launched by the call: append, (2 flush), q.K^T, softmax, probe, threshold, P.V, tail
-        self.launches += 1 + (2 if flush else 0) + (1 if qn else 0) + 1 + (3 if qn else 0) + (1 if rest or not qn else 0)
+        rest = 0 if flush else self.rest_len + (1 if append else 0)
+        tail = rest > 0 or qn == 0 or packed or self.v_mode == "order_free"
+        # kernels of this library launched by the call: append, (2 flush), q.K^T, softmax, probe, threshold, P.V
+        # (2 for the order-free form), tail
+        self.launches += 1 + (2 if flush else 0) + (1 if qn else 0) + 1 + \
+            ((3 + (1 if self.v_mode == "order_free" else 0)) if qn else 0) + (1 if tail else 0)
         self.rest_len, self.rest_start = rest, qn
-        self.cache_len += 1
-        return out
+        if append:
+            self.cache_len += 1
+        return rec if packed else out
 
     # ------------------------------------------------------------------ benchmark helpers
     def snapshot(self):
@@ -125,7 +158,7 @@ class DecodeLayer:
         self.lib.akv_timing_reset()
 
     def kernel_times(self):
-        """Mean CUDA-event duration of the two streaming kernels over the steps since reset_counters()."""
+        """Median CUDA-event duration of the two streaming kernels over the steps since reset_counters()."""
         torch.cuda.synchronize(self.device)
         k_us, v_us = ctypes.c_double(0), ctypes.c_double(0)
         n = self.lib.akv_timing_read(ctypes.byref(k_us), ctypes.byref(v_us))
@@ -137,25 +170,27 @@ class DecodeLayer:
     def bytes_accounting(self, q: torch.Tensor):
         """Algorithmic plane bytes of the LAST decode step under its read decisions (mid plane iff code < 2, low
         plane iff code < 1), from the state the step left behind, plus the dense fp16 equivalent."""
-        B, H, D = self.B, self.H, self.D
+        B, H, Hq, G, D = self.B, self.H, self.Hq, self.G, self.D
         qn = self.rest_start
-        kq = exponent_field(q) + self.k_exp_max
-        diff = (kq.max(dim=3, keepdim=True).values - kq)
-        k_rows = float(B * H * D) + 0.5 * float((diff < 8).sum()) + 0.5 * float((diff < 4).sum())
+        # K: per (batch, KV head, channel) the union over the group's query heads of the plane reads
+        kq = exponent_field(q).view(B, 1, H, G, D) + self.k_exp_max.view(B, 1, H, 1, D)
+        diff = (kq.max(dim=4, keepdim=True).values - kq)
+        k_rows = float(B * H * D) + 0.5 * float((diff < 8).any(dim=3).sum()) + 0.5 * float((diff < 4).any(dim=3).sum())
         k_bytes = qn * k_rows
         R = (qn // column_block + 1) * column_block
-        p = self.scratch[:B * H * R * 2].view(torch.half).view(B, H, R)[..., :qn]
+        p = self.scratch[:B * Hq * R * 2].view(torch.half).view(B, Hq, R)[..., :qn]
         amin_off = self._scratch_offset("amin")
-        amin = self.scratch[amin_off:amin_off + B * H].to(torch.int32).view(B, H, 1)
+        amin = self.scratch[amin_off:amin_off + B * Hq].to(torch.int32).view(B, Hq, 1)
         d = ((((amin << 10) & 0xFFFF) - p.view(torch.int16).to(torch.int32)) << 16) >> 16
-        v_rows = float(B * H * qn) + 0.5 * float((d < 0x800).sum()) + 0.5 * float((d < 0x400).sum())
+        d = d.view(B, H, G, qn)
+        v_rows = float(B * H * qn) + 0.5 * float((d < 0x800).any(dim=2).sum()) + 0.5 * float((d < 0x400).any(dim=2).sum())
         v_bytes = D * v_rows
         rest = 4.0 * (self.cache_len - qn) * D * B * H
         dense = 4.0 * B * H * self.cache_len * D
         return {"k_compute": k_bytes, "v_compute": v_bytes, "read": k_bytes + v_bytes + rest, "dense": dense}
 
     def _scratch_offset(self, name: str) -> int:
-        B, H, D = self.B, self.H, self.D
+        B, H, D = self.B, self.Hq, self.D
         R = (cdiv(self.L, column_block) + 1) * column_block
         up = lambda x: (x + 255) & ~255  # noqa: E731
         sizes = [("s", B * H * R * 2), ("kq", B * H * D), ("kqmax", B * H), ("pval", B * H * 32 * 2),

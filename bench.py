@@ -8,6 +8,11 @@ block through the plane-writer kernels), then one decode step (aligned q.K^T, so
 At N > 1 (launched with torchrun, one rank per GPU) every rank owns an independent shard of (batch, head) units of
 the same size - no collective is on the data path - so the job processes N x batch sequences per step.
 
+Other workloads (--workload): `llama3-8b-gqa-decode` (batch 64, 32 query heads over 8 KV heads, 8192 cached tokens;
+the batch is split across the ranks, no collective, strong scaling) and `long-context-decode` (batch 1, 32 heads,
+131072 cached tokens; at N > 1 the SEQUENCE is split across the ranks and the per-rank (max, sum, output) records are
+merged after one NCCL all-gather; order-free P.V kernel, because a 131072-step fp16 chain cannot be split).
+
 Prints ONE JSON line (rank 0).  `--impl reference` times the reference's CPU path (its torch dense attention,
 restated in oracle/pipeline.py) on the host cores instead.
 """
@@ -19,7 +24,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -27,10 +31,18 @@ sys.path.insert(0, ROOT)
 
 # Llama-2-7B-shaped decode attention, one layer (the configuration the metric is quoted on)
 WORKLOADS = {
-    "llama2-7b-layer-decode": dict(batch=8, heads=32, head_dim=128, cache_len=4096),
+    # sharding: "replicate" = every rank runs the whole shape on its own data (weak scaling); "batch" = the batch is
+    # split across ranks (strong); "sequence" = the cached sequence is split across ranks and merged (strong)
+    "llama2-7b-layer-decode": dict(batch=8, heads=32, kv_heads=32, head_dim=128, cache_len=4096, sharding="replicate",
+                                   v_mode="exact"),
     # a quarter of the batch: same kernels and per-(batch, head) work, planes still larger than L2; sized for profiler
     # captures that replay every launch many times
-    "llama2-7b-layer-decode-b2": dict(batch=2, heads=32, head_dim=128, cache_len=4096),
+    "llama2-7b-layer-decode-b2": dict(batch=2, heads=32, kv_heads=32, head_dim=128, cache_len=4096,
+                                      sharding="replicate", v_mode="exact"),
+    "llama3-8b-gqa-decode": dict(batch=64, heads=32, kv_heads=8, head_dim=128, cache_len=8192, sharding="batch",
+                                 v_mode="exact"),
+    "long-context-decode": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072, sharding="sequence",
+                                v_mode="order_free"),
 }
 WORKLOAD = dict(name="llama2-7b-layer-decode", **WORKLOADS["llama2-7b-layer-decode"])
 OUTLIER_CHANNELS = (3, 34, 65, 96)
@@ -47,6 +59,9 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--workload", default="llama2-7b-layer-decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--v-mode", default=None, choices=["exact", "order_free"],
+                    help="P.V kernel: exact = the reference's token order (bit-identical), order_free = split sequence, "
+                         "fp32 accumulation (default: per workload)")
     args = ap.parse_args()
     WORKLOAD.clear()
     WORKLOAD.update(name=args.workload, **WORKLOADS[args.workload])
@@ -76,7 +91,7 @@ def cpu_dense_baseline(seed: int, budget_s: float = 12.0):
         times.append(time.perf_counter() - t0)
     med = statistics.median(times)
     return {"value": 1.0 / med, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"1 of {WORKLOAD['batch']} batch rows (32 heads x 4096 cached tokens), median of {len(times)} "
+            "sample": f"1 of {WORKLOAD['batch']} batch rows ({H} heads x {L} cached tokens), median of {len(times)} "
                       f"runs of the reference's fp16 torch dense attention on CPU"}, med
 
 
@@ -100,44 +115,65 @@ def run_reference_arm(args):
 
 # ---------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs.  The sampler
+    is a separate process writing to a file, so that no Python thread competes with the launching thread."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines = []
+        self.path = None
 
     def start(self):
+        import tempfile
         try:
+            fd, self.path = tempfile.mkstemp(prefix="akv_clocks_", suffix=".csv")
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=fd,
+                                         stderr=subprocess.DEVNULL)
+            os.close(fd)
         except OSError:
             self.proc = None
 
-    def _pump(self):
-        for ln in self.proc.stdout:
-            self.lines.append((time.perf_counter(), ln.strip()))
-
-    def stop(self, t0: float, t1: float):
+    def stop(self, wall0: float, wall1: float):
+        """Summary of the samples taken between the two wall-clock times (time.time())."""
         if self.proc is None:
             return None
-        time.sleep(0.15)
+        time.sleep(0.25)
         self.proc.terminate()
-        rows = [ln.split(", ") for t, ln in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or \
-               [ln.split(", ") for _, ln in self.lines[-3:]]
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        import datetime
+        rows_all, rows_in = [], []
+        try:
+            with open(self.path) as f:
+                for ln in f:
+                    r = [x.strip() for x in ln.split(",")]
+                    if len(r) < 9:
+                        continue
+                    rows_all.append(r)
+                    try:
+                        ts = datetime.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    except ValueError:
+                        continue
+                    if wall0 - 0.5 <= ts <= wall1 + 0.5:    # the warm-up steps right before run the same load
+                        rows_in.append(r)
+            os.unlink(self.path)
+        except OSError:
+            return None
+        rows = rows_in or rows_all[-3:]
         sm, reasons, mx = [], set(), None
         for r in rows:
             try:
-                sm.append(float(r[0]))
-                mx = float(r[1])
+                sm.append(float(r[1]))
+                mx = float(r[2])
             except (ValueError, IndexError):
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
                 if val.strip().lower() == "active":
                     reasons.add(name)
         if not sm:
@@ -164,35 +200,60 @@ def run_ours(args):
     from alignedkv_b200.decode import DecodeLayer
     _lib.load()
 
-    B, H, D, L = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["head_dim"], WORKLOAD["cache_len"]
+    Bt, Hq, H, D, L = (WORKLOAD[k_] for k_ in ("batch", "heads", "kv_heads", "head_dim", "cache_len"))
+    sharding = WORKLOAD["sharding"] if world > 1 else "replicate"
+    v_mode = args.v_mode or WORKLOAD["v_mode"]
+    from alignedkv_b200.sharded import SequenceShardedDecoder, shard_batch, shard_bounds
+    if sharding == "batch":
+        lo, hi = shard_batch(Bt, world, rank)
+        B = hi - lo
+        if B == 0:
+            raise SystemExit(f"batch {Bt} cannot be split over {world} ranks")
+    else:
+        B = Bt
     g = torch.Generator(device=dev).manual_seed(args.seed + 1000 * rank)
-    k = torch.randn(B, L, H, D, device=dev, generator=g)
-    k[..., list(OUTLIER_CHANNELS)] *= 20
-    k = k.half()
-    v = torch.randn(B, L, H, D, device=dev, generator=g).half()
-    q = torch.randn(B, 1, H, D, device=dev, generator=g).half()
 
-    layer = DecodeLayer(B, L, H, D, dev)
-    layer.prefill(k[:, :L - 1].contiguous(), v[:, :L - 1].contiguous())
-    snap = layer.snapshot()                                # state with 4095 cached tokens (63 in the residual)
-    k_tok, v_tok = k[:, L - 1:].contiguous(), v[:, L - 1:].contiguous()
+    def draw(tokens):
+        k_ = torch.randn(B, tokens, H, D, device=dev, generator=g)
+        k_[..., list(OUTLIER_CHANNELS)] *= 20
+        return k_.half(), torch.randn(B, tokens, H, D, device=dev, generator=g).half()
+
+    if sharding == "sequence":
+        # rank r holds tokens [lo, hi) of the L-1 cached tokens; the last rank also takes the decode token
+        seq = SequenceShardedDecoder(B, L - 1, 1, H, D, dev, n_q_heads=Hq, v_mode=v_mode)
+        lo, hi = shard_bounds(L - 1, world)[rank]
+        k, v = draw(hi - lo + 1)
+        seq.prefill(k[:, :hi - lo].contiguous(), v[:, :hi - lo].contiguous())
+        layer = seq.backend.layer
+        k_tok, v_tok = k[:, hi - lo:].contiguous(), v[:, hi - lo:].contiguous()
+    else:
+        seq = None
+        layer = DecodeLayer(B, L, H, D, dev, n_q_heads=Hq, v_mode=v_mode)
+        k, v = draw(L)
+        layer.prefill(k[:, :L - 1].contiguous(), v[:, :L - 1].contiguous())
+        k_tok, v_tok = k[:, L - 1:].contiguous(), v[:, L - 1:].contiguous()
     del k, v
+    q = torch.randn(B, 1, Hq, D, device=dev, generator=torch.Generator(device=dev).manual_seed(args.seed + 7)).half()
+    snap = layer.snapshot()                                # state before the decode token (63 tokens in the residual)
+
+    def decode(q_, k_, v_):
+        return seq.decode(q_, k_, v_) if seq is not None else layer.decode(q_, k_, v_)
 
     def step_resident():
         layer.restore(snap)
-        return layer.decode(q, k_tok, v_tok)
+        return decode(q, k_tok, v_tok)
 
     # host-side buffers for the end-to-end number (pinned), device staging buffers, pinned result
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k_tok, v_tok))
     dq, dk, dv = (torch.empty_like(t) for t in (q, k_tok, v_tok))
-    hout = torch.empty((B, 1, H, D), dtype=torch.half).pin_memory()
+    hout = torch.empty((B, 1, Hq, D), dtype=torch.half).pin_memory()
 
     def step_e2e():
         layer.restore(snap)
         dq.copy_(hq, non_blocking=True)
         dk.copy_(hk, non_blocking=True)
         dv.copy_(hv, non_blocking=True)
-        out = layer.decode(dq, dk, dv)
+        out = decode(dq, dk, dv)
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()          # the caller reads the result on the host
         return hout
@@ -208,13 +269,13 @@ def run_ours(args):
             fn()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
+        t0 = time.time()
         e0.record()
         for _ in range(steps):
             fn()
         e1.record()
         torch.cuda.synchronize()
-        t1 = time.perf_counter()
+        t1 = time.time()
         ms = e0.elapsed_time(e1)
         barrier()
         if world > 1:
@@ -231,13 +292,22 @@ def run_ours(args):
     ms, t0, t1 = timed(step_resident, args.steps, warm)
     clocks = sampler.stop(t0, t1) if sampler else None
     launches = layer.launches // (args.steps + warm)       # kernels of this library per step
+    if seq is not None:
+        launches += 1                                      # the merge kernel
     kern = layer.kernel_times()                            # per-kernel CUDA-event durations inside the timed region
     ms_e2e, _, _ = timed(step_e2e, args.steps, warm)
 
+    # algorithmic bytes under this step's read decisions, summed over the ranks
+    acct = layer.bytes_accounting(q)
+    keys = ("k_compute", "v_compute", "read", "dense")
+    tot = torch.tensor([acct[k_] for k_ in keys], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tot)
+    total = dict(zip(keys, (float(x) for x in tot.tolist())))
+
     if rank == 0:
         ms_step = ms / args.steps
-        tokens = B * world
-        acct = layer.bytes_accounting(q)                   # algorithmic bytes under this step's read decisions
+        tokens = Bt * world if WORKLOAD["sharding"] == "replicate" else Bt
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -250,25 +320,32 @@ def run_ours(args):
             a = acct[dom] / (kern[dom]["us"] * 1e-6) / 1e9
             roofline = {"bound": "hbm", "kernel": dom, "achieved": a, "peak": peak, "unit": "GB/s", "frac": a / peak,
                         "peak_source": "measured" if peaks else "fallback",
-                        "traffic": layer.NCU_TRAFFIC.get(dom), "us_per_launch": kern[dom]["us"],
-                        "algorithmic_bytes": acct[dom]}
+                        "traffic": layer.NCU_TRAFFIC.get((WORKLOAD["name"], dom)), "us_per_launch": kern[dom]["us"],
+                        "algorithmic_bytes": acct[dom], "timing": "median of CUDA-event brackets inside the timed steps"}
         line = {
             "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak" if WORKLOAD["sharding"] == "replicate" else "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD["name"], **{k_: v_ for k_, v_ in WORKLOAD.items() if k_ != "name"},
-                       "per_gpu_batch": B, "global_batch": tokens, "sharding": "(batch, kv-head) units, no collective",
-                       "step": "rewind to 4095 tokens -> append token 4096 (flushes a 64-token block through the "
-                               "plane writers) -> decode",
-                       "l2": "inputs larger than L2 (planes 512 MiB, ~0.3 GB read per step)"},
-            "effective_hbm_gbs": acct["dense"] * world / (ms_step * 1e-3) / 1e9,
-            "achieved_hbm_gbs": acct["read"] * world / (ms_step * 1e-3) / 1e9,
-            "bytes_read_over_dense": acct["read"] / acct["dense"],
+            "config": {"workload": WORKLOAD["name"], "batch": Bt, "query_heads": Hq, "kv_heads": H, "head_dim": D,
+                       "cache_len": L, "per_gpu_batch": B, "global_batch": tokens, "pv_kernel": v_mode,
+                       "sharding": {"replicate": "(batch, kv-head) units, no collective; every rank runs the full shape",
+                                    "batch": "batch rows split across ranks, no collective",
+                                    "sequence": "cached sequence split across ranks; one all-gather of (max, sum, "
+                                                "output) records + log-sum-exp merge"}[sharding],
+                       "step": "rewind to cache_len-1 tokens -> append the last token (flushes a 64-token block through "
+                               "the plane writers) -> decode",
+                       "l2": "inputs larger than L2 (planes %.0f MiB per GPU)" % (
+                           sum(t.numel() for t in (layer.k_first_8, layer.k_mid_4, layer.k_last_4, layer.v_first_8,
+                                                   layer.v_mid_4, layer.v_last_4)) / 2 ** 20)},
+            "effective_hbm_gbs": total["dense"] / (ms_step * 1e-3) / 1e9,
+            "achieved_hbm_gbs": total["read"] / (ms_step * 1e-3) / 1e9,
+            "bytes_read_over_dense": total["read"] / total["dense"],
             "kernels_us": {n: round(kv_["us"], 2) for n, kv_ in kern.items()},
             "roofline": roofline,
             "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": int(3 * q.numel() * 2), "d2h_bytes_per_step": int(hout.numel() * 2),
-                    "ms_per_step": ms_e2e / args.steps},
+                    "h2d_bytes_per_step": int((q.numel() + k_tok.numel() + v_tok.numel()) * 2),
+                    "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches * args.steps,
             "clocks": clocks,
         }

@@ -134,6 +134,56 @@ int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_firs
 long long akv_decode_scratch_bytes(int bsz, int n_heads, int head_dim, int max_seq_len);
 
 /*
+ * Grouped-query forms (no counterpart in the reference, which asserts multi-head attention:
+ * model/KVCache_AlignedKV.py:32, extension/k_cache_file.py:133, extension/v_cache_file.py:146).  `group` query heads
+ * share each of the n_kv_heads KV heads; query head index = KV head * group + g.  Planes, exponent maxima and
+ * residual buffers are per KV head; kq, kqmax, q, score rows, amin and outputs are per query head.  Results equal the
+ * multi-head operators run on a cache whose KV heads were repeated `group` times, while every plane byte is
+ * fetched from HBM once per group.
+ * flags: AKV_STEP_REFERENCE reads every plane; AKV_STEP_ORDER_FREE selects the P.V kernel that splits the token axis
+ * across CTAs and accumulates in fp32 (same read decisions and substitute constants, different summation order:
+ * not bit-identical to the reference's fp16 token-order chain, closer to exact arithmetic; head_dim 128 only; needs a
+ * workspace of akv_v_cache_compute_scratch_bytes() bytes); AKV_STEP_NO_APPEND (decode step only) leaves the cache
+ * untouched - the new token belongs to another shard of the sequence.
+ */
+#define AKV_STEP_REFERENCE 1
+#define AKV_STEP_ORDER_FREE 2
+#define AKV_STEP_NO_APPEND 4
+int akv_k_cache_compute_gqa(const void* k_first_8, const void* k_mid_4, const void* k_last_4,
+                            const void* kq, const void* kqmax, const void* q, void* s_out,
+                            int bsz, int n_kv_heads, int group, int n_blocks, int n_max_blocks, int d_head, int d_block,
+                            int seqlen, float sqrt_dim, int reference, void* stream);
+int akv_v_cache_compute_gqa(const void* v_first_8, const void* v_mid_4, const void* v_last_4,
+                            const void* s, const void* amin, void* o_out, void* scratch, long long scratch_bytes,
+                            int bsz, int n_kv_heads, int group, int max_seq_len, int head_dim, int s_last_dim,
+                            int start_pos_add_seqlen, int flags, void* stream);
+long long akv_v_cache_compute_scratch_bytes(int bsz, int n_kv_heads, int group, int n_tokens);
+
+/*
+ * akv_decode_step with grouped-query attention, the choice of P.V kernel, and an optional packed result for
+ * sequence-sharded caches.  q and out are [B,1,n_kv_heads*group,D]; k_new, v_new, the residual buffers and exponent
+ * maxima are per KV head.  packed_out (may be NULL): fp32 [B*Hq, D+2] rows (maximum score, sum of exponentials,
+ * output[0..D-1]) over THIS cache's tokens - what akv_lse_merge combines across shards; `out` may be NULL when only
+ * the packed result is wanted.  With AKV_STEP_NO_APPEND k_new / v_new may be NULL and rest_len / rest_start stay
+ * as they are.
+ */
+int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                       void* k_exp_max, void* v_exp_max, void* restk, void* restv,
+                       const void* q, const void* k_new, const void* v_new, void* out, void* packed_out,
+                       void* scratch, long long scratch_bytes,
+                       int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
+                       int flags, void* stream);
+long long akv_decode_scratch_bytes_ex(int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int flags);
+
+/*
+ * Log-sum-exp merge of the packed results of n_ranks shards of one sequence (no counterpart in the reference, which
+ * is single-device).  packed: fp32 [n_ranks, rows, head_dim+2] as gathered from the shards (rows = B*Hq);
+ * out: fp16 [rows, head_dim] = sum_g w_g o_g with w_g = l_g exp(m_g - M) / sum_g' l_g' exp(m_g' - M), M = max_g m_g.
+ * Shards with l = 0 (no tokens) are ignored.
+ */
+int akv_lse_merge(const void* packed, void* out, int n_ranks, int rows, int head_dim, void* stream);
+
+/*
  * akv_decode_step for callers that cannot allocate device memory (no counterpart in the reference).
  * Same arguments and results as akv_decode_step, minus the workspace: it lives in a fixed array of
  * AKV_NOALLOC_SCRATCH_BYTES bytes of device global memory inside the library image, which every GPU that loads the
@@ -158,7 +208,7 @@ int akv_decode_step_noalloc(void* k_first_8, void* k_mid_4, void* k_last_4, void
 /*
  * Benchmark instrumentation (no counterpart in the reference): with akv_set_tuning("timing", 1), akv_decode_step
  * records CUDA events around its q.K^T and P.V launches.  akv_timing_read returns how many steps were recorded
- * since akv_timing_reset and their mean launch durations in microseconds; synchronise the stream first.
+ * since akv_timing_reset and their median launch durations in microseconds; synchronise the stream first.
  */
 int akv_timing_reset(void);
 int akv_timing_read(double* k_us, double* v_us);

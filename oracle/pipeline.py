@@ -196,3 +196,92 @@ class OracleLayerCache:
         rest = 4 * (self.cache_len - qn) * D * B * H
         return {"k": float(k_bytes), "v": float(v_bytes), "rest": float(rest),
                 "dense": float(4 * B * H * self.cache_len * D)}
+
+    # ------------------------------------------------------------------ variants used by the extended entry points
+    def dequantized_v(self) -> np.ndarray:
+        """fp16 values [B,H,qn,D] the latest decode step's P.V saw: planes reassembled under its read codes with
+        the reference's substitute constants (V_cache.cu:198-202,250-253)."""
+        qn = self.rest_start
+        codes = np.asarray(self.last["v_codes"]).reshape(self.B, self.H, -1)[..., :qn]          # B,H,qn
+        f = self.v_first_8[:, :, :qn].astype(np.uint16)                                          # B,H,qn,D
+        mid = self.v_mid_4[:, :, :qn].astype(np.uint16)
+        low = self.v_last_4[:, :, :qn].astype(np.uint16)
+        c = codes[..., None]
+        mid = np.where(c < 2, mid, 0x88)
+        low = np.where(c == 0, low, np.where(c == 1, 0x88, 0x00))
+        lo_e = (mid & 0xF0) | (low >> 4)
+        lo_o = ((mid << 4) & 0xF0) | (low & 0x0F)
+        bits = np.empty(f.shape, np.uint16)
+        bits[..., 0::2] = (f[..., 0::2] << 8) | lo_e
+        bits[..., 1::2] = (f[..., 1::2] << 8) | lo_o
+        return bits.view(np.float16)
+
+    def decode_record(self, q16, k16=None, v16=None, *, append: bool = True, reference: bool = False,
+                      order_free: bool = False):
+        """One decode step returning (out fp16 [B,1,H,D], record fp32 [B*H, D+2] = (max score, sum of exponentials,
+        output)).  append=False leaves the cache untouched.  order_free: P.V as an exact sum (float64) of
+        probability x dequantized value under the same read decisions, rounded once - the arithmetic the order-free
+        kernel approximates in fp32."""
+        if append:
+            self.save(k16, v16, self.cache_len, 1)
+        s = self.scores(q16, reference)
+        p = softmax_fp32_to_half(s)
+        self.last.update(s=s, p=p)
+        x = s.astype(np.float32)[..., :self.cache_len]
+        m = x.max(axis=-1)
+        l = np.exp(x - m[..., None], dtype=np.float32).sum(axis=-1, dtype=np.float32)
+        o16 = self.output(p, reference)                                   # B,H,1,D (also fills last["v_codes"])
+        if order_free:
+            qn = self.rest_start
+            o = np.zeros((self.B, self.H, self.D), np.float64)
+            if qn:
+                vq = self.dequantized_v().astype(np.float64)              # B,H,qn,D
+                o += np.einsum("bht,bhtd->bhd", p[:, :, 0, :qn].astype(np.float64), vq)
+            pr = p[:, :, 0, qn:self.cache_len].astype(np.float64)
+            vr = self.restv[:, :self.rest_len].astype(np.float64).transpose(0, 2, 1, 3)
+            o += np.einsum("bhr,bhrd->bhd", pr, vr)
+            o32 = o.astype(np.float32)
+            o16 = o32.astype(np.float16)[:, :, None, :]
+        else:
+            o32 = o16[:, :, 0, :].astype(np.float32)
+        rec = np.concatenate([m.reshape(-1, 1), l.reshape(-1, 1), o32.reshape(-1, self.D)], axis=1).astype(np.float32)
+        return o16.reshape(self.B, 1, self.H, self.D), rec
+
+
+class OracleGQACache:
+    """Grouped-query attention through the multi-head oracle: the reference asserts MHA
+    (model/KVCache_AlignedKV.py:32), so the specification of a G-way group is the reference run on a cache whose
+    KV heads are repeated G times (HF's repeat_kv).  KV head h is expanded head h*G."""
+
+    def __init__(self, bsz: int, max_seq_len: int, kv_heads: int, group: int, head_dim: int):
+        self.G = group
+        self.inner = OracleLayerCache(bsz, max_seq_len, kv_heads * group, head_dim)
+
+    def _expand(self, x16):
+        return np.ascontiguousarray(np.repeat(x16, self.G, axis=2))
+
+    def save(self, k16, v16, start_pos, seqlen):
+        self.inner.save(self._expand(k16), self._expand(v16), start_pos, seqlen)
+
+    def decode_record(self, q16, k16=None, v16=None, **kw):
+        if k16 is not None:
+            k16, v16 = self._expand(k16), self._expand(v16)
+        return self.inner.decode_record(q16, k16, v16, **kw)
+
+    def kv_planes(self):
+        """The six planes restricted to the real KV heads (every G-th expanded head)."""
+        i = self.inner
+        return tuple(x[:, ::self.G] for x in (i.k_first_8, i.k_mid_4, i.k_last_4, i.v_first_8, i.v_mid_4, i.v_last_4))
+
+
+def lse_merge_np(packed: np.ndarray) -> np.ndarray:
+    """Merge per-shard records [R, rows, D+2] = (m, l, o) -> fp16 [rows, D]:
+    out = sum_g w_g o_g, w_g = l_g exp(m_g - M) / sum_g' l_g' exp(m_g' - M).  Shards with l = 0 are ignored."""
+    packed = np.asarray(packed, np.float64)
+    m, l, o = packed[..., 0], packed[..., 1], packed[..., 2:]
+    m = np.where(l > 0, m, -np.inf)
+    M = m.max(axis=0, keepdims=True)
+    w = np.where(l > 0, l * np.exp(m - M), 0.0)
+    den = w.sum(axis=0, keepdims=True)
+    w = np.where(den > 0, w / np.where(den > 0, den, 1.0), 0.0)
+    return np.where(w[..., None] > 0, w[..., None] * o, 0.0).sum(axis=0).astype(np.float32).astype(np.float16)
