@@ -320,7 +320,8 @@ def run_ours(args):
             a = acct[dom] / (kern[dom]["us"] * 1e-6) / 1e9
             roofline = {"bound": "hbm", "kernel": dom, "achieved": a, "peak": peak, "unit": "GB/s", "frac": a / peak,
                         "peak_source": "measured" if peaks else "fallback",
-                        "traffic": layer.NCU_TRAFFIC.get((WORKLOAD["name"], dom)), "us_per_launch": kern[dom]["us"],
+                        "traffic": layer.NCU_TRAFFIC.get((WORKLOAD["name"], dom + ("_order_free" if dom == "v_compute" and
+                                                                                    v_mode == "order_free" else ""))), "us_per_launch": kern[dom]["us"],
                         "algorithmic_bytes": acct[dom], "timing": "median of CUDA-event brackets inside the timed steps"}
         line = {
             "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
