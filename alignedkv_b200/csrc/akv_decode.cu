@@ -10,7 +10,7 @@
 //   probe       akv_v_compute.cu, then the threshold byte per (batch, head) with the reference's [B,H,H,D] broadcast
 //   P.V         akv_v_compute.cu
 //   tail        adds the residual tokens' contribution
-#include "akv_common.cuh"
+#include "akv_save.cuh"
 
 namespace akv {
 
@@ -74,45 +74,82 @@ static size_t carve(Scratch* sc, uint8_t* base, int B, int H, int G, int D, int 
     return off;
 }
 
-// ------------------------------------------------------------------ append
-// grid B*H (KV heads), block D/2.  Thread c handles channels 2c, 2c+1.  With append == 0 nothing is stored (the
-// token belongs to another shard of the sequence) and only the alignment inputs of the G query heads are built.
-__global__ void __launch_bounds__(512)
-append_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, uint16_t* __restrict__ k_exp,
-              uint16_t* __restrict__ v_exp, const uint32_t* __restrict__ q, const uint32_t* __restrict__ k_new,
-              const uint32_t* __restrict__ v_new, uint16_t* __restrict__ kq, uint8_t* __restrict__ kqmax, int H, int G,
-              int D, int rest_len, int append) {
-    __shared__ uint32_t red[16];
-    const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
-    const int c = threadIdx.x, hd = D >> 1;
-    const size_t row = (size_t)bh * hd + c;                                  // [B,1,H,D] in words
-    auto exps = [](uint32_t w) { return ((w >> 10) & 0x1Fu) | (((w >> 26) & 0x1Fu) << 8); };   // two exponent bytes
-    uint32_t ke2 = k_exp[row];
-    if (append) {
-        const size_t rrow = (((size_t)b * BLK + rest_len) * H + h) * hd + c;     // [B,64,H,D] in words
-        const uint32_t kw = k_new[row], vw = v_new[row];
-        restk[rrow] = kw;
-        restv[rrow] = vw;
-        // running per-channel maxima of the exponent fields (k_cache_file.py:98-99, v_cache_file.py:98-99)
-        ke2 = __vmaxu4(ke2, exps(kw)) & 0xFFFFu;
-        k_exp[row] = (uint16_t)ke2;
-        v_exp[row] = (uint16_t)(__vmaxu4(v_exp[row], exps(vw)) & 0xFFFFu);
-    }
-    // exponent upper bound of every product q_d * k_{t,d} and its maximum over channels (k_cache_file.py:136-138)
-    for (int g = 0; g < G; ++g) {
-        const size_t qrow = ((size_t)bh * G + g) * hd + c;
-        const uint32_t kq2 = __vadd4(exps(q[qrow]), ke2) & 0xFFFFu;
-        kq[qrow] = (uint16_t)kq2;
-        uint32_t m = max(kq2 & 0xFFu, kq2 >> 8);
+// ------------------------------------------------------------------ append (+ block flush)
+// One launch, three roles by block index (128 threads each):
+//   [0, BH)            append: residual buffers, per-channel exponent maxima, alignment inputs kq / kqmax of the G
+//                      query heads.  With append == 0 nothing is stored (the token belongs to another shard of the
+//                      sequence) and only the alignment inputs are built.
+//   [BH, 2BH)          (flush only) K block writer: the 63 buffered tokens plus the new one -> planes, block qn/64
+//   [2BH, 2BH+BH*D/64) (flush only) V row writer for the same 64 tokens
+// The writers take token 63 straight from k_new / v_new, so they do not depend on the append role's stores.
+__global__ void __launch_bounds__(128)
+append_flush_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, uint16_t* __restrict__ k_exp,
+                    uint16_t* __restrict__ v_exp, const uint32_t* __restrict__ q, const uint32_t* __restrict__ k_new,
+                    const uint32_t* __restrict__ v_new, uint16_t* __restrict__ kq, uint8_t* __restrict__ kqmax,
+                    uint8_t* __restrict__ k_first_8, uint8_t* __restrict__ k_mid_4, uint8_t* __restrict__ k_last_4,
+                    uint8_t* __restrict__ v_first_8, uint8_t* __restrict__ v_mid_4, uint8_t* __restrict__ v_last_4,
+                    int B, int H, int G, int D, int rest_len, int append, int nmb, int max_seq_len, int qn) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ uint32_t red[4];
+    const int BH = B * H, hd = D >> 1;
+    if ((int)blockIdx.x < BH) {
+        const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
+        auto exps = [](uint32_t w) { return ((w >> 10) & 0x1Fu) | (((w >> 26) & 0x1Fu) << 8); };  // two exponent bytes
+        for (int g = -1; g < G; ++g) {
+            // g == -1: store the token and update the maxima; g >= 0: alignment inputs of query head g
+            uint32_t m = 0;
+            for (int c = threadIdx.x; c < hd; c += blockDim.x) {
+                const size_t row = (size_t)bh * hd + c;                              // [B,1,H,D] in words
+                if (g < 0) {
+                    if (append) {
+                        const size_t rrow = (((size_t)b * BLK + rest_len) * H + h) * hd + c;   // [B,64,H,D] in words
+                        const uint32_t kw = k_new[row], vw = v_new[row];
+                        restk[rrow] = kw;
+                        restv[rrow] = vw;
+                        // running per-channel maxima of the exponent fields (k_cache_file.py:98-99, v_cache_file.py:98-99)
+                        k_exp[row] = (uint16_t)(__vmaxu4(k_exp[row], exps(kw)) & 0xFFFFu);
+                        v_exp[row] = (uint16_t)(__vmaxu4(v_exp[row], exps(vw)) & 0xFFFFu);
+                    }
+                } else {
+                    // exponent upper bound of every product q_d * k_{t,d} (k_cache_file.py:136-138); this thread
+                    // wrote k_exp[row] itself
+                    const size_t qrow = ((size_t)bh * G + g) * hd + c;
+                    const uint32_t kq2 = __vadd4(exps(q[qrow]), k_exp[row]) & 0xFFFFu;
+                    kq[qrow] = (uint16_t)kq2;
+                    m = max(m, max(kq2 & 0xFFu, kq2 >> 8));
+                }
+            }
+            if (g < 0) continue;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-        __syncthreads();
-        if ((c & 31) == 0) red[c >> 5] = m;
-        __syncthreads();
-        if (c == 0) {
-            for (int w = 1; w < (hd + 31) / 32; ++w) m = max(m, red[w]);
-            kqmax[(size_t)bh * G + g] = (uint8_t)m;
+            for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+            __syncthreads();
+            if (threadIdx.x == 0) kqmax[(size_t)bh * G + g] = (uint8_t)max(max(red[0], red[1]), max(red[2], red[3]));
         }
+        return;
+    }
+    if ((int)blockIdx.x < 2 * BH) {
+        const int bh = blockIdx.x - BH, b = bh / H, h = bh - b * H;
+        const uint8_t* rk = reinterpret_cast<const uint8_t*>(restk);
+        const uint8_t* kn = reinterpret_cast<const uint8_t*>(k_new);
+        auto row = [&](int t) {
+            return t < BLK - 1 ? rk + 2 * ((((size_t)b * BLK + t) * H + h) * (size_t)D) : kn + 2 * ((size_t)bh * D);
+        };
+        k_write_block64(smem, k_first_8, k_mid_4, k_last_4, row, (long long)bh * nmb + qn / BLK, D);
+        return;
+    }
+    {
+        const int per_tok = D >> 5, per_bh = BLK * per_tok;              // 32-channel pieces per token / per (b,h)
+        const int i = (blockIdx.x - 2 * BH) * blockDim.x + threadIdx.x;   // grid covers BH * per_bh items exactly
+        const int bh = i / per_bh, r = i - bh * per_bh, t = r / per_tok, c = r - t * per_tok;
+        const int b = bh / H, h = bh - b * H;
+        const uint8_t* src = t < BLK - 1
+            ? reinterpret_cast<const uint8_t*>(restv) + 2 * ((((size_t)b * BLK + t) * H + h) * (size_t)D + c * 32)
+            : reinterpret_cast<const uint8_t*>(v_new) + 2 * ((size_t)bh * D + c * 32);
+        const size_t prow = (size_t)bh * max_seq_len + qn + t;
+        v_write32(reinterpret_cast<const uint4*>(src), v_first_8 + prow * D + c * 32, v_mid_4 + prow * hd + c * 16,
+                  v_last_4 + prow * hd + c * 16);
     }
 }
 
@@ -348,22 +385,34 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
     const int nmb = (max_seq_len + BLK - 1) / BLK;
     int rc;
 
-    append_kernel<<<B * H, D / 2, 0, st>>>(static_cast<uint32_t*>(restk), static_cast<uint32_t*>(restv),
-                                          static_cast<uint16_t*>(k_exp_max), static_cast<uint16_t*>(v_exp_max),
-                                          static_cast<const uint32_t*>(q), static_cast<const uint32_t*>(k_new),
-                                          static_cast<const uint32_t*>(v_new), reinterpret_cast<uint16_t*>(sc.kq),
-                                          sc.kqmax, H, G, D, rest_len, append ? 1 : 0);
-    if ((rc = cuda_status(cudaGetLastError(), "decode_step append launch")) != AKV_OK) return rc;
     int rest = rest_len + (append ? 1 : 0), qn = rest_start;
-    if (rest == BLK) {   // the buffered block goes to the planes (k_cache_file.py:102-118, v_cache_file.py:103-116)
-        rc = launch_k_save(static_cast<uint8_t*>(k_first_8), static_cast<uint8_t*>(k_mid_4),
-                           static_cast<uint8_t*>(k_last_4), static_cast<const uint8_t*>(restk), B, H, 1, nmb, D, BLK, qn,
-                           BLK, st);
-        if (rc != AKV_OK) return rc;
-        rc = launch_v_save(static_cast<uint8_t*>(v_first_8), static_cast<uint8_t*>(v_mid_4),
-                           static_cast<uint8_t*>(v_last_4), static_cast<const uint8_t*>(restv), B, H, max_seq_len, D, qn,
-                           BLK, BLK, st);
-        if (rc != AKV_OK) return rc;
+    const bool flush = rest == BLK;
+    // append and (when the residual buffer fills up) the flush of the block to the planes
+    // (k_cache_file.py:102-118, v_cache_file.py:103-116): one launch when the block tile fits in default shared memory
+    const bool fused_flush = flush && D <= 256 && aligned16(k_first_8) && aligned16(k_mid_4) && aligned16(k_last_4) &&
+                             aligned16(v_first_8) && aligned16(v_mid_4) && aligned16(v_last_4);
+    {
+        const int blocks = fused_flush ? B * H * (2 + D / 64) : B * H;
+        append_flush_kernel<<<blocks, 128, fused_flush ? (size_t)BLK * 2 * D : 0, st>>>(
+            static_cast<uint32_t*>(restk), static_cast<uint32_t*>(restv), static_cast<uint16_t*>(k_exp_max),
+            static_cast<uint16_t*>(v_exp_max), static_cast<const uint32_t*>(q), static_cast<const uint32_t*>(k_new),
+            static_cast<const uint32_t*>(v_new), reinterpret_cast<uint16_t*>(sc.kq), sc.kqmax,
+            static_cast<uint8_t*>(k_first_8), static_cast<uint8_t*>(k_mid_4), static_cast<uint8_t*>(k_last_4),
+            static_cast<uint8_t*>(v_first_8), static_cast<uint8_t*>(v_mid_4), static_cast<uint8_t*>(v_last_4), B, H, G, D,
+            rest_len, append ? 1 : 0, nmb, max_seq_len, qn);
+        if ((rc = cuda_status(cudaGetLastError(), "decode_step append launch")) != AKV_OK) return rc;
+    }
+    if (flush) {
+        if (!fused_flush) {
+            rc = launch_k_save(static_cast<uint8_t*>(k_first_8), static_cast<uint8_t*>(k_mid_4),
+                               static_cast<uint8_t*>(k_last_4), static_cast<const uint8_t*>(restk), B, H, 1, nmb, D, BLK,
+                               qn, BLK, st);
+            if (rc != AKV_OK) return rc;
+            rc = launch_v_save(static_cast<uint8_t*>(v_first_8), static_cast<uint8_t*>(v_mid_4),
+                               static_cast<uint8_t*>(v_last_4), static_cast<const uint8_t*>(restv), B, H, max_seq_len, D,
+                               qn, BLK, BLK, st);
+            if (rc != AKV_OK) return rc;
+        }
         qn += BLK;
         rest = 0;
     }

@@ -3,28 +3,13 @@
 // Replaces the reference's k_cache_save_prefill_kernel / k_cache_save_decoding_kernel
 // (extension/csrc/K_cache.cu:19-94) and v_cache_save_kernel (extension/csrc/V_cache.cu:17-41) with writers that
 // produce the same bytes using 128-bit loads and stores wherever the layout allows it.
-#include "akv_common.cuh"
+#include "akv_save.cuh"
 
 namespace akv {
 
 // ================================================================== V
 // One thread turns 32 consecutive channels of one token (64 input bytes) into 32 high bytes, 16 mid bytes and
-// 16 low bytes: two 16-byte stores into first_8, one each into mid_4 and last_4.
-
-__device__ __forceinline__ void v_split4(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3,  // 8 channels
-                                         uint32_t& hi01, uint32_t& hi23, uint32_t& mid, uint32_t& last) {
-    // word = [lo_even, hi_even, lo_odd, hi_odd]
-    hi01 = __byte_perm(w0, w1, 0x7531);
-    hi23 = __byte_perm(w2, w3, 0x7531);
-    uint32_t x01 = __byte_perm(w0, w1, 0x6420);  // [lo_e0, lo_o0, lo_e1, lo_o1]
-    uint32_t x23 = __byte_perm(w2, w3, 0x6420);
-    uint32_t m01 = (x01 & 0x00F000F0u) | ((x01 >> 12) & 0x000F000Fu);  // bytes 0 and 2 hold the pair bytes
-    uint32_t m23 = (x23 & 0x00F000F0u) | ((x23 >> 12) & 0x000F000Fu);
-    uint32_t l01 = ((x01 << 4) & 0x00F000F0u) | ((x01 >> 8) & 0x000F000Fu);
-    uint32_t l23 = ((x23 << 4) & 0x00F000F0u) | ((x23 >> 8) & 0x000F000Fu);
-    mid = __byte_perm(m01, m23, 0x6420);
-    last = __byte_perm(l01, l23, 0x6420);
-}
+// 16 low bytes: two 16-byte stores into first_8, one each into mid_4 and last_4 (v_write32, akv_save.cuh).
 
 __global__ void __launch_bounds__(256)
 v_save_vec_kernel(uint8_t* __restrict__ first8, uint8_t* __restrict__ mid4, uint8_t* __restrict__ last4,
@@ -41,18 +26,8 @@ v_save_vec_kernel(uint8_t* __restrict__ first8, uint8_t* __restrict__ mid4, uint
         long long b = bh / H;
         const uint4* src = reinterpret_cast<const uint4*>(
             v_new + 2 * (((b * v_new_tokens + p) * H + h) * (long long)D + c * 32));
-        uint4 a0 = __ldg(src), a1 = __ldg(src + 1), a2 = __ldg(src + 2), a3 = __ldg(src + 3);
-        uint4 f0, f1, m, l;
-        v_split4(a0.x, a0.y, a0.z, a0.w, f0.x, f0.y, m.x, l.x);
-        v_split4(a1.x, a1.y, a1.z, a1.w, f0.z, f0.w, m.y, l.y);
-        v_split4(a2.x, a2.y, a2.z, a2.w, f1.x, f1.y, m.z, l.z);
-        v_split4(a3.x, a3.y, a3.z, a3.w, f1.z, f1.w, m.w, l.w);
         long long row = (bh * max_seq_len + (start_pos + p));
-        uint4* fdst = reinterpret_cast<uint4*>(first8 + row * D + c * 32);
-        fdst[0] = f0;
-        fdst[1] = f1;
-        *reinterpret_cast<uint4*>(mid4 + row * (D >> 1) + c * 16) = m;
-        *reinterpret_cast<uint4*>(last4 + row * (D >> 1) + c * 16) = l;
+        v_write32(src, first8 + row * D + c * 32, mid4 + row * (D >> 1) + c * 16, last4 + row * (D >> 1) + c * 16);
     }
 }
 
@@ -96,10 +71,7 @@ int launch_v_save(uint8_t* first8, uint8_t* mid4, uint8_t* last4, const uint8_t*
 }
 
 // ================================================================== K
-// Block writer, 64-token blocks: one CTA per (batch, head, block).  The 64 x D fp16 tile is staged in shared
-// memory token-major (as it arrives), then thread d gathers channel d of all 64 tokens and emits one 64-byte
-// first_8 row and one 32-byte row of each nibble plane with 16-byte accesses.  Nibble rows are read-add-written
-// (bytewise, mod 256) so that the result equals the reference's `+=` on any prior plane contents.
+// Block writer, 64-token blocks: one CTA per (batch, head, block); body in akv_save.cuh (k_write_block64).
 
 template <int DB>  // DB = 64
 __global__ void __launch_bounds__(256)
@@ -108,60 +80,9 @@ k_save_block64_kernel(uint8_t* __restrict__ first8, uint8_t* __restrict__ mid4, 
     extern __shared__ __align__(16) uint8_t smem[];  // [64][D] halves, row pitch 2*D bytes
     const int z = blockIdx.x, h = blockIdx.y;
     const long long b = blockIdx.z;
-    const int pitch = 2 * D;
-    // stage: 64 rows of 2*D bytes, 16 bytes per access
-    const int vec_per_row = pitch >> 4;
-    for (int i = threadIdx.x; i < DB * vec_per_row; i += blockDim.x) {
-        int t = i / vec_per_row, v = i - t * vec_per_row;
-        const uint4* src = reinterpret_cast<const uint4*>(
-            k_new + 2 * (((b * seqlen + (long long)z * DB + t) * H + h) * (long long)D) + v * 16);
-        *reinterpret_cast<uint4*>(smem + t * pitch + v * 16) = __ldg(src);
-    }
-    __syncthreads();
     const long long tile = ((b * H + h) * n_max_blocks + (z + blk0));
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        uint32_t f[16], m[8], l[8];
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {  // 8 tokens per group
-            uint32_t hi[8], lo[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                uint32_t x = *reinterpret_cast<const uint16_t*>(smem + (g * 8 + j) * pitch + 2 * d);
-                hi[j] = x >> 8;
-                lo[j] = x & 0xFFu;
-            }
-            f[2 * g] = hi[0] | (hi[1] << 8) | (hi[2] << 16) | (hi[3] << 24);
-            f[2 * g + 1] = hi[4] | (hi[5] << 8) | (hi[6] << 16) | (hi[7] << 24);
-            uint32_t mw = 0, lw = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {  // token pair (2j, 2j+1) -> one byte, even token in the high nibble
-                uint32_t e = lo[2 * j], o = lo[2 * j + 1];
-                mw |= ((e & 0xF0u) | (o >> 4)) << (8 * j);
-                lw |= (((e & 0x0Fu) << 4) | (o & 0x0Fu)) << (8 * j);
-            }
-            m[g] = mw;
-            l[g] = lw;
-        }
-        uint4* fdst = reinterpret_cast<uint4*>(first8 + (tile * D + d) * DB);
-#pragma unroll
-        for (int v = 0; v < 4; ++v) fdst[v] = make_uint4(f[4 * v], f[4 * v + 1], f[4 * v + 2], f[4 * v + 3]);
-        uint4* mdst = reinterpret_cast<uint4*>(mid4 + (tile * D + d) * (DB / 2));
-        uint4* ldst = reinterpret_cast<uint4*>(last4 + (tile * D + d) * (DB / 2));
-#pragma unroll
-        for (int v = 0; v < 2; ++v) {
-            uint4 om = mdst[v], ol = ldst[v];
-            om.x = __vadd4(om.x, m[4 * v]);
-            om.y = __vadd4(om.y, m[4 * v + 1]);
-            om.z = __vadd4(om.z, m[4 * v + 2]);
-            om.w = __vadd4(om.w, m[4 * v + 3]);
-            ol.x = __vadd4(ol.x, l[4 * v]);
-            ol.y = __vadd4(ol.y, l[4 * v + 1]);
-            ol.z = __vadd4(ol.z, l[4 * v + 2]);
-            ol.w = __vadd4(ol.w, l[4 * v + 3]);
-            mdst[v] = om;
-            ldst[v] = ol;
-        }
-    }
+    auto row = [&](int t) { return k_new + 2 * (((b * seqlen + (long long)z * DB + t) * H + h) * (long long)D); };
+    k_write_block64(smem, first8, mid4, last4, row, tile, D);
 }
 
 // Any block length / partial blocks: one thread per (batch, head, block, channel) row, tokens in order.

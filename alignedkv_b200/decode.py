@@ -131,9 +131,9 @@ class DecodeLayer:
         qn = self.rest_start + (column_block if flush else 0)
         rest = 0 if flush else self.rest_len + (1 if append else 0)
         tail = rest > 0 or qn == 0 or packed or self.v_mode == "order_free"
-        # kernels of this library launched by the call: append, (2 flush), q.K^T, softmax, probe, threshold, P.V
-        # (2 for the order-free form), tail
-        self.launches += 1 + (2 if flush else 0) + (1 if qn else 0) + 1 + \
+        # kernels of this library launched by the call: append (+ flush in the same launch; 2 more launches when the
+        # head is too wide for that), q.K^T, softmax, probe, threshold, P.V (2 for the order-free form), tail
+        self.launches += 1 + (2 if flush and D > 256 else 0) + (1 if qn else 0) + 1 + \
             ((3 + (1 if self.v_mode == "order_free" else 0)) if qn else 0) + (1 if tail else 0)
         self.rest_len, self.rest_start = rest, qn
         if append:
