@@ -6,20 +6,26 @@
 // constants (V_cache.cu:198-202,250-253).
 //
 // Design (B200): the exact token order leaves only B*Hq*D/2 independent chains - two warps per (batch, query head)
-// - and a dependent fp16 FMA issues every ~4 cycles, so the kernel is organised around keeping those warps'
-// instruction stream at one FMA plus its operand fetch per token and never letting them wait for memory.
+// - and a dependent fp16 FMA issues every ~4 cycles while every shared-memory load a warp issues costs it several
+// more, so the kernel is organised around handing the chain warps operands they can take with few, wide loads.
 // One CTA per (batch, KV head); the G query heads of a grouped-query group share the CTA and the bytes it streams.
-//   chain warps (2 per query head; thread c owns channels 2c, 2c+1): tokens are handled in runs of 32.  While the
-//     32 dependent FMAs of one run execute, the operands of the next run are fetched from shared memory into
-//     registers in the FMAs' shadow (software pipelining across runs and across stages).  A run in which no token
-//     of this head reads a nibble plane ("lean") costs one 2-byte load and one byte permute per token.
-//   loader warps (64 threads; thread t owns token t of every 64-token stage): take each head's probability of the
-//     token from a buffer that is copied 16 stages ahead, decide from its bit pattern which of the token's 64-byte
-//     nibble rows are needed (V_cache.cu:211,250-251), and start the copies: ONE bulk asynchronous copy
-//     (cp.async.bulk, the TMA unit) for the stage's 8 KB of high bytes, and 64-byte bulk copies for just the
-//     needed nibble rows into a small side ring.  All copies complete on the stage's mbarrier by byte count, so a
-//     loader never waits for data, only for a free slot.
-// Every wait is a bounded spin; a wait that gives up raises a flag the host can read (akv_device_error_flag).
+//   producer warps (4: two pairs, pair p serves the 64-token stages j = p, p+2, ...; each warp of a pair serves one
+//     run of 32 tokens of the stage).  (1) issue - thread = token: it takes each head's probability of the token from
+//     a buffer bulk-copied 16 stages ahead, decides from its bit pattern which of the token's 64-byte nibble rows
+//     are needed (V_cache.cu:211,250-251), and starts the copies: ONE bulk asynchronous copy (cp.async.bulk, the
+//     TMA unit) for the stage's 8 KB of high bytes and 64-byte bulk copies of just the needed nibble rows into a
+//     small side ring, all byte-counted on the stage's mbarrier; a few stages per pair are kept in flight.
+//     (2) transform - once a stage has landed, the same warps transpose it into the "ready" ring as
+//     [channel pair][token] 16-bit words (8x8 tiles, 16-byte accesses both ways, swizzled so that neither side has
+//     bank conflicts) and - only for a run in which some token of a head reads a nibble plane - that head's
+//     low-byte words, built from the side ring with the reference's substitutes (mid 0x88 / low 0x00 when neither
+//     plane is read, low 0x88 when only mid is read).
+//   chain warps (2 per query head; thread c owns channels 2c, 2c+1): per run of 32 tokens four 16-byte loads of
+//     high words, eight of probability words, (four of low words when the run is not lean, else the constant 0x80
+//     bytes), then per token one byte permute and one FMA.  The next run's loads and permutes are written between
+//     the FMAs of the current one (software pipelining across runs and stages), so the chain sees ready operands.
+//     A run has two code paths (lean / not lean), chosen once per run; there is no per-token branch.
+// Every wait is time-bounded; a wait that gives up raises a flag the host can read (akv_device_error_flag).
 #include "akv_common.cuh"
 
 namespace akv {
@@ -62,8 +68,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity) {
     unsigned long long t0 = 0;
     for (int spin = 0; spin < (1 << 24); ++spin) {
         uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        // the hint lets the hardware park the warp (no issue slots taken from the chain warps that share its SM
+        // sub-partition) until the phase completes or the time (ns) runs out
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(a), "r"(parity), "r"(20000u) : "memory");
         if (ok) return true;
         if ((spin & 63) == 63) {
             unsigned long long t;
@@ -83,137 +91,133 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
 }
 
 // Shared-memory plan of one CTA.
-//   F ring     NS stages of 64 tokens x D high bytes, one bulk copy each
-//   s2 ring    per stage and query head: 64 probability words (the fp16 value in both halves)
-//   records    per stage and run of 32 tokens: {side slot or -1, union mid mask, union low mask, -} and per query
-//              head {mid mask, low mask}: bit u set = token u of the run reads that plane for that head
-//   side ring  per loader warp NML slots of [32 tokens x D/2 mid bytes][32 tokens x D/2 low bytes]; only the rows
-//              in the union masks are filled
-//   s chunks   three buffers of G x 16 stages x 64 probabilities.  Chunk c+1 is requested by one thread when it
-//              enters chunk c and lands in buffer (c+1) % 3, last read during chunk c-2; the other loader warp is
-//              in chunk c-1 or later because the ring (NS <= 16 stages) is shorter than a chunk.
-//   barriers   full / empty per stage, free per side-ring slot, landed per probability buffer
-template <int D, int G, int NS, int NML>
+//   F ring      NF stages of 64 tokens x D high bytes as they lie in the plane, one bulk copy each
+//   pending     per F slot: per run {side slot or -1, union mid mask, union low mask, -} and per query head
+//               {mid mask, low mask} (bit u set = token u of the run reads that plane for that head), and per head
+//               the 64 probability words (the fp16 value in both halves) the chain warps read
+//   side ring   per producer warp NML slots of [32 tokens x D/2 mid bytes][32 tokens x D/2 low bytes]; only the rows
+//               in the union masks are filled
+//   ready ring  NR slots of: high words [64 pairs][64 tokens] (2 bytes each, 16-byte chunks swizzled) and per head
+//               low words in the same layout (written only for runs that are not lean)
+//   s chunks    three buffers of G x 16 stages x 64 probabilities.  Chunk c+1 is requested when the first producer
+//               warp's issue side enters chunk c and lands in buffer (c+1) % 3, last read (by issue sides only)
+//               during chunk c-2; the producer warps' issue positions are less than 16 stages apart.
+//   barriers    landed per F slot, ready / free per ready slot, landed per probability buffer
+// Stage j uses F slot j % NF and ready slot j % NR; NF and NR are even, so each producer pair owns every other slot.
+template <int D, int G, int NF, int NR, int NML>
 struct VPlan {
     static constexpr int TOK = vc::TOK;
     static constexpr int HD = D / 2;
     static constexpr int F_BYTES = TOK * D;
-    static constexpr int S2_OFF = NS * F_BYTES;
-    static constexpr int S2_BYTES = G * TOK * 4;
-    static constexpr int REC_OFF = S2_OFF + NS * S2_BYTES;
-    static constexpr int REC_BYTES = (16 + G * 8 + 15) & ~15;
-    static constexpr int ML_OFF = (REC_OFF + NS * 2 * REC_BYTES + 127) & ~127;
+    static constexpr int PEND_OFF = NF * F_BYTES;
+    static constexpr int REC_BYTES = (16 + G * 8 + 15) & ~15;                  // one run's record
+    static constexpr int P_S2 = 2 * REC_BYTES;                                 // offsets inside a pending area
+    static constexpr int PEND_BYTES = P_S2 + G * TOK * 4;
+    static constexpr int ML_OFF = (PEND_OFF + NF * PEND_BYTES + 127) & ~127;
     static constexpr int ML_BYTES = vc::RUN * HD * 2;
-    static constexpr int SB_OFF = ML_OFF + 2 * NML * ML_BYTES;
-    static constexpr int SB_HEAD = vc::SCH * TOK * 2;          // bytes of one head's chunk
-    static constexpr int SB_BYTES = G * SB_HEAD;               // one buffer
+    static constexpr int RDY_OFF = ML_OFF + 4 * NML * ML_BYTES;
+    static constexpr int W_BYTES = HD * TOK * 2;                               // one [pair][token] array of 16-bit words
+    static constexpr int R_LO = W_BYTES;                                       // offset inside a ready slot
+    static constexpr int RDY_BYTES = (1 + G) * W_BYTES;
+    static constexpr int SB_OFF = RDY_OFF + NR * RDY_BYTES;
+    static constexpr int SB_HEAD = vc::SCH * TOK * 2;                          // bytes of one head's chunk
+    static constexpr int SB_BYTES = G * SB_HEAD;                               // one buffer
     static constexpr int BAR_OFF = SB_OFF + 3 * SB_BYTES;
-    static constexpr int BYTES = BAR_OFF + (2 * NS + 2 * NML + 3) * 8;
+    static constexpr int BYTES = BAR_OFF + (NF + 2 * NR + 3) * 8;
+    // Stages of one pair in flight beyond the one it transforms.  The pair's stage j + 2*AHEADP lands in the F slot
+    // of stage j - NR - 2.  A warp reaches iteration j only after the chain released stage j - 2 - NR (it waited
+    // for that to reuse the ready slot for stage j - 2), which also means both warps of the pair had published it:
+    // nobody reads that F slot, its records or its probability words any more.
+    static constexpr int AHEADP = NF / 2 - NR / 2 - 1;
+    static_assert(NF % 2 == 0 && NR % 2 == 0 && AHEADP >= 1 && NF + NR + 4 < vc::SCH, "ring sizes");
+    static_assert(PEND_BYTES % 16 == 0, "alignment");
 };
 
-// One run of 32 tokens of the chain, with the next run's operand fetch written between the dependent FMAs so that
-// the loads issue in the FMAs' latency shadow (they run AKV_V_PD tokens ahead of the FMA they are written next to).
-// KC / SC: operands of the current run (k~ words [lo_even, f_even, lo_odd, f_odd], probability words); KN / SN
-// receive the next run's.
-//   AKV_V_RUN_NONE  nothing to fetch (last run)
-//   AKV_V_RUN_LEAN  the next run's low bytes are the constant 0x80 (no nibble plane read)
-//   AKV_V_RUN_FULL  nibble bytes come from the side ring where the head's masks say so, else the reference's
-//                   substitutes (mid 0x88 / low 0x00 when neither plane is read, low 0x88 when only mid is read)
-//   AKV_V_PATCH     after a lean fetch: rebuild the few tokens whose mask bit is set (cheaper than a full fetch when
-//                   only one or two tokens of the run read a nibble plane, the common case)
-#define AKV_V_PD 8
-#define AKV_V_S(S_, v_, w_) ((w_) == 0 ? S_[v_].x : (w_) == 1 ? S_[v_].y : (w_) == 2 ? S_[v_].z : S_[v_].w)
-#define AKV_V_RUN_NONE(KC_, SC_)                                                         \
-    _Pragma("unroll") for (int v_ = 0; v_ < 8; ++v_) {                                   \
-        _Pragma("unroll") for (int w_ = 0; w_ < 4; ++w_)                                 \
-            acc = hfma2_bits(KC_[4 * v_ + w_], AKV_V_S(SC_, v_, w_), acc);               \
-    }
-#define AKV_V_RUN_LEAN(KC_, SC_, KN_, SN_, fa_, sa_)                                     \
-    {                                                                                    \
-        uint32_t raw_[32];                                                               \
-        _Pragma("unroll") for (int v_ = 0; v_ < 8; ++v_) SN_[v_] = lds128((sa_) + v_ * 16); \
-        _Pragma("unroll") for (int u_ = 0; u_ < AKV_V_PD; ++u_) raw_[u_] = lds16((fa_) + u_ * D); \
-        _Pragma("unroll") for (int v_ = 0; v_ < 8; ++v_) {                               \
-            _Pragma("unroll") for (int w_ = 0; w_ < 4; ++w_) {                           \
-                const int u_ = 4 * v_ + w_;                                              \
-                if (u_ + AKV_V_PD < 32) raw_[u_ + AKV_V_PD] = lds16((fa_) + (u_ + AKV_V_PD) * D); \
-                acc = hfma2_bits(KC_[u_], AKV_V_S(SC_, v_, w_), acc);                    \
-                KN_[u_] = __byte_perm(raw_[u_], 0x80u, 0x1404);                          \
-            }                                                                            \
-        }                                                                                \
-    }
-#define AKV_V_ASSEMBLE(f_, mb_, lb_) \
-    __byte_perm((f_), (((mb_) & 0xF0u) | ((lb_) >> 4)) | (((((mb_) << 4) & 0xF0u) | ((lb_) & 0x0Fu)) << 8), 0x1504)
-#define AKV_V_RUN_FULL(KC_, SC_, KN_, SN_, fa_, sa_, mla_, mm_, lm_)                     \
-    _Pragma("unroll") for (int v_ = 0; v_ < 8; ++v_) {                                   \
-        SN_[v_] = lds128((sa_) + v_ * 16);                                               \
-        _Pragma("unroll") for (int w_ = 0; w_ < 4; ++w_) {                               \
-            const int u_ = 4 * v_ + w_;                                                  \
-            acc = hfma2_bits(KC_[u_], AKV_V_S(SC_, v_, w_), acc);                        \
-            const uint32_t f_ = lds16((fa_) + u_ * D);                                   \
-            uint32_t mb_ = lds8((mla_) + u_ * HD), lb_ = lds8((mla_) + (32 + u_) * HD);  \
-            const bool m_ = ((mm_) >> u_) & 1u, l_ = ((lm_) >> u_) & 1u;                 \
-            mb_ = m_ ? mb_ : 0x88u;                                                      \
-            lb_ = l_ ? lb_ : (m_ ? 0x88u : 0x00u);                                       \
-            KN_[u_] = AKV_V_ASSEMBLE(f_, mb_, lb_);                                      \
-        }                                                                                \
-    }
-#define AKV_V_PATCH(KN_, fa_, mla_, mm_, lm_)                                            \
-    for (uint32_t rem_ = (mm_); rem_; rem_ &= rem_ - 1) {                                \
-        const int t_ = __ffs((int)rem_) - 1;                                             \
-        const uint32_t f_ = lds16((fa_) + t_ * D);                                       \
-        const uint32_t mb_ = lds8((mla_) + t_ * HD);                                     \
-        uint32_t lb_ = lds8((mla_) + (32 + t_) * HD);                                    \
-        lb_ = (((lm_) >> t_) & 1u) ? lb_ : 0x88u;                                        \
-        const uint32_t w_ = AKV_V_ASSEMBLE(f_, mb_, lb_);                                \
-        _Pragma("unroll") for (int u_ = 0; u_ < 32; ++u_) KN_[u_] = (u_ == t_) ? w_ : KN_[u_]; \
-    }
-// Run over KC/SC while fetching run `half_` of the stage in `slot_` into KN/SN; the run's record is (ms_, hm_).
-#define AKV_V_STEP(KC_, SC_, KN_, SN_, slot_, half_, ms_, hm_)                                                       \
-    {                                                                                                                \
-        const uint32_t fa_ = base + (uint32_t)(slot_) * P::F_BYTES + (uint32_t)(half_) * (vc::RUN * D) + c * 2;      \
-        const uint32_t sa_ = base + P::S2_OFF + (uint32_t)(slot_) * P::S2_BYTES + (uint32_t)(g * TOK + (half_) * vc::RUN) * 4; \
-        const uint32_t mla_ = base + P::ML_OFF + (uint32_t)((half_) * NML + ((ms_) < 0 ? 0 : (ms_))) * P::ML_BYTES + c; \
-        if (__popc((hm_).x) <= 3) {                                                                                  \
-            AKV_V_RUN_LEAN(KC_, SC_, KN_, SN_, fa_, sa_)                                                             \
-            AKV_V_PATCH(KN_, fa_, mla_, (hm_).x, (hm_).y)                                                            \
-        } else {                                                                                                     \
-            AKV_V_RUN_FULL(KC_, SC_, KN_, SN_, fa_, sa_, mla_, (hm_).x, (hm_).y)                                     \
-        }                                                                                                            \
-    }
-// Records of both runs of the stage in `slot_`: side slots and this head's {mid mask, low mask}.
-#define AKV_V_RECORDS(slot_, msa_, hma_, msb_, hmb_)                                                  \
-    {                                                                                                 \
-        const uint32_t ra_ = base + P::REC_OFF + (uint32_t)((slot_) * 2) * P::REC_BYTES;              \
-        msa_ = (int)lds32(ra_);                                                                       \
-        hma_ = lds64(ra_ + 16 + g * 8);                                                               \
-        msb_ = (int)lds32(ra_ + P::REC_BYTES);                                                        \
-        hmb_ = lds64(ra_ + P::REC_BYTES + 16 + g * 8);                                                \
-    }
+// 16-byte chunk k (tokens 8k..8k+7) of pair c's row in a [pair][token] array: swizzled so that a quarter-warp of
+// consecutive pairs reading one chunk, and a quarter-warp of pair groups writing one pair, each hit 8 bank groups.
+__device__ __forceinline__ uint32_t v_chunk(int c, int k) {
+    return (uint32_t)c * 128u + (uint32_t)(((k ^ (c >> 3) ^ c) & 7) << 4);
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint32_t u4w(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-template <int D, int G, int NS, int NML>
-__global__ void __launch_bounds__(64 * G + 64) v_compute_kernel(const VParams p) {
-    using P = VPlan<D, G, NS, NML>;
+// 8 tokens x 8 pairs tile: R[j] = four words of token j (word i = pairs 2i, 2i+1, two bytes each) -> for pair q the
+// 16 bytes of its 8 tokens, stored at the pair's swizzled chunk.  dst = array base; c0 = first pair, k = chunk index.
+__device__ __forceinline__ void v_store_transposed(const uint4 (&R)[8], uint32_t dst, int c0, int k) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const uint32_t sel = (q & 1) ? 0x7632u : 0x5410u;
+        uint32_t o[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m)   // [pair q of token 2m, pair q of token 2m+1]
+            o[m] = __byte_perm(u4w(R[2 * m], q >> 1), u4w(R[2 * m + 1], q >> 1), sel);
+        sts128(dst + v_chunk(c0 + q, k), o[0], o[1], o[2], o[3]);
+    }
+}
+
+// One run of 32 tokens of the chain.  KC / SC: the current run's k~ words [lo_even, f_even, lo_odd, f_odd] and
+// probability words.  KN / SN receive the next run's: its 16-byte loads are written between the first sixteen FMAs and
+// the byte permutes that build k~ between the last sixteen, so that all of it issues in the FMAs' latency shadow and
+// the next run starts with operands that are ready.  FETCH == false: last run, nothing to load.
+template <bool FETCH, bool LEAN>
+__device__ __forceinline__ void v_run_impl(uint32_t& acc, const uint32_t (&KC)[32], const uint4 (&SC)[8],
+                                           uint32_t (&KN)[32], uint4 (&SN)[8], uint32_t hi_a, uint32_t lo_a, uint32_t s_a,
+                                           int c, int k0) {
+    uint4 H[4], L[4];
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {          // 4 tokens per step
+        if (FETCH) {
+            SN[v] = lds128(s_a + v * 16);
+            if (v < 4) {
+                H[v] = lds128(hi_a + v_chunk(c, k0 + v));
+                L[v] = LEAN ? make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u)
+                            : lds128(lo_a + v_chunk(c, k0 + v));
+            } else {
+                const int i = v - 4;       // chunk i: word m holds tokens 8i+2m, 8i+2m+1
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    KN[8 * i + 2 * m] = __byte_perm(u4w(H[i], m), u4w(L[i], m), 0x1504);
+                    KN[8 * i + 2 * m + 1] = __byte_perm(u4w(H[i], m), u4w(L[i], m), 0x3726);
+                }
+            }
+        }
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc = hfma2_bits(KC[4 * v + w], u4w(SC[v], w), acc);
+    }
+}
+
+template <bool FETCH>
+__device__ __forceinline__ void v_run(uint32_t& acc, const uint32_t (&KC)[32], const uint4 (&SC)[8], uint32_t (&KN)[32],
+                                      uint4 (&SN)[8], uint32_t hi_a, uint32_t lo_a, uint32_t s_a, int c, int k0,
+                                      uint32_t not_lean) {
+    if (!FETCH || not_lean == 0) v_run_impl<FETCH, true>(acc, KC, SC, KN, SN, hi_a, lo_a, s_a, c, k0);   // (warp-uniform)
+    else v_run_impl<FETCH, false>(acc, KC, SC, KN, SN, hi_a, lo_a, s_a, c, k0);
+}
+
+template <int D, int G, int NF, int NR, int NML>
+__global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p) {
+    using P = VPlan<D, G, NF, NR, NML>;
     constexpr int TOK = P::TOK;
     constexpr int NCH = 64 * G;                    // chain threads
     constexpr int HD = P::HD;                      // nibble row bytes
     static_assert(D == 128, "thread c of a head's two chain warps owns channels 2c, 2c+1");
-    static_assert(NS <= vc::SCH, "the probability buffers are recycled assuming the ring is shorter than a chunk");
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x;
     const long long bh = blockIdx.x;               // (batch, KV head)
     const int n = p.n;
     const int nst = (n + TOK - 1) / TOK;
     const uint32_t base = smem_u32(smem);
-    const uint32_t bar_full = base + P::BAR_OFF, bar_empty = bar_full + NS * 8, bar_ml = bar_empty + NS * 8;
-    const uint32_t bar_sb = bar_ml + 2 * NML * 8;
+    const uint32_t bar_full = base + P::BAR_OFF, bar_ready = bar_full + NF * 8, bar_free = bar_ready + NR * 8;
+    const uint32_t bar_sb = bar_free + NR * 8;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) {
-            mbar_init(bar_full + s * 8, 2);          // one arrival per loader warp (+ the bytes they announce)
-            mbar_init(bar_empty + s * 8, 2 * G);     // one arrival per chain warp
+        for (int s = 0; s < NF; ++s) mbar_init(bar_full + s * 8, 2);   // one arrival per warp of the pair (+ bytes)
+        for (int s = 0; s < NR; ++s) {
+            mbar_init(bar_ready + s * 8, 2);         // one arrival per warp of the pair
+            mbar_init(bar_free + s * 8, 2 * G);      // one arrival per chain warp
         }
-        for (int s = 0; s < 2 * NML; ++s) mbar_init(bar_ml + s * 8, 2 * G);
         for (int s = 0; s < 3; ++s) mbar_init(bar_sb + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -230,70 +234,71 @@ __global__ void __launch_bounds__(64 * G + 64) v_compute_kernel(const VParams p)
         for (int u = 0; u < 32; ++u) kA[u] = kB[u] = 0;
 #pragma unroll
         for (int v = 0; v < 8; ++v) sA[v] = sB[v] = make_uint4(0, 0, 0, 0);
-        int slot = 0;              // slot of the stage whose first run is in kA / sA
+        int rs = 0, fs = 0;        // ready slot and F slot of the stage whose first run is in the A registers
         uint32_t phase = 0;
         bool alive = true;
-        int ms0 = -1, ms1 = -1, msn0 = -1, msn1 = -1;      // side slots of this stage's / the next stage's runs
-        uint2 hm0 = make_uint2(0, 0), hm1 = hm0, hmn0 = hm0, hmn1 = hm0;
+        auto rdy = [&](int r) { return base + P::RDY_OFF + (uint32_t)r * P::RDY_BYTES; };
+        auto pend = [&](int f) { return base + P::PEND_OFF + (uint32_t)f * P::PEND_BYTES; };
+        // "not lean" flag (this head's mid mask) of run `half` of the stage in F slot f
+        auto flag = [&](int f, int half) { return lds32(pend(f) + half * P::REC_BYTES + 16 + g * 8); };
+        uint32_t fl1 = 0;          // "not lean" flag of the second run of the stage in the A registers
         if (nsf > 0) {
-            alive = mbar_wait(bar_full, 0);
-            if (alive) {
-                AKV_V_RECORDS(0, ms0, hm0, ms1, hm1)
-                AKV_V_STEP(kB, sB, kA, sA, 0, 0, ms0, hm0)     // (a chain over zeros) fetch run 0 of stage 0
+            alive = mbar_wait(bar_ready, 0);
+            if (alive) {   // (a chain over zeros) fetch run 0 of stage 0
+                fl1 = flag(0, 1);
+                v_run<true>(acc, kB, sB, kA, sA, rdy(0), rdy(0) + P::R_LO + g * P::W_BYTES,
+                            pend(0) + P::P_S2 + g * TOK * 4, c, 0, flag(0, 0));
             }
         }
         for (int j = 0; j < nsf && alive; ++j) {
-            // the next stage is looked at a run early, so that its records are in registers when they are needed
-            const int nslot = slot + 1 == NS ? 0 : slot + 1;
-            const uint32_t nphase = slot + 1 == NS ? phase ^ 1 : phase;
+            const int nrs = rs + 1 == NR ? 0 : rs + 1, nfs = fs + 1 == NF ? 0 : fs + 1;
+            const uint32_t nphase = rs + 1 == NR ? phase ^ 1 : phase;
             const bool more = j + 1 < nsf;
+            // the next stage is looked at a run early, so that its flags are in registers when they are needed
+            uint32_t nflag = 0, nfl1 = 0;
             if (more) {
-                alive = mbar_wait(bar_full + nslot * 8, nphase);
+                alive = mbar_wait(bar_ready + nrs * 8, nphase);
                 if (!alive) break;
-                AKV_V_RECORDS(nslot, msn0, hmn0, msn1, hmn1)
+                nflag = flag(nfs, 0);
+                nfl1 = flag(nfs, 1);
             }
             // first run of stage j while its second run is fetched
-            AKV_V_STEP(kA, sA, kB, sB, slot, 1, ms1, hm1)
-            // both runs of the stage are in registers: hand the slot and its side-ring slots back
+            v_run<true>(acc, kA, sA, kB, sB, rdy(rs), rdy(rs) + P::R_LO + g * P::W_BYTES,
+                        pend(fs) + P::P_S2 + (g * TOK + vc::RUN) * 4, c, 4, fl1);
+            // both runs of the stage are in registers: hand the ready slot (and with it the F slot's records and
+            // probability words) back
             __syncwarp();
-            if (lane == 0) {
-                if (ms0 >= 0) mbar_arrive(bar_ml + (0 * NML + ms0) * 8);
-                if (ms1 >= 0) mbar_arrive(bar_ml + (1 * NML + ms1) * 8);
-                mbar_arrive(bar_empty + slot * 8);
-            }
+            if (lane == 0) mbar_arrive(bar_free + rs * 8);
             // second run of stage j while the first run of stage j+1 is fetched
-            if (more) {
-                AKV_V_STEP(kB, sB, kA, sA, nslot, 0, msn0, hmn0)
-            } else {
-                AKV_V_RUN_NONE(kB, sB)
-            }
-            slot = nslot; phase = nphase;
-            ms0 = msn0; hm0 = hmn0; ms1 = msn1; hm1 = hmn1;
+            if (more)
+                v_run<true>(acc, kB, sB, kA, sA, rdy(nrs), rdy(nrs) + P::R_LO + g * P::W_BYTES,
+                            pend(nfs) + P::P_S2 + g * TOK * 4, c, 0, nflag);
+            else
+                v_run<false>(acc, kB, sB, kA, sA, 0, 0, 0, c, 0, 0);
+            rs = nrs; fs = nfs; phase = nphase;
+            fl1 = nfl1;
         }
         if (tail > 0 && alive) {
-            // last, partial stage: token by token straight from shared memory
-            alive = mbar_wait(bar_full + slot * 8, phase);
-            for (int t = 0; t < tail && alive; ++t) {
-                const int half = t >> 5, u = t & 31;
-                const uint32_t ra = base + P::REC_OFF + (uint32_t)(slot * 2 + half) * P::REC_BYTES;
-                const int ms = (int)lds32(ra);
-                const uint2 hm = lds64(ra + 16 + g * 8);
-                uint32_t k = __byte_perm(lds16(base + (uint32_t)slot * P::F_BYTES + t * D + c * 2), 0x80u, 0x1404);
-                if ((hm.x >> u) & 1u) {
-                    const uint32_t mla = base + P::ML_OFF + (uint32_t)(half * NML + ms) * P::ML_BYTES + c;
-                    const uint32_t mb = lds8(mla + u * HD);
-                    const uint32_t lb = ((hm.y >> u) & 1u) ? lds8(mla + (32 + u) * HD) : 0x88u;
-                    k = AKV_V_ASSEMBLE(lds16(base + (uint32_t)slot * P::F_BYTES + t * D + c * 2), mb, lb);
+            // last, partial stage: token by token from the ready slot
+            alive = mbar_wait(bar_ready + rs * 8, phase);
+            if (alive) {
+                const uint32_t r = rdy(rs);
+                const uint32_t f0 = flag(fs, 0), f1 = flag(fs, 1);
+                for (int t = 0; t < tail; ++t) {
+                    const uint32_t off = v_chunk(c, t >> 3) + (t & 7) * 2;
+                    const uint32_t hw = lds16(r + off);
+                    const uint32_t lw = ((t < vc::RUN) ? f0 : f1) ? lds16(r + P::R_LO + g * P::W_BYTES + off) : 0x8080u;
+                    acc = hfma2_bits(__byte_perm(hw, lw, 0x1504), lds32(pend(fs) + P::P_S2 + (g * TOK + t) * 4), acc);
                 }
-                acc = hfma2_bits(k, lds32(base + P::S2_OFF + (uint32_t)slot * P::S2_BYTES + (g * TOK + t) * 4), acc);
             }
         }
         if (alive) reinterpret_cast<uint32_t*>(p.o)[((size_t)bh * G + g) * 64 + c] = acc;
         return;
     }
 
-    // ---------------------------------------------------------------------- loader warps
-    const int pt = tid - NCH, lane = pt & 31, pw = pt >> 5;
+    // ---------------------------------------------------------------------- producer warps
+    const int pt = tid - NCH, lane = pt & 31, pw = pt >> 5, pair = pw >> 1, half = pw & 1;
+    const int tok = half * vc::RUN + lane;         // this thread's token of every stage of its pair
     const uint8_t* F = p.first8 + (size_t)bh * p.max_seq_len * D;
     const uint8_t* M = p.mid4 + (size_t)bh * p.max_seq_len * HD;
     const uint8_t* L = p.last4 + (size_t)bh * p.max_seq_len * HD;
@@ -314,72 +319,132 @@ __global__ void __launch_bounds__(64 * G + 64) v_compute_kernel(const VParams p)
             bulk_copy(base + P::SB_OFF + (uint32_t)(c % 3) * P::SB_BYTES + g * P::SB_HEAD,
                       s_rows + (size_t)g * p.s_last_dim + t0, bytes, bar);
     };
-    int slot = 0, ml_used = 0;          // stage slot; side-ring slots this warp has handed out so far
-    uint32_t phase = 0;
     bool alive = true;
+    int iss = pair;                     // next stage of this pair to issue
+    int ml_alloc = 0, ml_freed = 0;     // side-ring slots this warp has handed out / taken back
+    int last_chunk = -1;                // probability chunk the issue side has entered
     if (pt == 0 && nst > 0) request_s(0);
 
-    for (int j = 0; j < nst && alive; ++j) {
-        if (j >= NS) alive = mbar_wait(bar_empty + slot * 8, phase ^ 1);   // stage j-NS has been consumed
-        const int t0 = j * TOK;
+    // ---- issue: decisions and copies of stage i (this warp's run of it); false when it has to wait for a side slot
+    auto issue = [&](int i) -> bool {
+        const int fs = i % NF;
+        const int t0 = i * TOK;
         const int cnt = (n - t0) < TOK ? (n - t0) : TOK;
-        const int c = j / vc::SCH, js = j - c * vc::SCH;
-        if (js == 0) {   // entering chunk c: ask for the next one, make sure this one has landed
+        const int c = i / vc::SCH;
+        if (c > last_chunk) {   // entering chunk c (once, even if this stage is retried): ask for the next one, make
+            last_chunk = c;     // sure this one has landed
             if (pt == 0 && (c + 1) * vc::SCH < nst) request_s(c + 1);
             alive = alive && mbar_wait(bar_sb + (c % 3) * 8, (uint32_t)(c / 3) & 1u);
+            if (!alive) return true;
         }
-        if (!alive) break;
         // decisions from the bit patterns (V_cache.cu:211,250-251): 16-bit wrap-around, signed compare
-        uint32_t mm[G], lm[G];
+        const uint32_t sbase = base + P::SB_OFF + (uint32_t)(c % 3) * P::SB_BYTES + (i - c * vc::SCH) * (TOK * 2) + tok * 2;
+        uint32_t mm[G], lm[G], sb[G];
         int ucode = 2;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const uint32_t sb = (pt < cnt) ? lds16(base + P::SB_OFF + (uint32_t)(c % 3) * P::SB_BYTES + g * P::SB_HEAD +
-                                                   js * (TOK * 2) + pt * 2) : 0u;
-            const int diff = (int)(int16_t)(uint16_t)(A[g] - sb);
+            sb[g] = (tok < cnt) ? lds16(sbase + g * P::SB_HEAD) : 0u;
+            const int diff = (int)(int16_t)(uint16_t)(A[g] - sb[g]);
             int code = p.reference ? 0 : (diff >= 0x0800 ? 2 : (diff >= 0x0400 ? 1 : 0));
-            if (pt >= cnt) code = 2;
+            if (tok >= cnt) code = 2;
             mm[g] = __ballot_sync(0xFFFFFFFFu, code < 2);
             lm[g] = __ballot_sync(0xFFFFFFFFu, code == 0);
             ucode = code < ucode ? code : ucode;
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(base + P::S2_OFF + (uint32_t)slot * P::S2_BYTES + (g * TOK + pt) * 4),
-                         "r"(sb | (sb << 16)) : "memory");
         }
         const uint32_t umm = __ballot_sync(0xFFFFFFFFu, ucode < 2), ulm = __ballot_sync(0xFFFFFFFFu, ucode == 0);
         int ms = -1;
-        uint32_t bytes = (pw == 0) ? (uint32_t)cnt * D : 0u;
+        uint32_t bytes = (half == 0) ? (uint32_t)cnt * D : 0u;
         if (umm) {
-            // the rows some head reads go to a slot of this warp's side ring
-            ms = ml_used % NML;
-            if (ml_used >= NML) alive = mbar_wait(bar_ml + (pw * NML + ms) * 8, ((ml_used / NML) & 1) ^ 1);
-            ++ml_used;
+            // the rows some head reads go to a slot of this warp's side ring (freed by this warp's own transform)
+            if (ml_alloc - ml_freed == NML) return false;
+            ms = ml_alloc % NML;
+            ++ml_alloc;
             bytes += (uint32_t)HD * (__popc(umm) + __popc(ulm));
         }
-        const uint32_t bar = bar_full + slot * 8;
+        const uint32_t bar = bar_full + fs * 8;
+        const uint32_t pa = base + P::PEND_OFF + (uint32_t)fs * P::PEND_BYTES;
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(pa + P::P_S2 + (g * TOK + tok) * 4), "r"(sb[g] | (sb[g] << 16)) : "memory");
         if (lane == 0) {
-            const uint32_t ra = base + P::REC_OFF + (uint32_t)(slot * 2 + pw) * P::REC_BYTES;
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(ra), "r"(ms), "r"(umm), "r"(ulm), "r"(0) : "memory");
+            const uint32_t ra = pa + half * P::REC_BYTES;
+            sts128(ra, (uint32_t)ms, umm, ulm, 0u);
 #pragma unroll
             for (int g = 0; g < G; ++g)
                 asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(ra + 16 + g * 8), "r"(mm[g]), "r"(lm[g]) : "memory");
         }
         __syncwarp();
-        if (!alive) break;
         if (lane == 0) {
             if (bytes) mbar_arrive_expect(bar, bytes);   // publishes this warp's stores, announces its copies
             else mbar_arrive(bar);
         }
-        if (pt == 0) bulk_copy(base + (uint32_t)slot * P::F_BYTES, F + (size_t)t0 * D, (uint32_t)cnt * D, bar);
+        if (half == 0 && lane == 0) bulk_copy(base + (uint32_t)fs * P::F_BYTES, F + (size_t)t0 * D, (uint32_t)cnt * D, bar);
         if (umm) {
             const uint32_t dm = base + P::ML_OFF + (uint32_t)(pw * NML + ms) * P::ML_BYTES;
-            const size_t src = (size_t)(t0 + pw * vc::RUN) * HD;
+            const size_t src = (size_t)(t0 + half * vc::RUN) * HD;
             // a run that reads a plane for all 32 tokens takes it as one 2 KB copy, otherwise row by row
             if (umm == 0xFFFFFFFFu) { if (lane == 0) bulk_copy(dm, M + src, vc::RUN * HD, bar); }
             else if (ucode < 2) bulk_copy(dm + lane * HD, M + src + (size_t)lane * HD, HD, bar);
             if (ulm == 0xFFFFFFFFu) { if (lane == 0) bulk_copy(dm + vc::RUN * HD, L + src, vc::RUN * HD, bar); }
             else if (ucode == 0) bulk_copy(dm + (vc::RUN + lane) * HD, L + src + (size_t)lane * HD, HD, bar);
         }
-        if (++slot == NS) { slot = 0; phase ^= 1; }
+        return true;
+    };
+
+    const int tg = 4 * half + (lane >> 3), pg = lane & 7;      // this lane's 8-token x 8-pair tile of every stage
+    for (int j = pair; j < nst && alive; j += 2) {
+        // keep AHEADP stages of this pair in flight beyond the one transformed now
+        while (alive && iss < nst && iss <= j + 2 * P::AHEADP) {
+            if (!issue(iss)) break;
+            iss += 2;
+        }
+        if (!alive) break;
+        const int fs = j % NF, rs = j % NR;
+        alive = mbar_wait(bar_full + fs * 8, (uint32_t)(j / NF) & 1u);                       // the stage has landed
+        if (alive && j >= NR) alive = mbar_wait(bar_free + rs * 8, (uint32_t)(j / NR - 1) & 1u);   // slot consumed
+        if (!alive) break;
+        const uint32_t fa = base + (uint32_t)fs * P::F_BYTES, r = base + P::RDY_OFF + (uint32_t)rs * P::RDY_BYTES;
+        const uint32_t ra = base + P::PEND_OFF + (uint32_t)fs * P::PEND_BYTES + half * P::REC_BYTES;
+        // high bytes: transpose this lane's tile
+        {
+            uint4 R[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) R[t] = lds128(fa + (8 * tg + t) * D + pg * 16);
+            v_store_transposed(R, r, 8 * pg, tg);
+        }
+        // low bytes, only for the heads that read a nibble plane in this warp's run
+        const uint32_t umm = lds32(ra + 4);
+        if (umm) {
+            const int ms = (int)lds32(ra);
+            const uint32_t mla = base + P::ML_OFF + (uint32_t)(pw * NML + ms) * P::ML_BYTES;
+            const int u0 = 8 * (lane >> 3);                       // first token of the tile inside the run
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const uint2 hm = lds64(ra + 16 + g * 8);
+                if (hm.x == 0) continue;                          // (warp-uniform)
+                uint4 R[8];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    uint2 mb = lds64(mla + (u0 + t) * HD + pg * 8);
+                    uint2 lb = lds64(mla + (vc::RUN + u0 + t) * HD + pg * 8);
+                    const bool m = (hm.x >> (u0 + t)) & 1u, l = (hm.y >> (u0 + t)) & 1u;
+                    if (!m) mb = make_uint2(0x88888888u, 0x88888888u);
+                    if (!l) lb = m ? make_uint2(0x88888888u, 0x88888888u) : make_uint2(0u, 0u);
+                    const uint32_t le0 = (mb.x & 0xF0F0F0F0u) | ((lb.x >> 4) & 0x0F0F0F0Fu);   // even channels, pairs 0-3
+                    const uint32_t le1 = (mb.y & 0xF0F0F0F0u) | ((lb.y >> 4) & 0x0F0F0F0Fu);   //                pairs 4-7
+                    const uint32_t lo0 = ((mb.x << 4) & 0xF0F0F0F0u) | (lb.x & 0x0F0F0F0Fu);   // odd channels
+                    const uint32_t lo1 = ((mb.y << 4) & 0xF0F0F0F0u) | (lb.y & 0x0F0F0F0Fu);
+                    R[t].x = __byte_perm(le0, lo0, 0x5140);       // pairs 0,1: [even, odd, even, odd]
+                    R[t].y = __byte_perm(le0, lo0, 0x7362);       // pairs 2,3
+                    R[t].z = __byte_perm(le1, lo1, 0x5140);
+                    R[t].w = __byte_perm(le1, lo1, 0x7362);
+                }
+                v_store_transposed(R, r + P::R_LO + g * P::W_BYTES, 8 * pg, tg);
+            }
+            ++ml_freed;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ready + rs * 8);
     }
     if (!alive) {
         // a wait gave up (never expected): give the copies already in flight time to land before the CTA's shared
@@ -419,19 +484,19 @@ v_compute_generic_kernel(const VParams p, int bhq_count) {
     }
 }
 
-template <int G, int NS, int NML>
+template <int G, int NF, int NR, int NML>
 static int launch_v_fast(const VParams& p, int BH, cudaStream_t st) {
-    using K = VPlan<128, G, NS, NML>;
+    using K = VPlan<128, G, NF, NR, NML>;
     static bool configured[64] = {false};   // the attribute is per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(v_compute_kernel<128, G, NS, NML>,
+        cudaError_t e = cudaFuncSetAttribute(v_compute_kernel<128, G, NF, NR, NML>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)K::BYTES);
         if (e != cudaSuccess) return cuda_status(e, "v_cache_compute smem attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    v_compute_kernel<128, G, NS, NML><<<BH, 64 * G + 64, K::BYTES, st>>>(p);
+    v_compute_kernel<128, G, NF, NR, NML><<<BH, 64 * G + 128, K::BYTES, st>>>(p);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
 }
 
@@ -451,9 +516,9 @@ int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     const bool fast = D == 128 && aligned16(first8) && aligned16(mid4) && aligned16(last4) &&
                       (n == 0 || (aligned16(s) && s_last_dim % 8 == 0 && ((n + 7) & ~7) <= s_last_dim)) &&
                       ((reinterpret_cast<uintptr_t>(o) & 3u) == 0);
-    if (fast && group == 1) return launch_v_fast<1, 10, 2>(p, BH, st);
-    if (fast && group == 2) return launch_v_fast<2, 10, 2>(p, BH, st);
-    if (fast && group == 4) return launch_v_fast<4, 8, 2>(p, BH, st);
+    if (fast && group == 1) return launch_v_fast<1, 6, 2, 1>(p, BH, st);
+    if (fast && group == 2) return launch_v_fast<2, 6, 2, 2>(p, BH, st);
+    if (fast && group == 4) return launch_v_fast<4, 6, 2, 2>(p, BH, st);
     long long total = (long long)BH * group * (D >> 1);
     long long want = (total + 127) / 128;
     int grid = (int)(want < (long long)sm_count() * 16 ? want : (long long)sm_count() * 16);
