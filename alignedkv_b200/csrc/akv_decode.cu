@@ -29,6 +29,7 @@ int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int
 int launch_lse_merge(const float*, uint8_t*, int, int, int, cudaStream_t);
 
 constexpr int TOPK = 32;     // residue classes of the magnitude probe (extension/v_cache_file.py:16)
+constexpr int SM_CHUNK = 4096;   // scores per CTA of the split softmax
 constexpr int BLK = 64;      // tokens per K block (extension/k_cache_file.py:5-6)
 
 // Workspace of one decode step.  H = KV heads, Hq = query heads.
@@ -44,6 +45,9 @@ struct Scratch {
     float* stats;        // [B*Hq,2] maximum score and sum of exponentials of the softmax
     float* o_main32;     // [B,Hq,D] fp32 result of the order-free P.V kernel
     float* partial;      // chunk partials of the order-free P.V kernel
+    float* cstat;        // [B*Hq, chunks, 2] chunk statistics of the split softmax
+    uint32_t* cand_val;  // [B*Hq, chunks, 32] residue-class candidates of the split softmax
+    int32_t* cand_idx;
 };
 
 static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -63,6 +67,10 @@ static size_t carve(Scratch* sc, uint8_t* base, int B, int H, int G, int D, int 
     p = take(Q);                if (sc) sc->amin = p;
     p = take(Q * D * 2);        if (sc) sc->o_main = reinterpret_cast<uint16_t*>(p);
     p = take(Q * 2 * 4);        if (sc) sc->stats = reinterpret_cast<float*>(p);
+    const size_t chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
+    p = take(Q * chunks * 2 * 4);       if (sc) sc->cstat = reinterpret_cast<float*>(p);
+    p = take(Q * chunks * TOPK * 4);    if (sc) sc->cand_val = reinterpret_cast<uint32_t*>(p);
+    p = take(Q * chunks * TOPK * 4);    if (sc) sc->cand_idx = reinterpret_cast<int32_t*>(p);
     if (order_free) {
         p = take(Q * D * 4);    if (sc) sc->o_main32 = reinterpret_cast<float*>(p);
         p = take((size_t)v_split_scratch_bytes(B, H, G, max_seq_len));
@@ -229,6 +237,127 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
         }
         pval[(size_t)bhq * TOPK + tid] = (uint16_t)bv;
         pidx[(size_t)bhq * TOPK + tid] = bi;
+    }
+}
+
+// ------------------------------------------------------------------ softmax over long rows, split across CTAs
+// With few (batch, head) rows and a long sequence one CTA per row cannot keep up, so the row is cut into chunks of
+// SM_CHUNK scores: (1) per chunk the maximum and the sum of exponentials relative to it (the chunk that holds the
+// residual tokens computes their scores first), (2) every chunk CTA combines the chunk statistics into the row's
+// (max, sum), writes its probabilities and its candidates for the 32 residue classes, (3) one small CTA per row
+// reduces the candidates (largest probability, then first position) and stores the row statistics.
+__global__ void __launch_bounds__(256)
+softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
+                           float* __restrict__ cstat, int H, int G, int D, int R, int qn, int rest, float sqrt_d,
+                           int chunks) {
+    __shared__ float redf[8];
+    const int bhq = blockIdx.y, ch = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint16_t* row = s + (size_t)bhq * R;
+    const int len = qn + rest;
+    const int t0 = ch * SM_CHUNK, t1 = min(len, t0 + SM_CHUNK);
+    // residual-token scores (k_cache_file.py:156-157) by the chunk(s) that hold them
+    for (int r = warp; r < rest; r += 8) {
+        if (qn + r < t0 || qn + r >= t1) continue;
+        const __half* kr = restk + (((size_t)b * BLK + r) * H + h) * D;
+        const __half* qr = q + (size_t)bhq * D;
+        float acc = 0.f;
+        for (int d = lane; d < D; d += 32) acc += __half2float(qr[d]) * __half2float(kr[d]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (lane == 0) row[qn + r] = __half_as_ushort(__float2half_rn(__half2float(__float2half_rn(acc)) / sqrt_d));
+    }
+    __syncthreads();
+    float m = -INFINITY;
+    for (int t = t0 + tid; t < t1; t += 256) m = fmaxf(m, __half2float(__ushort_as_half(row[t])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane == 0) redf[warp] = m;
+    __syncthreads();
+    m = redf[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, redf[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int t = t0 + tid; t < t1; t += 256) sum += expf(__half2float(__ushort_as_half(row[t])) - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if (lane == 0) redf[warp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sum += redf[w];
+        cstat[((size_t)bhq * chunks + ch) * 2] = m;            // -inf for an empty chunk
+        cstat[((size_t)bhq * chunks + ch) * 2 + 1] = sum;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ cstat, uint32_t* __restrict__ cand_val,
+                           int32_t* __restrict__ cand_idx, int R, int qn, int len, int chunks) {
+    __shared__ uint32_t cand_v[256];
+    __shared__ int32_t cand_i[256];
+    const int bhq = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
+    uint16_t* row = s + (size_t)bhq * R;
+    // row statistics from the chunk statistics, in chunk order (every CTA of the row computes the same values)
+    float m = -INFINITY;
+    for (int c = 0; c < chunks; ++c) m = fmaxf(m, cstat[((size_t)bhq * chunks + c) * 2]);
+    float sum = 0.f;
+    for (int c = 0; c < chunks; ++c) {
+        const float mc = cstat[((size_t)bhq * chunks + c) * 2];
+        if (mc > -INFINITY) sum += cstat[((size_t)bhq * chunks + c) * 2 + 1] * expf(mc - m);
+    }
+    const int t0 = ch * SM_CHUNK, t1 = min(R, t0 + SM_CHUNK);
+    uint32_t best = 0;
+    int32_t best_g = 0;
+    for (int t = t0 + tid; t < t1; t += 256) {     // (t0 and 256 are multiples of 32: a thread keeps its class)
+        uint16_t pb = 0;
+        if (t < len) pb = __half_as_ushort(__float2half_rn(expf(__half2float(__ushort_as_half(row[t])) - m) / sum));
+        row[t] = pb;
+        if (t < qn && pb > best) {
+            best = pb;
+            best_g = t >> 5;
+        }
+    }
+    cand_v[tid] = best;
+    cand_i[tid] = best_g;
+    __syncthreads();
+    if (tid < TOPK) {
+        uint32_t bv = cand_v[tid];
+        int32_t bi = cand_i[tid];
+        for (int w = 1; w < 8; ++w) {
+            const uint32_t v = cand_v[tid + 32 * w];
+            const int32_t i = cand_i[tid + 32 * w];
+            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        }
+        cand_val[((size_t)bhq * chunks + ch) * TOPK + tid] = bv;
+        cand_idx[((size_t)bhq * chunks + ch) * TOPK + tid] = bi;
+    }
+}
+
+__global__ void __launch_bounds__(32)
+softmax_class_reduce_kernel(const float* __restrict__ cstat, const uint32_t* __restrict__ cand_val,
+                            const int32_t* __restrict__ cand_idx, uint16_t* __restrict__ pval,
+                            int32_t* __restrict__ pidx, float* __restrict__ stats, int chunks) {
+    const int bhq = blockIdx.x, tid = threadIdx.x;
+    uint32_t bv = 0;
+    int32_t bi = 0;
+    for (int c = 0; c < chunks; ++c) {      // chunks are in position order: a later chunk wins only when larger
+        const uint32_t v = cand_val[((size_t)bhq * chunks + c) * TOPK + tid];
+        if (v > bv) { bv = v; bi = cand_idx[((size_t)bhq * chunks + c) * TOPK + tid]; }
+    }
+    pval[(size_t)bhq * TOPK + tid] = (uint16_t)bv;
+    pidx[(size_t)bhq * TOPK + tid] = bi;
+    if (tid == 0) {
+        float m = -INFINITY, sum = 0.f;
+        for (int c = 0; c < chunks; ++c) m = fmaxf(m, cstat[((size_t)bhq * chunks + c) * 2]);
+        for (int c = 0; c < chunks; ++c) {
+            const float mc = cstat[((size_t)bhq * chunks + c) * 2];
+            if (mc > -INFINITY) sum += cstat[((size_t)bhq * chunks + c) * 2 + 1] * expf(mc - m);
+        }
+        stats[(size_t)bhq * 2] = m;
+        stats[(size_t)bhq * 2 + 1] = sum;
     }
 }
 
@@ -428,8 +557,21 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
         if (ev) cudaEventRecord(ev[1], st);
         if (rc != AKV_OK) return rc;
     }
-    softmax_kernel<<<B * H * G, 256, 0, st>>>(sc.s, static_cast<const __half*>(q), static_cast<const __half*>(restk),
-                                             sc.pval, sc.pidx, sc.stats, H, G, D, R, qn, rest, sqrtf((float)D));
+    // one CTA per row while there are enough rows to fill the GPU or the rows are short; else the split form
+    const int sm_chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
+    if (sm_chunks >= 2 && B * H * G < 2 * sm_count()) {
+        dim3 grid(sm_chunks, B * H * G);
+        softmax_chunk_stats_kernel<<<grid, 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
+                                                        static_cast<const __half*>(restk), sc.cstat, H, G, D, R, qn, rest,
+                                                        sqrtf((float)D), sm_chunks);
+        softmax_chunk_write_kernel<<<grid, 256, 0, st>>>(sc.s, sc.cstat, sc.cand_val, sc.cand_idx, R, qn, qn + rest,
+                                                        sm_chunks);
+        softmax_class_reduce_kernel<<<B * H * G, 32, 0, st>>>(sc.cstat, sc.cand_val, sc.cand_idx, sc.pval, sc.pidx,
+                                                             sc.stats, sm_chunks);
+    } else {
+        softmax_kernel<<<B * H * G, 256, 0, st>>>(sc.s, static_cast<const __half*>(q), static_cast<const __half*>(restk),
+                                                 sc.pval, sc.pidx, sc.stats, H, G, D, R, qn, rest, sqrtf((float)D));
+    }
     if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
     const bool need_tail = rest > 0 || qn == 0 || packed_out != nullptr || order_free;
     if (qn > 0) {

@@ -72,6 +72,7 @@ class DecodeLayer:
         if nbytes < 0:
             raise ValueError("bad extents")
         self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.launches = 0
 
     def _flags(self, append: bool = True) -> int:
@@ -133,7 +134,9 @@ class DecodeLayer:
         tail = rest > 0 or qn == 0 or packed or self.v_mode == "order_free"
         # kernels of this library launched by the call: append (+ flush in the same launch; 2 more launches when the
         # head is too wide for that), q.K^T, softmax, probe, threshold, P.V (2 for the order-free form), tail
-        self.launches += 1 + (2 if flush and D > 256 else 0) + (1 if qn else 0) + 1 + \
+        R = (qn // column_block + 1) * column_block
+        split_softmax = R > 4096 and B * Hq < 2 * self._sm_count     # rows cut into 4096-score chunks: 3 launches
+        self.launches += 1 + (2 if flush and D > 256 else 0) + (1 if qn else 0) + (3 if split_softmax else 1) + \
             ((3 + (1 if self.v_mode == "order_free" else 0)) if qn else 0) + (1 if tail else 0)
         self.rest_len, self.rest_start = rest, qn
         if append:
