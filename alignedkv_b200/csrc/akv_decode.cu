@@ -156,7 +156,7 @@ append_flush_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, 
             ? reinterpret_cast<const uint8_t*>(restv) + 2 * ((((size_t)b * BLK + t) * H + h) * (size_t)D + c * 32)
             : reinterpret_cast<const uint8_t*>(v_new) + 2 * ((size_t)bh * D + c * 32);
         const size_t prow = (size_t)bh * max_seq_len + qn + t;
-        v_write32(reinterpret_cast<const uint4*>(src), v_first_8 + prow * D + c * 32, v_mid_4 + prow * hd + c * 16,
+        v_write32_global(reinterpret_cast<const uint4*>(src), v_first_8 + prow * D + c * 32, v_mid_4 + prow * hd + c * 16,
                   v_last_4 + prow * hd + c * 16);
     }
 }

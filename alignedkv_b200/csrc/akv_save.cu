@@ -27,7 +27,7 @@ v_save_vec_kernel(uint8_t* __restrict__ first8, uint8_t* __restrict__ mid4, uint
         const uint4* src = reinterpret_cast<const uint4*>(
             v_new + 2 * (((b * v_new_tokens + p) * H + h) * (long long)D + c * 32));
         long long row = (bh * max_seq_len + (start_pos + p));
-        v_write32(src, first8 + row * D + c * 32, mid4 + row * (D >> 1) + c * 16, last4 + row * (D >> 1) + c * 16);
+        v_write32_global(src, first8 + row * D + c * 32, mid4 + row * (D >> 1) + c * 16, last4 + row * (D >> 1) + c * 16);
     }
 }
 

@@ -21,10 +21,10 @@ __device__ __forceinline__ void v_split4(uint32_t w0, uint32_t w1, uint32_t w2, 
     last = __byte_perm(l01, l23, 0x6420);
 }
 
-// 32 consecutive channels of one V token: src = 64 input bytes; writes 32 + 16 + 16 plane bytes with 16-byte stores.
-__device__ __forceinline__ void v_write32(const uint4* __restrict__ src, uint8_t* __restrict__ f_dst,
+// 32 consecutive channels of one V token (a0..a3 = its 64 input bytes): writes 32 + 16 + 16 plane bytes with 16-byte
+// stores.
+__device__ __forceinline__ void v_write32(uint4 a0, uint4 a1, uint4 a2, uint4 a3, uint8_t* __restrict__ f_dst,
                                           uint8_t* __restrict__ m_dst, uint8_t* __restrict__ l_dst) {
-    uint4 a0 = __ldg(src), a1 = __ldg(src + 1), a2 = __ldg(src + 2), a3 = __ldg(src + 3);
     uint4 f0, f1, m, l;
     v_split4(a0.x, a0.y, a0.z, a0.w, f0.x, f0.y, m.x, l.x);
     v_split4(a1.x, a1.y, a1.z, a1.w, f0.z, f0.w, m.y, l.y);
@@ -35,35 +35,51 @@ __device__ __forceinline__ void v_write32(const uint4* __restrict__ src, uint8_t
     *reinterpret_cast<uint4*>(m_dst) = m;
     *reinterpret_cast<uint4*>(l_dst) = l;
 }
+// the same, reading the 64 input bytes from GLOBAL memory through the read-only path
+__device__ __forceinline__ void v_write32_global(const uint4* __restrict__ src, uint8_t* __restrict__ f_dst,
+                                                 uint8_t* __restrict__ m_dst, uint8_t* __restrict__ l_dst) {
+    v_write32(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3), f_dst, m_dst, l_dst);
+}
 
 // One 64-token K block of one (batch, head): the 64 x D fp16 tile is staged in shared memory token-major (as it
 // arrives; row(t) gives the global address of token t's D halves), then thread d gathers channel d of all 64
 // tokens and emits one 64-byte first_8 row and one 32-byte row of each nibble plane with 16-byte accesses.  Nibble
 // rows are read-add-written (bytewise, mod 256) so that the result equals the reference's `+=`
 // (extension/csrc/K_cache.cu:49-56) on any prior plane contents.  `tile` = plane tile index (b*H + h)*nmb + block.
+// Stage a [64 tokens][D] fp16 tile in shared memory, token-major; row(t) = global address of token t's D halves.
 template <class RowPtr>
-__device__ __forceinline__ void k_write_block64(uint8_t* smem, uint8_t* __restrict__ first8, uint8_t* __restrict__ mid4,
-                                                uint8_t* __restrict__ last4, RowPtr row, long long tile, int D) {
-    constexpr int DB = 64;
+__device__ __forceinline__ void stage_tile64(uint8_t* smem, RowPtr row, int D, int tokens = 64) {
     const int pitch = 2 * D;
     const int vec_per_row = pitch >> 4;
-    for (int i = threadIdx.x; i < DB * vec_per_row; i += blockDim.x) {
+    for (int i = threadIdx.x; i < tokens * vec_per_row; i += blockDim.x) {
         int t = i / vec_per_row, v = i - t * vec_per_row;
         *reinterpret_cast<uint4*>(smem + t * pitch + v * 16) = __ldg(reinterpret_cast<const uint4*>(row(t)) + v);
     }
-    __syncthreads();
+}
+
+// Emit one K block from a staged tile (see k_write_block64).  MAXOUT: also return, per channel, the signed maximum
+// over the 64 tokens as fp16 bits in max_out[d] (the prompt's exponent maxima use the signed maximum,
+// extension/k_cache_file.py:77-78).
+template <bool MAXOUT>
+__device__ __forceinline__ void k_emit_block64(const uint8_t* smem, uint8_t* __restrict__ first8,
+                                               uint8_t* __restrict__ mid4, uint8_t* __restrict__ last4, long long tile,
+                                               int D, uint16_t* max_out) {
+    constexpr int DB = 64;
+    const int pitch = 2 * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         // the nibble rows this thread adds onto: requested before the gather so that their latency overlaps it
         uint4* mdst = reinterpret_cast<uint4*>(mid4 + (tile * D + d) * (DB / 2));
         uint4* ldst = reinterpret_cast<uint4*>(last4 + (tile * D + d) * (DB / 2));
         uint4 om[2] = {mdst[0], mdst[1]}, ol[2] = {ldst[0], ldst[1]};
         uint32_t f[16], m[8], l[8];
+        float mx = -INFINITY;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {  // 8 tokens per group
             uint32_t hi[8], lo[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 uint32_t x = *reinterpret_cast<const uint16_t*>(smem + (g * 8 + j) * pitch + 2 * d);
+                if (MAXOUT) mx = fmaxf(mx, __half2float(__ushort_as_half((unsigned short)x)));
                 hi[j] = x >> 8;
                 lo[j] = x & 0xFFu;
             }
@@ -79,6 +95,7 @@ __device__ __forceinline__ void k_write_block64(uint8_t* smem, uint8_t* __restri
             m[g] = mw;
             l[g] = lw;
         }
+        if (MAXOUT) max_out[d] = __half_as_ushort(__float2half_rn(mx));
         uint4* fdst = reinterpret_cast<uint4*>(first8 + (tile * D + d) * DB);
 #pragma unroll
         for (int v = 0; v < 4; ++v) fdst[v] = make_uint4(f[4 * v], f[4 * v + 1], f[4 * v + 2], f[4 * v + 3]);
@@ -96,6 +113,19 @@ __device__ __forceinline__ void k_write_block64(uint8_t* smem, uint8_t* __restri
             ldst[v] = ol[v];
         }
     }
+}
+
+// One 64-token K block of one (batch, head): the 64 x D fp16 tile is staged in shared memory token-major (as it
+// arrives; row(t) gives the global address of token t's D halves), then thread d gathers channel d of all 64
+// tokens and emits one 64-byte first_8 row and one 32-byte row of each nibble plane with 16-byte accesses.  Nibble
+// rows are read-add-written (bytewise, mod 256) so that the result equals the reference's `+=`
+// (extension/csrc/K_cache.cu:49-56) on any prior plane contents.  `tile` = plane tile index (b*H + h)*nmb + block.
+template <class RowPtr>
+__device__ __forceinline__ void k_write_block64(uint8_t* smem, uint8_t* __restrict__ first8, uint8_t* __restrict__ mid4,
+                                                uint8_t* __restrict__ last4, RowPtr row, long long tile, int D) {
+    stage_tile64(smem, row, D);
+    __syncthreads();
+    k_emit_block64<false>(smem, first8, mid4, last4, tile, D, nullptr);
 }
 
 }  // namespace akv

@@ -81,23 +81,41 @@ class DecodeLayer:
 
     # ------------------------------------------------------------------ prompt
     def prefill(self, k: torch.Tensor, v: torch.Tensor) -> None:
-        """Write a prompt [B,S,H,D] to the planes (whole 64-token blocks) and the residual buffers (the tail);
-        bookkeeping of extension/k_cache_file.py:76-96 and extension/v_cache_file.py:79-96."""
+        """Ingest a prompt [B,S,H,D]: whole 64-token blocks to the planes, the tail to the residual buffers, the
+        exponent of the signed per-channel maximum to the exponent tensors (extension/k_cache_file.py:76-96,
+        extension/v_cache_file.py:79-96) - one pass over the inputs (`akv_prefill`)."""
         B, H, D = self.B, self.H, self.D
         S = k.shape[1]
         assert self.cache_len == 0 and k.shape == (B, S, H, D) and v.shape == (B, S, H, D) and S <= self.L
-        self.k_exp_max.copy_(exponent_field(torch.max(k, dim=1, keepdim=True).values))
-        self.v_exp_max.copy_(exponent_field(torch.max(v, dim=1, keepdim=True).values))
-        cuda_module.k_cache_save(self.k_first_8, self.k_mid_4, self.k_last_4, k.view(torch.uint8), B, H,
-                                 S // column_block, cdiv(self.L, column_block), D, column_block, 0, S)
+        for name, t in (("k", k), ("v", v)):
+            if t.dtype != torch.half or not t.is_cuda or not t.is_contiguous():
+                raise RuntimeError(f"{name}: expected a contiguous CUDA fp16 tensor")
         full = S - S % column_block
-        cuda_module.v_cache_save(self.v_first_8, self.v_mid_4, self.v_last_4, v.view(torch.uint8), B, H, self.L, D, 0,
-                                 full)
-        self.launches += 2 if full else 0
+        if S > 0 and D % 32 == 0 and D <= 256:
+            nbytes = self.lib.akv_prefill_scratch_bytes(B, H, D, S)
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            with torch.cuda.device(self.device):
+                rc = self.lib.akv_prefill(
+                    self.k_first_8.data_ptr(), self.k_mid_4.data_ptr(), self.k_last_4.data_ptr(),
+                    self.v_first_8.data_ptr(), self.v_mid_4.data_ptr(), self.v_last_4.data_ptr(),
+                    self.k_exp_max.data_ptr(), self.v_exp_max.data_ptr(), self.restk.data_ptr(), self.restv.data_ptr(),
+                    k.data_ptr(), v.data_ptr(), ws.data_ptr(), nbytes, B, H, D, self.L, S,
+                    torch.cuda.current_stream(self.device).cuda_stream)
+            _lib.check("prefill", rc)
+            self.launches += 2
+        elif S > 0:
+            # head sizes the fused kernel does not cover: the operator-by-operator route
+            self.k_exp_max.copy_(exponent_field(torch.max(k, dim=1, keepdim=True).values))
+            self.v_exp_max.copy_(exponent_field(torch.max(v, dim=1, keepdim=True).values))
+            cuda_module.k_cache_save(self.k_first_8, self.k_mid_4, self.k_last_4, k.view(torch.uint8), B, H,
+                                     S // column_block, cdiv(self.L, column_block), D, column_block, 0, S)
+            cuda_module.v_cache_save(self.v_first_8, self.v_mid_4, self.v_last_4, v.view(torch.uint8), B, H, self.L, D,
+                                     0, full)
+            self.launches += 2 if full else 0
+            self.restk[:, :S - full] = k[:, full:]
+            self.restv[:, :S - full] = v[:, full:]
         self.rest_len = S % column_block
         self.rest_start = full
-        self.restk[:, :self.rest_len] = k[:, full:]
-        self.restv[:, :self.rest_len] = v[:, full:]
         self.cache_len = S
 
     # ------------------------------------------------------------------ one decode token

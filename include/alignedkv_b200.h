@@ -176,6 +176,22 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
 long long akv_decode_scratch_bytes_ex(int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int flags);
 
 /*
+ * Prompt ingestion in one pass: K_Cache_Class.save + V_Cache_Class.save for start_pos == 0
+ * (extension/k_cache_file.py:76-96, extension/v_cache_file.py:79-96; writers extension/csrc/K_cache.cu:19-58,
+ * extension/csrc/V_cache.cu:17-41).  k, v: fp16 [B,seqlen,H,D].  Writes the whole 64-token blocks to the planes (K
+ * nibbles are added, so planes must start zeroed), the remaining seqlen % 64 tokens to rows 0.. of the residual
+ * buffers [B,64,H,D] (other rows are left as they are), and the exponent field of the SIGNED per-channel maximum
+ * over the prompt to k_exp_max / v_exp_max [B,1,H,D] (the reference takes the signed maximum here and magnitudes on
+ * decode).  Afterwards rest_len = seqlen % 64, rest_start = seqlen - rest_len.  head_dim: multiple of 32, <= 256.
+ * scratch: akv_prefill_scratch_bytes() bytes, 16-byte aligned.
+ */
+int akv_prefill(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* k, const void* v,
+                void* scratch, long long scratch_bytes, int bsz, int n_kv_heads, int head_dim, int max_seq_len,
+                int seqlen, void* stream);
+long long akv_prefill_scratch_bytes(int bsz, int n_kv_heads, int head_dim, int seqlen);
+
+/*
  * Log-sum-exp merge of the packed results of n_ranks shards of one sequence (no counterpart in the reference, which
  * is single-device).  packed: fp32 [n_ranks, rows, head_dim+2] as gathered from the shards (rows = B*Hq);
  * out: fp16 [rows, head_dim] = sum_g w_g o_g with w_g = l_g exp(m_g - M) / sum_g' l_g' exp(m_g' - M), M = max_g m_g.

@@ -165,12 +165,40 @@ def test_decode_step_ex(akv_lib, B, H, G, prompt, steps, max_len, v_mode):
             assert np.allclose(rec[:, 1], want_rec[:, 1], rtol=1e-4), "sum of exponentials"
             assert rel_err(rec[:, 2:], want_rec[:, 2:]) <= TOL, f"step {i}: {rel_err(rec[:, 2:], want_rec[:, 2:]):.2e}"
     torch.cuda.synchronize()
+    # exponent maxima (signed maximum over the prompt, then magnitudes of the decode tokens) per KV head
+    assert np.array_equal(layer.k_exp_max.cpu().numpy(), orc.inner.k_exp_max[:, :, ::G]), "k exponent maxima"
+    assert np.array_equal(layer.v_exp_max.cpu().numpy(), orc.inner.v_exp_max[:, :, ::G]), "v exponent maxima"
     got_planes = [x.cpu().numpy() for x in (layer.k_first_8, layer.k_mid_4, layer.k_last_4, layer.v_first_8,
                                             layer.v_mid_4, layer.v_last_4)]
     for g_, w_, name in zip(got_planes, orc.kv_planes(), ("k_first_8", "k_mid_4", "k_last_4", "v_first_8", "v_mid_4",
                                                           "v_last_4")):
         assert np.array_equal(g_, w_), f"plane {name} differs from the oracle"
     assert akv_lib.akv_device_error_flag() == 0
+
+
+@pytest.mark.parametrize("B,H,D,S,max_len", [(2, 4, 128, 200, 256), (1, 8, 128, 640, 640), (2, 2, 64, 70, 128),
+                                              (1, 4, 256, 130, 192), (3, 4, 128, 63, 64)])
+def test_prefill_one_pass(akv_lib, B, H, D, S, max_len):
+    """akv_prefill (planes + residual tail + exponent maxima in one pass) against the oracle's prompt save:
+    everything bit-exact, including the SIGNED maximum the reference uses for a prompt."""
+    from alignedkv_b200.decode import DecodeLayer
+    from oracle.pipeline import OracleLayerCache
+    k, v, _ = make_kvq(91, B, S, H, D)
+    k[:, :, 0, 5] = -np.abs(k[:, :, 0, 5])          # an all-negative channel: signed max != max magnitude
+    layer = DecodeLayer(B, max_len, H, D, "cuda:0")
+    orc = OracleLayerCache(B, max_len, H, D)
+    layer.prefill(dev(k), dev(v))
+    orc.save(k, v, 0, S)
+    torch.cuda.synchronize()
+    for name, got, want in (("k_first_8", layer.k_first_8, orc.k_first_8), ("k_mid_4", layer.k_mid_4, orc.k_mid_4),
+                            ("k_last_4", layer.k_last_4, orc.k_last_4), ("v_first_8", layer.v_first_8, orc.v_first_8),
+                            ("v_mid_4", layer.v_mid_4, orc.v_mid_4), ("v_last_4", layer.v_last_4, orc.v_last_4),
+                            ("k_exp_max", layer.k_exp_max, orc.k_exp_max), ("v_exp_max", layer.v_exp_max, orc.v_exp_max)):
+        assert np.array_equal(got.cpu().numpy(), want), f"{name} differs from the oracle"
+    r = S % 64
+    assert (layer.rest_len, layer.rest_start) == (r, S - r)
+    assert np.array_equal(layer.restk[:, :r].cpu().numpy().view(np.uint16), orc.restk[:, :r].view(np.uint16))
+    assert np.array_equal(layer.restv[:, :r].cpu().numpy().view(np.uint16), orc.restv[:, :r].view(np.uint16))
 
 
 def test_lse_merge(akv_lib):
