@@ -146,6 +146,7 @@ class DecodeLayer:
                 self.scratch.data_ptr(), self.scratch.numel(), B, H, self.G, D, self.L, self.rest_len, self.rest_start,
                 self._flags(append), torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check("decode_step", rc)
+        self.last_q = q                                   # (for bytes_accounting)
         flush = append and self.rest_len + 1 == column_block
         qn = self.rest_start + (column_block if flush else 0)
         rest = 0 if flush else self.rest_len + (1 if append else 0)
@@ -197,10 +198,11 @@ class DecodeLayer:
             return {}
         return {"k_compute": {"us": k_us.value, "launches": n}, "v_compute": {"us": v_us.value, "launches": n}}
 
-    def bytes_accounting(self, q: torch.Tensor):
+    def bytes_accounting(self, q: torch.Tensor | None = None):
         """Algorithmic plane bytes of the LAST decode step under its read decisions (mid plane iff code < 2, low
         plane iff code < 1), from the state the step left behind, plus the dense fp16 equivalent."""
         B, H, Hq, G, D = self.B, self.H, self.Hq, self.G, self.D
+        q = self.last_q if q is None else q
         qn = self.rest_start
         # K: per (batch, KV head, channel) the union over the group's query heads of the plane reads
         kq = exponent_field(q).view(B, 1, H, G, D) + self.k_exp_max.view(B, 1, H, 1, D)

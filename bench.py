@@ -43,6 +43,11 @@ WORKLOADS = {
                                  v_mode="exact"),
     "long-context-decode": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072, sharding="sequence",
                                 v_mode="order_free"),
+    # full random-init Llama-2-7B decoder, AlignedKV cache on every layer: prompt of 1024 uniform-random ids, then greedy
+    # decoding; a step = one token per sequence through all 32 layers (cache_len = prompt length, it grows by one per step)
+    "llama2-7b-decoder": dict(batch=16, heads=32, kv_heads=32, head_dim=128, cache_len=1024, sharding="replicate",
+                              v_mode="exact", decoder=dict(hidden_size=4096, intermediate_size=11008,
+                                                           num_hidden_layers=32, vocab_size=32000)),
 }
 WORKLOAD = dict(name="llama2-7b-layer-decode", **WORKLOADS["llama2-7b-layer-decode"])
 OUTLIER_CHANNELS = (3, 34, 65, 96)
@@ -357,10 +362,143 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_decoder(args):
+    """The full-decoder workload: tokens/s of greedy decoding with the AlignedKV cache on every layer."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: alignedkv_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from alignedkv_b200.llama import LlamaConfig, LlamaDecoder
+
+    B, Hq, H, D, S = (WORKLOAD[k_] for k_ in ("batch", "heads", "kv_heads", "head_dim", "cache_len"))
+    dc = WORKLOAD["decoder"]
+    cfg = LlamaConfig(hidden_size=dc["hidden_size"], intermediate_size=dc["intermediate_size"],
+                      num_hidden_layers=dc["num_hidden_layers"], num_attention_heads=Hq, num_key_value_heads=H,
+                      vocab_size=dc["vocab_size"])
+    warm = max(args.warmup, 3)
+    v_mode = args.v_mode or WORKLOAD["v_mode"]
+    max_len = -(-(S + 2 * (warm + args.steps) + 2) // 64) * 64
+    model = LlamaDecoder(cfg, B, max_len, dev, seed=args.seed + rank, v_mode=v_mode)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), device=dev,
+                        generator=torch.Generator(device=dev).manual_seed(args.seed + 100 + rank))
+    tok = model.prefill(ids).argmax(-1)
+    lib = model.caches[0].lib
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    state = {"tok": tok}
+    htok = torch.empty(B, dtype=torch.int64).pin_memory()
+    hin = tok.cpu().pin_memory()
+
+    def step_resident():
+        state["tok"] = model.step(state["tok"]).argmax(-1)
+
+    def step_e2e():
+        t = hin.to(dev, non_blocking=True)               # the caller hands the previous tokens over from the host
+        nxt = model.step(t).argmax(-1)
+        htok.copy_(nxt, non_blocking=True)
+        torch.cuda.current_stream().synchronize()        # and reads the new ones there
+        hin.copy_(htok)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        ms = e0.elapsed_time(e1)
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, t0, t1
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for c in model.caches:
+        c.launches = 0
+    lib.akv_set_tuning(b"timing", 1)
+    lib.akv_timing_reset()
+    if sampler:
+        sampler.start()
+    ms, t0, t1 = timed(step_resident, args.steps, warm)
+    clocks = sampler.stop(t0, t1) if sampler else None
+    kern = model.caches[0].kernel_times()                 # medians over every layer's launches in the timed steps
+    launches = sum(c.launches for c in model.caches) // (args.steps + warm)
+    acct = {"k_compute": 0.0, "v_compute": 0.0, "read": 0.0, "dense": 0.0}
+    for c in model.caches:                                # the last step's read decisions, every layer
+        a = c.bytes_accounting()
+        for k_ in acct:
+            acct[k_] += a[k_]
+    ms_e2e, _, _ = timed(step_e2e, args.steps, warm)
+    if rank == 0:
+        ms_step = ms / args.steps
+        tokens = B * world
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        L_now = model.caches[0].cache_len
+        nl = cfg.num_hidden_layers
+        weight_bytes = 2.0 * sum(t.numel() for lyr in model.layers for t in lyr.values()) + 2.0 * model.lm_head.numel()
+        dom = max(kern, key=lambda n: kern[n]["us"]) if kern else None
+        roofline = None
+        if dom:
+            a = acct[dom] / nl / (kern[dom]["us"] * 1e-6) / 1e9     # per launch = per layer
+            roofline = {"bound": "hbm", "kernel": dom, "achieved": a, "peak": peak, "unit": "GB/s", "frac": a / peak,
+                        "peak_source": "measured" if peaks else "fallback", "traffic": None,
+                        "us_per_launch": kern[dom]["us"], "algorithmic_bytes": acct[dom] / nl,
+                        "timing": "median of CUDA-event brackets over every layer's launch in the timed steps"}
+        line = {
+            "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic (random-init weights ~N(0,0.02), uniform-random prompt ids)",
+            "config": {"workload": WORKLOAD["name"], "batch": B, "query_heads": Hq, "kv_heads": H, "head_dim": D,
+                       "layers": nl, "hidden": cfg.hidden_size, "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                       "prompt_len": S, "cache_len_at_end": L_now, "global_batch": tokens, "pv_kernel": v_mode,
+                       "step": "one greedy token per sequence through all layers (projections and MLP: fp16 cuBLAS "
+                               "through torch; attention: the AlignedKV decode step of every layer)",
+                       "l2": "weights 13.5 GB + planes, far larger than L2"},
+            "attention_kernels_us_per_layer": {n: round(kv_["us"], 2) for n, kv_ in kern.items()},
+            "attention_bytes_read_over_dense": acct["read"] / acct["dense"],
+            "weight_bytes_per_step": weight_bytes,
+            "roofline": roofline,
+            "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * 8,
+                    "d2h_bytes_per_step": B * 8, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif "decoder" in WORKLOAD:
+        run_decoder(args)
     else:
         run_ours(args)
 
