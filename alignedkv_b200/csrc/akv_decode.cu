@@ -412,6 +412,29 @@ tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_mai
     }
 }
 
+// ------------------------------------------------------------------ rollback of appended tokens
+// Undo appends: the exponent maxima are put back from copies the caller took earlier, and the K nibble planes of
+// blocks that were written since are cleared (the K writer ADDS nibbles, extension/csrc/K_cache.cu:52-56, so a block
+// has to be zero before it is written again).  High bytes, V planes and residual rows need nothing: they are
+// overwritten by plain stores when the positions are appended again.  grid B*H, 128 threads.
+__global__ void __launch_bounds__(128)
+rollback_kernel(uint4* __restrict__ k_mid_4, uint4* __restrict__ k_last_4, uint4* __restrict__ k_exp,
+                uint4* __restrict__ v_exp, const uint4* __restrict__ k_exp_saved, const uint4* __restrict__ v_exp_saved,
+                int D, int nmb, int first_block, int n_blocks) {
+    const long long bh = blockIdx.x;
+    const int vec_per_block = D * (BLK / 2) / 16;                     // 16-byte pieces of one nibble-plane block
+    uint4* m = k_mid_4 + (bh * nmb + first_block) * vec_per_block;
+    uint4* l = k_last_4 + (bh * nmb + first_block) * vec_per_block;
+    for (int i = threadIdx.x; i < n_blocks * vec_per_block; i += blockDim.x) {
+        m[i] = make_uint4(0, 0, 0, 0);
+        l[i] = make_uint4(0, 0, 0, 0);
+    }
+    for (int i = threadIdx.x; i < D / 16; i += blockDim.x) {
+        k_exp[bh * (D / 16) + i] = k_exp_saved[bh * (D / 16) + i];
+        v_exp[bh * (D / 16) + i] = v_exp_saved[bh * (D / 16) + i];
+    }
+}
+
 // ------------------------------------------------------------------ optional per-kernel timing
 struct Timing {
     static constexpr int CAP = 4096;
@@ -617,6 +640,26 @@ int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_firs
     return akv_decode_step_ex(k_first_8, k_mid_4, k_last_4, v_first_8, v_mid_4, v_last_4, k_exp_max, v_exp_max, restk,
                               restv, q, k_new, v_new, out, nullptr, scratch, scratch_bytes, bsz, n_heads, 1, head_dim,
                               max_seq_len, rest_len, rest_start, reference ? AKV_STEP_REFERENCE : 0, stream);
+}
+
+int akv_rollback(void* k_mid_4, void* k_last_4, void* k_exp_max, void* v_exp_max, const void* k_exp_saved,
+                 const void* v_exp_saved, int bsz, int n_kv_heads, int head_dim, int max_seq_len, int first_block,
+                 int n_blocks, void* stream) {
+    set_error("");
+    AKV_REQUIRE(k_mid_4 && k_last_4 && k_exp_max && v_exp_max && k_exp_saved && v_exp_saved, AKV_ERR_NULL,
+                "rollback: null pointer");
+    const int nmb = (max_seq_len + BLK - 1) / BLK;
+    AKV_REQUIRE(bsz > 0 && n_kv_heads > 0 && head_dim > 0 && head_dim % 16 == 0 && max_seq_len > 0 && first_block >= 0 &&
+                n_blocks >= 0 && first_block + n_blocks <= nmb, AKV_ERR_SHAPE,
+                "rollback: bad extent (bsz %d, heads %d, head_dim %d, blocks [%d, %d) of %d)", bsz, n_kv_heads, head_dim,
+                first_block, first_block + n_blocks, nmb);
+    AKV_REQUIRE(aligned16(k_mid_4) && aligned16(k_last_4) && aligned16(k_exp_max) && aligned16(v_exp_max) &&
+                aligned16(k_exp_saved) && aligned16(v_exp_saved), AKV_ERR_ALIGN, "rollback: pointers must be 16-byte aligned");
+    rollback_kernel<<<bsz * n_kv_heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint4*>(k_mid_4), static_cast<uint4*>(k_last_4), static_cast<uint4*>(k_exp_max),
+        static_cast<uint4*>(v_exp_max), static_cast<const uint4*>(k_exp_saved), static_cast<const uint4*>(v_exp_saved),
+        head_dim, nmb, first_block, n_blocks);
+    return cuda_status(cudaGetLastError(), "rollback launch");
 }
 
 int akv_lse_merge(const void* packed, void* out, int n_ranks, int rows, int head_dim, void* stream) {

@@ -164,23 +164,27 @@ class DecodeLayer:
 
     # ------------------------------------------------------------------ benchmark helpers
     def snapshot(self):
-        """Everything a decode step mutates, so that the same step can be replayed."""
+        """What is needed to come back to the current length later (`restore`): the counters and the exponent maxima."""
         return dict(rest_len=self.rest_len, rest_start=self.rest_start, cache_len=self.cache_len,
-                    restk=self.restk.clone(), restv=self.restv.clone(), k_exp=self.k_exp_max.clone(),
-                    v_exp=self.v_exp_max.clone())
+                    k_exp=self.k_exp_max.clone(), v_exp=self.v_exp_max.clone())
 
     def restore(self, snap) -> None:
-        """Rewind to a snapshot taken at most one block earlier.  The K nibble planes of blocks written since are
-        zeroed because the K writer accumulates nibbles (extension/csrc/K_cache.cu:52-56)."""
+        """Roll the cache back to a snapshot (`akv_rollback`): the exponent maxima are put back and the K nibble planes
+        of blocks written since are cleared, because the K writer accumulates nibbles
+        (extension/csrc/K_cache.cu:52-56).  Tokens that were still in the residual buffer at the snapshot stay
+        there: later appends only wrote rows behind them."""
         first_blk = snap["rest_start"] // column_block
-        last_blk = cdiv(self.cache_len, column_block)
-        if last_blk > first_blk:
-            self.k_mid_4[:, :, first_blk:last_blk].zero_()
-            self.k_last_4[:, :, first_blk:last_blk].zero_()
-        self.restk.copy_(snap["restk"])
-        self.restv.copy_(snap["restv"])
-        self.k_exp_max.copy_(snap["k_exp"])
-        self.v_exp_max.copy_(snap["v_exp"])
+        last_blk = self.rest_start // column_block
+        appended = self.cache_len - snap["cache_len"]
+        if appended < 0 or (snap["rest_len"] and snap["rest_len"] + appended > column_block):
+            raise RuntimeError("restore: the residual tokens of the snapshot have been overwritten since")
+        with torch.cuda.device(self.device):
+            rc = self.lib.akv_rollback(self.k_mid_4.data_ptr(), self.k_last_4.data_ptr(), self.k_exp_max.data_ptr(),
+                                       self.v_exp_max.data_ptr(), snap["k_exp"].data_ptr(), snap["v_exp"].data_ptr(),
+                                       self.B, self.H, self.D, self.L, first_blk, max(0, last_blk - first_blk),
+                                       torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check("rollback", rc)
+        self.launches += 1
         self.rest_len, self.rest_start, self.cache_len = snap["rest_len"], snap["rest_start"], snap["cache_len"]
 
     def reset_counters(self) -> None:

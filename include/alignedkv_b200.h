@@ -192,6 +192,18 @@ int akv_prefill(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8,
 long long akv_prefill_scratch_bytes(int bsz, int n_kv_heads, int head_dim, int seqlen);
 
 /*
+ * Roll the cache back to an earlier length (no counterpart in the reference; used to drop speculative tokens and to
+ * replay a step).  The caller keeps copies of the exponent maxima taken at the earlier length and its own
+ * (rest_len, rest_start); this call puts the maxima back and clears the K nibble planes of the blocks
+ * [first_block, first_block + n_blocks) that were written since - the K writer adds nibbles, so a block must be zero
+ * before it is written again.  Nothing else needs undoing: high bytes, V planes and residual rows are overwritten by
+ * plain stores when the positions are appended again.
+ */
+int akv_rollback(void* k_mid_4, void* k_last_4, void* k_exp_max, void* v_exp_max, const void* k_exp_saved,
+                 const void* v_exp_saved, int bsz, int n_kv_heads, int head_dim, int max_seq_len, int first_block,
+                 int n_blocks, void* stream);
+
+/*
  * Log-sum-exp merge of the packed results of n_ranks shards of one sequence (no counterpart in the reference, which
  * is single-device).  packed: fp32 [n_ranks, rows, head_dim+2] as gathered from the shards (rows = B*Hq);
  * out: fp16 [rows, head_dim] = sum_g w_g o_g with w_g = l_g exp(m_g - M) / sum_g' l_g' exp(m_g' - M), M = max_g m_g.

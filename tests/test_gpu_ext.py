@@ -201,6 +201,38 @@ def test_prefill_one_pass(akv_lib, B, H, D, S, max_len):
     assert np.array_equal(layer.restv[:, :r].cpu().numpy().view(np.uint16), orc.restv[:, :r].view(np.uint16))
 
 
+@pytest.mark.parametrize("prompt,steps", [(255, 1), (200, 5), (192, 70)])
+def test_rollback_replays_bit_exactly(akv_lib, prompt, steps):
+    """snapshot -> decode some tokens (with or without a block flush) -> restore -> the same tokens again: outputs and
+    planes are bit-identical to the first pass (akv_rollback clears the K nibble blocks written since, which the
+    accumulating K writer needs)."""
+    from alignedkv_b200.decode import DecodeLayer
+    B, H, D, max_len = 2, 4, 128, 320
+    k, v, _ = make_kvq(95, B, prompt + steps, H, D)
+    rng = np.random.default_rng(96)
+    qs = rng.standard_normal((steps, B, 1, H, D), dtype=np.float32).astype(np.float16)
+    layer = DecodeLayer(B, max_len, H, D, "cuda:0")
+    layer.prefill(dev(k[:, :prompt]), dev(v[:, :prompt]))
+    snap = layer.snapshot()
+
+    def run():
+        outs = [layer.decode(dev(qs[i]), dev(k[:, prompt + i:prompt + i + 1]), dev(v[:, prompt + i:prompt + i + 1]))
+                for i in range(steps)]
+        planes = [x.clone() for x in (layer.k_first_8, layer.k_mid_4, layer.k_last_4, layer.v_first_8, layer.v_mid_4,
+                                      layer.v_last_4, layer.k_exp_max, layer.v_exp_max)]
+        return outs, planes
+    o1, p1 = run()
+    layer.restore(snap)
+    assert (layer.cache_len, layer.rest_len) == (prompt, prompt % 64)
+    o2, p2 = run()
+    for a, b in zip(o1 + p1, o2 + p2):
+        assert torch.equal(a, b)
+    future = layer.snapshot()
+    future["cache_len"] = layer.cache_len + 1          # a snapshot from the future cannot be restored
+    with pytest.raises(RuntimeError):
+        layer.restore(future)
+
+
 def test_lse_merge(akv_lib):
     from oracle.pipeline import lse_merge_np
     lib = akv_lib
