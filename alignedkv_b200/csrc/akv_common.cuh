@@ -22,6 +22,7 @@ struct Tuning {
     int timing = 0;     // 1: akv_decode_step records CUDA events around its two streaming kernels
     int debug = 0;      // experiments only: 1 = skip the consumer math, 2 = skip the global copies (wrong results)
     int k_wpc = 0;      // cap on warps per CTA of the q.K^T kernel (0 = as many as shared memory allows)
+    int pdl = 1;        // 1: the kernels of a decode step are chained with programmatic dependent launch
 };
 Tuning& tuning();
 
@@ -34,6 +35,31 @@ Tuning& tuning();
     } while (0)
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// The kernels of one decode step form a chain in one stream.  Launched with the programmatic-serialization
+// attribute, a kernel's CTAs may become resident while its predecessor is still running; every such kernel calls
+// pdl_enter() first: it lets ITS successor be scheduled early and then blocks until the predecessor grid has
+// completed and its memory is visible.  Without the attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+template <class Kernel, class... Args>
+static inline cudaError_t launch_chained(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                         Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 // ---------------------------------------------------------------- async copies global -> shared (LDGSTS)
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -99,6 +99,7 @@ append_flush_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, 
                     int B, int H, int G, int D, int rest_len, int append, int nmb, int max_seq_len, int qn) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ uint32_t red[4];
+    pdl_enter();
     const int BH = B * H, hd = D >> 1;
     if ((int)blockIdx.x < BH) {
         const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
@@ -170,6 +171,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     __shared__ float redf[8];
     __shared__ uint32_t cand_v[256];
     __shared__ int32_t cand_i[256];
+    pdl_enter();
     const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint16_t* row = s + (size_t)bhq * R;
@@ -369,6 +371,7 @@ softmax_class_reduce_kernel(const float* __restrict__ cstat, const uint32_t* __r
 __global__ void __launch_bounds__(128)
 amin_kernel(const uint16_t* __restrict__ test_o, const uint8_t* __restrict__ v_exp, uint8_t* __restrict__ amin,
             int BHq, int H, int G, int D) {
+    pdl_enter();
     const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (i >= BHq) return;
     const int lane = threadIdx.x & 31, Hq = H * G;
@@ -393,6 +396,7 @@ __global__ void __launch_bounds__(256)
 tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_main32, const uint16_t* __restrict__ p,
             const __half* __restrict__ restv, __half* __restrict__ out, const float* __restrict__ stats,
             float* __restrict__ packed, int H, int G, int D, int R, int qn, int rest) {
+    pdl_enter();
     const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f;
@@ -421,6 +425,7 @@ __global__ void __launch_bounds__(128)
 rollback_kernel(uint4* __restrict__ k_mid_4, uint4* __restrict__ k_last_4, uint4* __restrict__ k_exp,
                 uint4* __restrict__ v_exp, const uint4* __restrict__ k_exp_saved, const uint4* __restrict__ v_exp_saved,
                 int D, int nmb, int first_block, int n_blocks) {
+    pdl_enter();
     const long long bh = blockIdx.x;
     const int vec_per_block = D * (BLK / 2) / 16;                     // 16-byte pieces of one nibble-plane block
     uint4* m = k_mid_4 + (bh * nmb + first_block) * vec_per_block;
@@ -545,7 +550,7 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
                              aligned16(v_first_8) && aligned16(v_mid_4) && aligned16(v_last_4);
     {
         const int blocks = fused_flush ? B * H * (2 + D / 64) : B * H;
-        append_flush_kernel<<<blocks, 128, fused_flush ? (size_t)BLK * 2 * D : 0, st>>>(
+        launch_chained(append_flush_kernel, dim3(blocks), dim3(128), fused_flush ? (size_t)BLK * 2 * D : 0, st,
             static_cast<uint32_t*>(restk), static_cast<uint32_t*>(restv), static_cast<uint16_t*>(k_exp_max),
             static_cast<uint16_t*>(v_exp_max), static_cast<const uint32_t*>(q), static_cast<const uint32_t*>(k_new),
             static_cast<const uint32_t*>(v_new), reinterpret_cast<uint16_t*>(sc.kq), sc.kqmax,
@@ -592,8 +597,9 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
         softmax_class_reduce_kernel<<<B * H * G, 32, 0, st>>>(sc.cstat, sc.cand_val, sc.cand_idx, sc.pval, sc.pidx,
                                                              sc.stats, sm_chunks);
     } else {
-        softmax_kernel<<<B * H * G, 256, 0, st>>>(sc.s, static_cast<const __half*>(q), static_cast<const __half*>(restk),
-                                                 sc.pval, sc.pidx, sc.stats, H, G, D, R, qn, rest, sqrtf((float)D));
+        launch_chained(softmax_kernel, dim3(B * H * G), dim3(256), 0, st, sc.s, static_cast<const __half*>(q),
+                       static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats, H, G, D, R, qn, rest,
+                       sqrtf((float)D));
     }
     if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
     const bool need_tail = rest > 0 || qn == 0 || packed_out != nullptr || order_free;
@@ -602,8 +608,8 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
                             reinterpret_cast<const uint8_t*>(sc.pidx), reinterpret_cast<uint8_t*>(sc.test_o), B, H, G,
                             max_seq_len, D, TOPK, st);
         if (rc != AKV_OK) return rc;
-        amin_kernel<<<(B * H * G + 3) / 4, 128, 0, st>>>(sc.test_o, static_cast<const uint8_t*>(v_exp_max), sc.amin,
-                                                        B * H * G, H, G, D);
+        launch_chained(amin_kernel, dim3((B * H * G + 3) / 4), dim3(128), 0, st, (const uint16_t*)sc.test_o,
+                       static_cast<const uint8_t*>(v_exp_max), sc.amin, B * H * G, H, G, D);
         if ((rc = cuda_status(cudaGetLastError(), "decode_step threshold launch")) != AKV_OK) return rc;
         if (ev) cudaEventRecord(ev[2], st);
         if (order_free)
@@ -623,10 +629,11 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
         if (rc != AKV_OK) return rc;
     }
     if (need_tail) {
-        tail_kernel<<<B * H * G, D < 256 ? ((D + 31) / 32) * 32 : 256, 0, st>>>(
-            (qn > 0 && !order_free) ? sc.o_main : nullptr, order_free ? sc.o_main32 : nullptr, sc.s,
-            static_cast<const __half*>(restv), static_cast<__half*>(out), sc.stats, static_cast<float*>(packed_out), H, G,
-            D, R, qn, rest);
+        launch_chained(tail_kernel, dim3(B * H * G), dim3(D < 256 ? ((D + 31) / 32) * 32 : 256), 0, st,
+                       (const uint16_t*)((qn > 0 && !order_free) ? sc.o_main : nullptr),
+                       (const float*)(order_free ? sc.o_main32 : nullptr), (const uint16_t*)sc.s,
+                       static_cast<const __half*>(restv), static_cast<__half*>(out), (const float*)sc.stats,
+                       static_cast<float*>(packed_out), H, G, D, R, qn, rest);
         if ((rc = cuda_status(cudaGetLastError(), "decode_step tail launch")) != AKV_OK) return rc;
     }
     return AKV_OK;
@@ -655,7 +662,7 @@ int akv_rollback(void* k_mid_4, void* k_last_4, void* k_exp_max, void* v_exp_max
                 first_block, first_block + n_blocks, nmb);
     AKV_REQUIRE(aligned16(k_mid_4) && aligned16(k_last_4) && aligned16(k_exp_max) && aligned16(v_exp_max) &&
                 aligned16(k_exp_saved) && aligned16(v_exp_saved), AKV_ERR_ALIGN, "rollback: pointers must be 16-byte aligned");
-    rollback_kernel<<<bsz * n_kv_heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_chained(rollback_kernel, dim3(bsz * n_kv_heads), dim3(128), 0, static_cast<cudaStream_t>(stream),
         static_cast<uint4*>(k_mid_4), static_cast<uint4*>(k_last_4), static_cast<uint4*>(k_exp_max),
         static_cast<uint4*>(v_exp_max), static_cast<const uint4*>(k_exp_saved), static_cast<const uint4*>(v_exp_saved),
         head_dim, nmb, first_block, n_blocks);

@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     constexpr int TILES_PER_IT = 32 / ROW_LANES;  // 1 (KCH 16) or 2 (KCH 8)
     static_assert(KCH == 8 || KCH == 16, "channels per stage");
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_enter();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wpc = blockDim.x >> 5;
     const int w = blockIdx.x * wpc + warp;
@@ -333,7 +334,7 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     auto go = [&](auto kern) -> int {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_status(e, "k_cache_compute smem attribute");
-        kern<<<grid, wpc * 32, smem, st>>>(p);
+        launch_chained(kern, dim3(grid), dim3(wpc * 32), smem, st, p);
         return AKV_OK;
     };
     int rc;

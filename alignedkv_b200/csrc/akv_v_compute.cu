@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
     const uint32_t bar_full = base + P::BAR_OFF, bar_ready = bar_full + NF * 8, bar_free = bar_ready + NR * 8;
     const uint32_t bar_sb = bar_free + NR * 8;
 
+    pdl_enter();
     if (tid == 0) {
         for (int s = 0; s < NF; ++s) mbar_init(bar_full + s * 8, 2);   // one arrival per warp of the pair (+ bytes)
         for (int s = 0; s < NR; ++s) {
@@ -496,7 +497,7 @@ static int launch_v_fast(const VParams& p, int BH, cudaStream_t st) {
         if (e != cudaSuccess) return cuda_status(e, "v_cache_compute smem attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    v_compute_kernel<128, G, NF, NR, NML><<<BH, 64 * G + 128, K::BYTES, st>>>(p);
+    launch_chained(v_compute_kernel<128, G, NF, NR, NML>, dim3(BH), dim3(64 * G + 128), K::BYTES, st, p);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
 }
 
@@ -534,6 +535,7 @@ template <int KMAX>
 __global__ void __launch_bounds__(128)
 v_probe_kernel(const uint8_t* __restrict__ first8, const uint16_t* __restrict__ s_val,
                const int32_t* __restrict__ s_idx, uint16_t* __restrict__ out, int max_seq_len, int D, int K, int G) {
+    pdl_enter();
     const long long bh = blockIdx.x;                                    // (batch, query head)
     const uint8_t* F = first8 + (size_t)(bh / G) * max_seq_len * D;     // planes of its KV head
     for (int c = threadIdx.x; c < (D >> 1); c += blockDim.x) {
@@ -567,9 +569,9 @@ v_probe_kernel(const uint8_t* __restrict__ first8, const uint16_t* __restrict__ 
 int launch_v_probe(const uint8_t* first8, const uint8_t* s_val, const uint8_t* s_idx, uint8_t* out, int bsz, int H,
                    int group, int max_seq_len, int D, int K, cudaStream_t st) {
     int threads = (D >> 1) < 128 ? (((D >> 1) + 31) / 32) * 32 : 128;
-    v_probe_kernel<32><<<bsz * H * group, threads, 0, st>>>(first8, reinterpret_cast<const uint16_t*>(s_val),
-                                                            reinterpret_cast<const int32_t*>(s_idx),
-                                                            reinterpret_cast<uint16_t*>(out), max_seq_len, D, K, group);
+    launch_chained(v_probe_kernel<32>, dim3(bsz * H * group), dim3(threads), 0, st, first8,
+                   reinterpret_cast<const uint16_t*>(s_val), reinterpret_cast<const int32_t*>(s_idx),
+                   reinterpret_cast<uint16_t*>(out), max_seq_len, D, K, group);
     return cuda_status(cudaGetLastError(), "v_cache_test_compute launch");
 }
 

@@ -47,7 +47,7 @@ int akv_device_error_flag(void);
 
 /*
  * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16, "k_prefetch" 0..64,
- * "timing" 0|1).
+ * "timing" 0|1, "pdl" 0|1: chain the kernels of a decode step with programmatic dependent launch).
  * Process-wide; results never depend on them.  No counterpart in the reference.
  */
 int akv_set_tuning(const char* key, int value);
