@@ -585,9 +585,10 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
         if (ev) cudaEventRecord(ev[1], st);
         if (rc != AKV_OK) return rc;
     }
-    // one CTA per row while there are enough rows to fill the GPU or the rows are short; else the split form
+    // one CTA per row while there are enough rows to fill the GPU or the rows are short (three launches cost more
+    // than they save below ~16k scores); else the split form
     const int sm_chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
-    if (sm_chunks >= 2 && B * H * G < 2 * sm_count()) {
+    if (sm_chunks >= 4 && B * H * G < 2 * sm_count()) {
         dim3 grid(sm_chunks, B * H * G);
         softmax_chunk_stats_kernel<<<grid, 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
                                                         static_cast<const __half*>(restk), sc.cstat, H, G, D, R, qn, rest,

@@ -154,7 +154,7 @@ class DecodeLayer:
         # kernels of this library launched by the call: append (+ flush in the same launch; 2 more launches when the
         # head is too wide for that), q.K^T, softmax, probe, threshold, P.V (2 for the order-free form), tail
         R = (qn // column_block + 1) * column_block
-        split_softmax = R > 4096 and B * Hq < 2 * self._sm_count     # rows cut into 4096-score chunks: 3 launches
+        split_softmax = R > 3 * 4096 and B * Hq < 2 * self._sm_count     # rows cut into 4096-score chunks: 3 launches
         self.launches += 1 + (2 if flush and D > 256 else 0) + (1 if qn else 0) + (3 if split_softmax else 1) + \
             ((3 + (1 if self.v_mode == "order_free" else 0)) if qn else 0) + (1 if tail else 0)
         self.rest_len, self.rest_start = rest, qn
