@@ -18,9 +18,7 @@ int max_dyn_smem();      // opt-in dynamic shared memory per block of the curren
 struct Tuning {
     int k_kch = 16;     // channels per stage of the q.K^T kernel (8 or 16)
     int k_stages = 3;   // ring depth per warp of the q.K^T kernel (3..6, see launch_k_compute)
-    int k_prefetch = 0; // L2 prefetch distance of the q.K^T kernel in stages (0 = off)
     int timing = 0;     // 1: akv_decode_step records CUDA events around its two streaming kernels
-    int debug = 0;      // experiments only: 1 = skip the consumer math, 2 = skip the global copies (wrong results)
     int k_wpc = 0;      // cap on warps per CTA of the q.K^T kernel (0 = as many as shared memory allows)
     int pdl = 1;        // 1: the kernels of a decode step are chained with programmatic dependent launch
 };
