@@ -7,14 +7,17 @@
 //
 // Design (B200): the kernel is a pure HBM stream.  Each WARP owns a private ring of shared-memory stages that
 // it fills with 16-byte asynchronous copies and drains itself - no block-level barrier exists.  A warp works
-// through a contiguous run of units; a unit is 4 consecutive 64-token blocks of one (batch, head), and a stage
+// through a contiguous run of units; a unit is 4 consecutive 64-token blocks of one (batch, KV head), and a stage
 // holds KCH channels of those 4 blocks: the high-byte rows plus, only for the channels whose alignment code
 // asks for them, the 32-byte rows of the mid / low nibble planes (rows that are skipped are never requested
-// from memory; the producer writes the substitute constants into their slots so that the consumer is
-// branch-free).  Lane (tile, i) owns tokens 8i..8i+7 of its tile and keeps four fp16x2 accumulators: one 8-byte
-// and two 4-byte shared loads feed four FMAs, and no cross-lane reduction exists, which is what keeps the
-// channel-order fp16 sum exact.  Grouped-query attention (G query heads per KV head) runs the G passes over a
-// unit's tiles back to back on the same warp, so that only the first pass reads HBM.
+// from memory).  Lane (tile, i) owns tokens 8i..8i+7 of its tile and keeps four fp16x2 accumulators per query head:
+// one 8-byte and two 4-byte shared loads feed four FMAs, and no cross-lane reduction exists, which is what keeps the
+// channel-order fp16 sum exact.
+// Grouped-query attention (G query heads per KV head): a row is fetched when ANY head of the group needs it, every
+// staged row is read from shared memory once and applied to the G heads in turn, each head substituting the
+// reference's constants where its own code skips the plane - so plane bytes cross HBM once per group and the
+// results equal G independent multi-head passes.  With G == 1 the producer writes the constants into the skipped
+// rows' slots instead, and the consumer has no per-row selects.
 #include "akv_common.cuh"
 
 namespace akv {
@@ -22,11 +25,16 @@ namespace akv {
 namespace kc {
 constexpr int TILES = 4;                         // 64-token blocks per warp unit
 constexpr int MAX_D = 256;
-constexpr int META = 64 + 4 * MAX_D;             // plane-read masks (16 words) + q as duplicated fp16x2 words
 constexpr int NMETA = 3;
 __host__ __device__ constexpr int f_tile(int kch) { return kch * 64 + 64; }   // +64: tiles land on distinct banks
 __host__ __device__ constexpr int n_tile(int kch) { return kch * 32 + 32; }
 __host__ __device__ constexpr int stage_bytes(int kch) { return TILES * f_tile(kch) + 2 * TILES * n_tile(kch); }
+}  // namespace kc
+
+namespace kc {
+// per (batch, KV head) metadata slot: union masks (16 words), then per query head masks (16 words) + q words
+__host__ __device__ constexpr int head_meta(int D) { return 64 + 4 * D; }
+__host__ __device__ constexpr int meta_bytes(int D, int G) { return 64 + G * head_meta(D); }
 }  // namespace kc
 
 struct KParams {
@@ -37,8 +45,7 @@ struct KParams {
     const uint8_t* kqmax;
     const uint8_t* q;
     uint8_t* s;
-    int BH, nb, nmb, D, ngroups;
-    int G;                // query heads per KV head; kq, kqmax, q and s are per (batch, query head)
+    int BH, nb, nmb, D, ngroups;   // BH = batch x KV heads
     int units, upw;       // total units, units per warp (contiguous run)
     uint32_t scale2;      // half(sqrt_dim) in both halves
     int reference;
@@ -48,16 +55,14 @@ __device__ __forceinline__ void st_shared_v4(uint32_t a, uint32_t v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(a), "r"(v) : "memory");
 }
 
-// Position of a stream of stages (unit, channel chunk) inside one warp's run of units.  Units are ordered
-// (batch, KV head) -> group of 4 blocks -> query head of the group, so the G passes over the same tiles (one per
-// query head) run back to back on the same warp and all but the first are served by L2.
+// Position of a stream of stages (unit, channel chunk) inside one warp's run of units.
 struct KCursor {
-    int u, g, bh, gq, c;      // absolute unit, block group inside (batch, KV head), (batch, KV head), query head, chunk
-    int slot;                 // metadata slot of the current (batch, query head)
+    int u, g, bh, c;          // absolute unit, block group inside (batch, KV head), (batch, KV head), channel chunk
+    int slot;                 // metadata slot of the current (batch, KV head)
     size_t row;               // plane row index of (tile 0 of the unit, first channel of the chunk)
 };
 
-template <int KCH, int STAGES>
+template <int KCH, int STAGES, int G>
 __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     using namespace kc;
     constexpr int F_TILE = f_tile(KCH), N_TILE = n_tile(KCH);
@@ -77,7 +82,7 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     const int nch = p.D / KCH;
     const int total = (u_end - u_begin) * nch;
     const size_t tile_f = (size_t)p.D * 64, tile_n = (size_t)p.D * 32;
-    const int G = p.G;
+    const int META = meta_bytes(p.D, G), HMETA = head_meta(p.D);
 
     uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META);
     uint8_t* meta0 = ring + STAGES * STAGE;
@@ -86,31 +91,21 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     auto cursor_at = [&](int u) {
         KCursor k;
         k.u = u;
-        k.gq = u % G;
-        const int ug = u / G;
-        k.bh = ug / p.ngroups;
-        k.g = ug - k.bh * p.ngroups;
+        k.bh = u / p.ngroups;
+        k.g = u - k.bh * p.ngroups;
         k.c = 0;
         k.slot = 0;
         k.row = ((size_t)k.bh * p.nmb + (size_t)k.g * TILES) * p.D;
         return k;
     };
-    auto advance = [&](KCursor& k) {   // next stage; returns true when a new (batch, query head) starts
+    auto advance = [&](KCursor& k) {   // next stage; returns true when a new (batch, KV head) starts
         k.row += KCH;
         if (++k.c < nch) return false;
         k.c = 0;
         ++k.u;
-        if (++k.gq < G) {                                 // same tiles again for the next query head of the group
-            k.row -= (size_t)p.D;
-            k.slot = (k.slot + 1 == NMETA) ? 0 : k.slot + 1;
-            return true;
-        }
-        k.gq = 0;
         if (++k.g < p.ngroups) {
             k.row += (size_t)(TILES - 1) * p.D;          // next 4 tiles of the same (batch, KV head)
-            if (G == 1) return false;
-            k.slot = (k.slot + 1 == NMETA) ? 0 : k.slot + 1;
-            return true;
+            return false;
         }
         k.g = 0;
         ++k.bh;
@@ -118,25 +113,45 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
         k.row = (size_t)k.bh * p.nmb * p.D;
         return true;
     };
-    // Per (batch, query head): plane-read masks (bit d set = row d of that plane is read: mid iff
-    // (u8)(kqmax - kq[d]) < 8, low iff < 4; K_cache.cu:211,249-250) and q as fp16x2 words with both halves equal.
-    auto load_meta = [&](long long bhq, int slot) {
-        uint32_t* masks = reinterpret_cast<uint32_t*>(meta0 + (size_t)slot * META);
-        uint32_t* q2 = masks + 16;
-        const uint32_t top = __ldg(p.kqmax + bhq);
-        for (int r = 0; r < (p.D + 31) / 32; ++r) {
-            const int d = r * 32 + lane;
-            uint32_t diff = 0, qh = 0;
-            if (d < p.D) {
-                diff = (top - (uint32_t)__ldg(p.kq + (size_t)bhq * p.D + d)) & 0xFFu;
-                qh = __ldg(reinterpret_cast<const uint16_t*>(p.q) + (size_t)bhq * p.D + d);
-                q2[d] = qh | (qh << 16);
+    // Per (batch, KV head): for every query head of the group the plane-read masks (bit d set = row d of that plane
+    // is read: mid iff (u8)(kqmax - kq[d]) < 8, low iff < 4; K_cache.cu:211,249-250) and q as fp16x2 words with
+    // both halves equal; and the union of the masks, which is what the producer fetches.
+    auto load_meta = [&](long long bh, int slot) {
+        uint32_t* um = reinterpret_cast<uint32_t*>(meta0 + (size_t)slot * META);
+        uint32_t u_mm[8], u_lm[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) u_mm[r] = u_lm[r] = 0;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const long long bhq = bh * G + g;
+            uint32_t* masks = reinterpret_cast<uint32_t*>(meta0 + (size_t)slot * META + 64 + (size_t)g * HMETA);
+            uint32_t* q2 = masks + 16;
+            const uint32_t top = __ldg(p.kqmax + bhq);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r * 32 >= p.D) break;
+                const int d = r * 32 + lane;
+                uint32_t diff = 0, qh = 0;
+                if (d < p.D) {
+                    diff = (top - (uint32_t)__ldg(p.kq + (size_t)bhq * p.D + d)) & 0xFFu;
+                    qh = __ldg(reinterpret_cast<const uint16_t*>(p.q) + (size_t)bhq * p.D + d);
+                    q2[d] = qh | (qh << 16);
+                }
+                const uint32_t mm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 8);
+                const uint32_t lm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 4);
+                u_mm[r] |= mm;
+                u_lm[r] |= lm;
+                if (lane == 0) {
+                    masks[r] = mm;
+                    masks[8 + r] = lm;
+                }
             }
-            const uint32_t mm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 8);
-            const uint32_t lm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 4);
-            if (lane == 0) {
-                masks[r] = mm;
-                masks[8 + r] = lm;
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                um[r] = u_mm[r];
+                um[8 + r] = u_lm[r];
             }
         }
         __syncwarp();
@@ -148,7 +163,7 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     KCursor pk = cursor_at(u_begin);
     int pstage = 0;
     auto issue = [&]() {
-        const uint32_t* masks = reinterpret_cast<const uint32_t*>(meta0 + (size_t)pk.slot * META);
+        const uint32_t* masks = reinterpret_cast<const uint32_t*>(meta0 + (size_t)pk.slot * META);   // union masks
         const int sh = ((pk.c * KCH) & 31) + nrow, wi = (pk.c * KCH) >> 5;
         const bool need_m = (masks[wi] >> sh) & 1u;
         const bool need_l = (masks[8 + wi] >> sh) & 1u;
@@ -163,29 +178,31 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
         const size_t pn = (pk.row + nrow) * 32 + nhalf;
         const uint32_t nd = st + F_BYTES + nrow * 32 + nhalf;
 #pragma unroll
-        for (int it = 0; it < TILES / TILES_PER_IT; ++it) {   // nibble planes: rows the rule reads, else constants
+        for (int it = 0; it < TILES / TILES_PER_IT; ++it) {   // nibble planes: only the rows some head reads
             const int t = it * TILES_PER_IT + ntsub;
             if (t < ptiles) {
                 const uint32_t dm = nd + t * N_TILE, dl = dm + N_BYTES;
                 if (need_m) cp_async16(dm, p.mid4 + pn + t * tile_n);
-                else st_shared_v4(dm, 0x88888888u);              // plane not read: low byte becomes 0x80
+                else if (G == 1) st_shared_v4(dm, 0x88888888u);              // plane not read: low byte becomes 0x80
                 if (need_l) cp_async16(dl, p.last4 + pn + t * tile_n);
-                else st_shared_v4(dl, need_m ? 0x88888888u : 0u);  // low plane not read: low nibble becomes 8
+                else if (G == 1) st_shared_v4(dl, need_m ? 0x88888888u : 0u);  // low plane not read: low nibble becomes 8
             }
         }
         pstage = (pstage + 1 == STAGES) ? 0 : pstage + 1;
-        if (advance(pk) && pk.u < u_end) load_meta((long long)pk.bh * G + pk.gq, pk.slot);
+        if (advance(pk) && pk.u < u_end) load_meta(pk.bh, pk.slot);
     };
 
     // ---- prologue
-    load_meta((long long)pk.bh * G + pk.gq, 0);
+    load_meta(pk.bh, 0);
     for (int j = 0; j < STAGES - 1; ++j) {
         if (j < total) issue();
         cp_async_commit();
     }
 
     const int tile = lane >> 3, li = lane & 7;
-    uint32_t acc02 = 0, acc13 = 0, acc46 = 0, acc57 = 0;
+    uint32_t acc[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0;
     KCursor ck = cursor_at(u_begin);
     int cstage = 0;
     for (int i = 0; i < total; ++i) {
@@ -199,44 +216,93 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
         const uint2* fp = reinterpret_cast<const uint2*>(stp + tile * F_TILE + li * 8);
         const uint32_t* mp = reinterpret_cast<const uint32_t*>(stp + F_BYTES + tile * N_TILE + li * 4);
         const uint32_t* lp = reinterpret_cast<const uint32_t*>(stp + F_BYTES + N_BYTES + tile * N_TILE + li * 4);
-        const uint4* qp = reinterpret_cast<const uint4*>(meta0 + (size_t)ck.slot * META + 64 + ck.c * (KCH * 4));
+        const uint8_t* hm0 = meta0 + (size_t)ck.slot * META + 64;
+        const int ch0 = ck.c * KCH;                       // first channel of the stage
+        // per head (and for the union): the stage's KCH mask bits of each plane, shifted down to bit 0; `dis` marks the
+        // rows on which some head's code differs from the union's
+        uint32_t mmw[G], lmw[G], ummw = 0, ulmw = 0, dis = 0;
+        if (G > 1) {
+            const uint32_t* um = reinterpret_cast<const uint32_t*>(meta0 + (size_t)ck.slot * META);
+            ummw = um[ch0 >> 5] >> (ch0 & 31);
+            ulmw = um[8 + (ch0 >> 5)] >> (ch0 & 31);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const uint32_t* masks = reinterpret_cast<const uint32_t*>(hm0 + (size_t)g * HMETA);
+            mmw[g] = masks[ch0 >> 5] >> (ch0 & 31);
+            lmw[g] = masks[8 + (ch0 >> 5)] >> (ch0 & 31);
+            dis |= (mmw[g] ^ ummw) | (lmw[g] ^ ulmw);
+        }
 #pragma unroll
         for (int r4 = 0; r4 < KCH / 4; ++r4) {
-            const uint4 qv = qp[r4];
-            const uint32_t q2s[4] = {qv.x, qv.y, qv.z, qv.w};
+            uint4 qv[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+                qv[g] = *reinterpret_cast<const uint4*>(hm0 + (size_t)g * HMETA + 64 + (size_t)(ch0 + r4 * 4) * 4);
 #pragma unroll
             for (int rr = 0; rr < 4; ++rr) {
                 const int r = r4 * 4 + rr;
                 const uint2 f = fp[r * 8];
                 const uint32_t M = mp[r * 8], L = lp[r * 8];
-                const uint32_t lbe = (M & 0xF0F0F0F0u) | ((L >> 4) & 0x0F0F0F0Fu);   // low bytes, tokens 0,2,4,6
-                const uint32_t lbo = ((M << 4) & 0xF0F0F0F0u) | (L & 0x0F0F0F0Fu);   // low bytes, tokens 1,3,5,7
-                acc02 = hfma2_bits(__byte_perm(lbe, f.x, 0x6140), q2s[rr], acc02);
-                acc13 = hfma2_bits(__byte_perm(lbo, f.x, 0x7150), q2s[rr], acc13);
-                acc46 = hfma2_bits(__byte_perm(lbe, f.y, 0x6342), q2s[rr], acc46);
-                acc57 = hfma2_bits(__byte_perm(lbo, f.y, 0x7352), q2s[rr], acc57);
+                if (G == 1 || !((dis >> r) & 1u)) {
+                    // one reassembly serves every head of the group (warp-uniform branch): with G == 1 the producer
+                    // has written the substitutes, else the union's code (= every head's code on this row) picks them
+                    uint32_t Mu = M, Lu = L;
+                    if (G > 1) {
+                        const bool m = (ummw >> r) & 1u, l = (ulmw >> r) & 1u;
+                        Mu = m ? M : 0x88888888u;
+                        Lu = l ? L : (m ? 0x88888888u : 0u);
+                    }
+                    const uint32_t lbe = (Mu & 0xF0F0F0F0u) | ((Lu >> 4) & 0x0F0F0F0Fu);   // low bytes, tokens 0,2,4,6
+                    const uint32_t lbo = ((Mu << 4) & 0xF0F0F0F0u) | (Lu & 0x0F0F0F0Fu);   // low bytes, tokens 1,3,5,7
+                    const uint32_t k0 = __byte_perm(lbe, f.x, 0x6140), k1 = __byte_perm(lbo, f.x, 0x7150);
+                    const uint32_t k2 = __byte_perm(lbe, f.y, 0x6342), k3 = __byte_perm(lbo, f.y, 0x7352);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const uint32_t q2 = rr == 0 ? qv[g].x : rr == 1 ? qv[g].y : rr == 2 ? qv[g].z : qv[g].w;
+                        acc[g][0] = hfma2_bits(k0, q2, acc[g][0]);
+                        acc[g][1] = hfma2_bits(k1, q2, acc[g][1]);
+                        acc[g][2] = hfma2_bits(k2, q2, acc[g][2]);
+                        acc[g][3] = hfma2_bits(k3, q2, acc[g][3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {   // this head's own code: the staged bytes or the substitutes
+                        const bool m = (mmw[g] >> r) & 1u, l = (lmw[g] >> r) & 1u;
+                        const uint32_t Mg = m ? M : 0x88888888u;
+                        const uint32_t Lg = l ? L : (m ? 0x88888888u : 0u);
+                        const uint32_t q2 = rr == 0 ? qv[g].x : rr == 1 ? qv[g].y : rr == 2 ? qv[g].z : qv[g].w;
+                        const uint32_t lbe = (Mg & 0xF0F0F0F0u) | ((Lg >> 4) & 0x0F0F0F0Fu);
+                        const uint32_t lbo = ((Mg << 4) & 0xF0F0F0F0u) | (Lg & 0x0F0F0F0Fu);
+                        acc[g][0] = hfma2_bits(__byte_perm(lbe, f.x, 0x6140), q2, acc[g][0]);
+                        acc[g][1] = hfma2_bits(__byte_perm(lbo, f.x, 0x7150), q2, acc[g][1]);
+                        acc[g][2] = hfma2_bits(__byte_perm(lbe, f.y, 0x6342), q2, acc[g][2]);
+                        acc[g][3] = hfma2_bits(__byte_perm(lbo, f.y, 0x7352), q2, acc[g][3]);
+                    }
+                }
             }
         }
-        const long long cbhq = (long long)ck.bh * G + ck.gq;
+        const long long cbh = ck.bh;
         const int cg = ck.g;
         const bool last_chunk = (ck.c == nch - 1);
         advance(ck);
-        if (last_chunk) {  // unit finished: scale, reorder to token order, one 16-byte store per lane
+        if (last_chunk) {  // unit finished: scale, reorder to token order, one 16-byte store per lane and head
             const int blk = cg * TILES + tile;
-            if (blk < p.nb) {
-                acc02 = hmul2_bits(acc02, p.scale2);
-                acc13 = hmul2_bits(acc13, p.scale2);
-                acc46 = hmul2_bits(acc46, p.scale2);
-                acc57 = hmul2_bits(acc57, p.scale2);
-                uint4 o;
-                o.x = __byte_perm(acc02, acc13, 0x5410);
-                o.y = __byte_perm(acc02, acc13, 0x7632);
-                o.z = __byte_perm(acc46, acc57, 0x5410);
-                o.w = __byte_perm(acc46, acc57, 0x7632);
-                const size_t row = (size_t)cbhq * (size_t)(p.nb + 1) * 64 + (size_t)blk * 64 + li * 8;
-                *reinterpret_cast<uint4*>(p.s + row * 2) = o;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                if (blk < p.nb) {
+                    const uint32_t a0 = hmul2_bits(acc[g][0], p.scale2), a1 = hmul2_bits(acc[g][1], p.scale2);
+                    const uint32_t a2 = hmul2_bits(acc[g][2], p.scale2), a3 = hmul2_bits(acc[g][3], p.scale2);
+                    uint4 o;
+                    o.x = __byte_perm(a0, a1, 0x5410);
+                    o.y = __byte_perm(a0, a1, 0x7632);
+                    o.z = __byte_perm(a2, a3, 0x5410);
+                    o.w = __byte_perm(a2, a3, 0x7632);
+                    const size_t row = (size_t)(cbh * G + g) * (size_t)(p.nb + 1) * 64 + (size_t)blk * 64 + li * 8;
+                    *reinterpret_cast<uint4*>(p.s + row * 2) = o;
+                }
+                acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0;
             }
-            acc02 = acc13 = acc46 = acc57 = 0;
         }
     }
     cp_async_wait<0>();
@@ -283,7 +349,8 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     using namespace kc;
     const __half scale = __float2half_rn(sqrt_dim);
     const bool fast = d_block == 64 && D % 16 == 0 && D >= 64 && D <= MAX_D && aligned16(first8) &&
-                      aligned16(mid4) && aligned16(last4) && aligned16(kq) && aligned16(q) && aligned16(s);
+                      aligned16(mid4) && aligned16(last4) && aligned16(kq) && aligned16(q) && aligned16(s) &&
+                      (group == 1 || group == 2 || group == 4 || group == 8);
     if (!fast) {
         long long total = (long long)bsz * H * group * nb * d_block;
         long long want = (total + 127) / 128;
@@ -298,8 +365,7 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     p.first8 = first8; p.mid4 = mid4; p.last4 = last4; p.kq = kq; p.kqmax = kqmax; p.q = q; p.s = s;
     p.BH = bsz * H; p.nb = nb; p.nmb = nmb; p.D = D;
     p.ngroups = (nb + TILES - 1) / TILES;
-    p.G = group;
-    const long long units = (long long)p.BH * p.ngroups * group;
+    const long long units = (long long)p.BH * p.ngroups;
     AKV_REQUIRE(units < (1ll << 30), AKV_ERR_OVERFLOW, "k_cache_compute: too many blocks");
     p.units = (int)units;
     const unsigned short sb = __half_as_ushort(scale);
@@ -310,8 +376,15 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     // count so that every warp gets (nearly) the same whole number of units.
     const int sms = sm_count();
     const int budget = max_dyn_smem();
-    const int kch = tuning().k_kch, stages = tuning().k_stages;
-    const int per_warp = stages * stage_bytes(kch) + NMETA * META;
+    // (channels per stage, ring depth): the instantiated combinations; anything else falls back to the default of
+    // its group size, and the shared-memory budget below is computed from what is actually launched
+    // groups: 8-channel stages (smaller rings, more warps per SM: the consumer does G times the arithmetic per byte)
+    const int kch = group > 1 ? 8 : tuning().k_kch;
+    int stages = tuning().k_stages;
+    if (group > 1) stages = 4;
+    else if (!((kch == 8 && (stages == 3 || stages == 4 || stages == 6)) || (kch == 16 && stages >= 3 && stages <= 5)))
+        stages = (kch == 8) ? 4 : 3;
+    const int per_warp = stages * stage_bytes(kch) + NMETA * meta_bytes(D, group);
     int wmax = budget / per_warp;
     if (wmax > 16) wmax = 16;
     if (tuning().k_wpc > 0 && tuning().k_wpc < wmax) wmax = tuning().k_wpc;
@@ -338,13 +411,24 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
         return AKV_OK;
     };
     int rc;
-    switch (kch * 10 + stages) {
-        case 83: rc = go(k_compute_kernel<8, 3>); break;
-        case 84: rc = go(k_compute_kernel<8, 4>); break;
-        case 86: rc = go(k_compute_kernel<8, 6>); break;
-        case 164: rc = go(k_compute_kernel<16, 4>); break;
-        case 165: rc = go(k_compute_kernel<16, 5>); break;
-        default: rc = go(k_compute_kernel<16, 3>); break;
+    if (group == 1) {
+        switch (kch * 10 + stages) {
+            case 83: rc = go(k_compute_kernel<8, 3, 1>); break;
+            case 84: rc = go(k_compute_kernel<8, 4, 1>); break;
+            case 86: rc = go(k_compute_kernel<8, 6, 1>); break;
+            case 164: rc = go(k_compute_kernel<16, 4, 1>); break;
+            case 165: rc = go(k_compute_kernel<16, 5, 1>); break;
+            case 163: rc = go(k_compute_kernel<16, 3, 1>); break;
+            default:
+                set_error("k_cache_compute: no kernel for %d channels x %d stages", kch, stages);
+                return AKV_ERR_SHAPE;
+        }
+    } else if (group == 2) {
+        rc = (kch == 8) ? go(k_compute_kernel<8, 4, 2>) : go(k_compute_kernel<16, 3, 2>);
+    } else if (group == 4) {
+        rc = (kch == 8) ? go(k_compute_kernel<8, 4, 4>) : go(k_compute_kernel<16, 3, 4>);
+    } else {
+        rc = (kch == 8) ? go(k_compute_kernel<8, 4, 8>) : go(k_compute_kernel<16, 3, 8>);
     }
     if (rc != AKV_OK) return rc;
     return cuda_status(cudaGetLastError(), "k_cache_compute launch");
