@@ -130,7 +130,7 @@ struct VPlan {
     // nobody reads that F slot, its records or its probability words any more.
     static constexpr int AHEADP = NF / 2 - NR / 2 - 1;
     static_assert(NF % 2 == 0 && NR % 2 == 0 && AHEADP >= 1 && NF + NR + 4 < vc::SCH, "ring sizes");
-    static_assert(PEND_BYTES % 16 == 0, "alignment");
+    static_assert(PEND_BYTES % 16 == 0 && RDY_OFF % 128 == 0 && W_BYTES % 128 == 0, "alignment");
 };
 
 // 16-byte chunk k (tokens 8k..8k+7) of pair c's row in a [pair][token] array: swizzled so that a quarter-warp of
@@ -166,14 +166,16 @@ __device__ __forceinline__ void v_run_impl(uint32_t& acc, const uint32_t (&KC)[3
                                            uint32_t (&KN)[32], uint4 (&SN)[8], uint32_t hi_a, uint32_t lo_a, uint32_t s_a,
                                            int c, int k0) {
     uint4 H[4], L[4];
+    // v_chunk(c, k) = v_chunk(c, 0) ^ (k << 4): the arrays are 128-byte aligned, so one XOR per load addresses a chunk
+    const uint32_t hx = hi_a + v_chunk(c, 0), lx = lo_a + v_chunk(c, 0);
 #pragma unroll
     for (int v = 0; v < 8; ++v) {          // 4 tokens per step
         if (FETCH) {
             SN[v] = lds128(s_a + v * 16);
             if (v < 4) {
-                H[v] = lds128(hi_a + v_chunk(c, k0 + v));
+                H[v] = lds128(hx ^ (uint32_t)((k0 + v) << 4));
                 L[v] = LEAN ? make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u)
-                            : lds128(lo_a + v_chunk(c, k0 + v));
+                            : lds128(lx ^ (uint32_t)((k0 + v) << 4));
             } else {
                 const int i = v - 4;       // chunk i: word m holds tokens 8i+2m, 8i+2m+1
 #pragma unroll
@@ -254,15 +256,6 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
         for (int j = 0; j < nsf && alive; ++j) {
             const int nrs = rs + 1 == NR ? 0 : rs + 1, nfs = fs + 1 == NF ? 0 : fs + 1;
             const uint32_t nphase = rs + 1 == NR ? phase ^ 1 : phase;
-            const bool more = j + 1 < nsf;
-            // the next stage is looked at a run early, so that its flags are in registers when they are needed
-            uint32_t nflag = 0, nfl1 = 0;
-            if (more) {
-                alive = mbar_wait(bar_ready + nrs * 8, nphase);
-                if (!alive) break;
-                nflag = flag(nfs, 0);
-                nfl1 = flag(nfs, 1);
-            }
             // first run of stage j while its second run is fetched
             v_run<true>(acc, kA, sA, kB, sB, rdy(rs), rdy(rs) + P::R_LO + g * P::W_BYTES,
                         pend(fs) + P::P_S2 + (g * TOK + vc::RUN) * 4, c, 4, fl1);
@@ -270,14 +263,18 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
             // probability words) back
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_free + rs * 8);
-            // second run of stage j while the first run of stage j+1 is fetched
-            if (more)
+            // second run of stage j while the first run of stage j+1 is fetched.  The wait for stage j+1 comes as
+            // late as this: between handing back a slot and needing its next content lie two runs, which is about
+            // the time the producer pair needs to wake up and transform a stage (one run was not enough).
+            if (j + 1 < nsf) {
+                alive = mbar_wait(bar_ready + nrs * 8, nphase);
+                if (!alive) break;
+                fl1 = flag(nfs, 1);
                 v_run<true>(acc, kB, sB, kA, sA, rdy(nrs), rdy(nrs) + P::R_LO + g * P::W_BYTES,
-                            pend(nfs) + P::P_S2 + g * TOK * 4, c, 0, nflag);
-            else
+                            pend(nfs) + P::P_S2 + g * TOK * 4, c, 0, flag(nfs, 0));
+            } else
                 v_run<false>(acc, kB, sB, kA, sA, 0, 0, 0, c, 0, 0);
             rs = nrs; fs = nfs; phase = nphase;
-            fl1 = nfl1;
         }
         if (tail > 0 && alive) {
             // last, partial stage: token by token from the ready slot
