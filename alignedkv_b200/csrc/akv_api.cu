@@ -3,6 +3,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "akv_common.cuh"
 
 namespace akv {
@@ -40,6 +42,9 @@ static DevInfo dev_info() {
 static Tuning g_tuning;
 Tuning& tuning() { return g_tuning; }
 
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
 int sm_count() { return dev_info().sms; }
 int max_dyn_smem() { return dev_info().smem; }
 
@@ -73,6 +78,8 @@ extern "C" {
 int akv_abi_version(void) { return 1; }
 
 const char* akv_last_error(void) { return g_err; }
+
+long long akv_launch_count(void) { return akv::launches(); }
 
 int akv_set_tuning(const char* key, int value) {
     g_err[0] = 0;

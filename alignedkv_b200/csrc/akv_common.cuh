@@ -13,6 +13,7 @@ void set_error(const char* fmt, ...);
 int cuda_status(cudaError_t e, const char* what);
 int sm_count();          // SMs of the current device (cached per device)
 int max_dyn_smem();      // opt-in dynamic shared memory per block of the current device
+void count_launch(int n = 1);   // every kernel launch of this library is counted (akv_launch_count)
 
 // Launch-shape knobs (defaults are the measured best on B200); see akv_set_tuning().
 struct Tuning {
@@ -56,6 +57,7 @@ static inline cudaError_t launch_chained(Kernel kernel, dim3 grid, dim3 block, s
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = tuning().pdl ? 1 : 0;
+    count_launch();
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
@@ -112,6 +114,27 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
     return d;
+}
+
+// Threshold byte of P.V for flat row i = b*Hq + h of the reference's [B,Hq,Hq,1] tensor, computed by one warp:
+// min_d ((exp(test_o[bb, hp, d]) & 0x1E) + 15 - v_exp[bb, he, d]) mod 256 with bb = i / (Hq*Hq), hp = (i / Hq) % Hq,
+// he = i % Hq (extension/v_cache_file.py:142,156-160).  The exponent maxima are stored per KV head; query head he
+// belongs to KV head he / G (for G > 1 this is the reference's rule applied to the cache with its KV heads repeated
+// G times).  Every lane returns the result.
+__device__ __forceinline__ uint32_t v_threshold_warp(const uint16_t* __restrict__ test_o,
+                                                     const uint8_t* __restrict__ v_exp, long long i, int H, int G,
+                                                     int D, int lane) {
+    const long long Hq = (long long)H * G;
+    const long long bb = i / (Hq * Hq), hp = (i / Hq) % Hq, he = i % Hq;
+    uint32_t m = 255;
+    for (int d = lane; d < D; d += 32) {
+        const uint32_t e = ((uint32_t)test_o[(size_t)(bb * Hq + hp) * D + d] >> 10) & 0x1Eu;
+        const uint32_t a = (e + 15u - v_exp[(size_t)(bb * H + he / G) * D + d]) & 0xFFu;
+        m = min(m, a);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    return m;
 }
 
 }  // namespace akv

@@ -21,6 +21,10 @@ int launch_k_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8
                      const uint8_t*, uint8_t*, int, int, int, int, int, int, int, float, int, cudaStream_t);
 int launch_v_compute(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*,
                      int, int, int, int, int, int, int, int, cudaStream_t);
+bool v_compute_takes_probe(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, int, int, int,
+                           int);
+int launch_v_compute_probe(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, const uint8_t*,
+                           const uint8_t*, uint8_t*, int, int, int, int, int, int, int, int, cudaStream_t);
 int launch_v_split(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, float*,
                    float*, int, int, int, int, int, int, int, int, cudaStream_t);
 long long v_split_scratch_bytes(int, int, int, int);
@@ -162,11 +166,20 @@ append_flush_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, 
     }
 }
 
-// ------------------------------------------------------------------ softmax (+ residual scores, class maxima)
+// ------------------------------------------------------------------ softmax (+ residual scores, class maxima, probe)
 // grid B*Hq, block 256.  Row = [0, qn) aligned scores | [qn, qn+rest) residual scores | -inf up to R.
+// CACHED: the row has at most 256*SM_REGS scores and every thread keeps its share in registers, so the row is read
+// from memory once instead of three times.  The per-thread and cross-thread summation order is the same either way.
+// PROBE (and first8 != nullptr): the magnitude probe (V_cache.cu:104-119; see v_probe_kernel) of this row follows in
+// the same CTA from the class maxima it has just found, and lands in test_o.  Both forms pay when the grid is a wave
+// or two and the step is bound by the latency of its kernel chain; with many rows the plain form plus a separate
+// probe launch keeps more CTAs per SM and is faster.
+constexpr int SM_REGS = 32;
+template <bool CACHED, bool PROBE>
 __global__ void __launch_bounds__(256)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
-               uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats, int H, int G, int D,
+               uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats,
+               const uint8_t* __restrict__ first8, uint16_t* __restrict__ test_o, int max_seq_len, int H, int G, int D,
                int R, int qn, int rest, float sqrt_d) {
     __shared__ float redf[8];
     __shared__ uint32_t cand_v[256];
@@ -188,9 +201,19 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
         if (lane == 0) row[qn + r] = __half_as_ushort(__float2half_rn(__half2float(__float2half_rn(acc)) / sqrt_d));
     }
     __syncthreads();
+    float x[CACHED ? SM_REGS : 1];
     // pass 1: maximum
     float m = -INFINITY;
-    for (int t = tid; t < len; t += 256) m = fmaxf(m, __half2float(__ushort_as_half(row[t])));
+    if (CACHED) {
+#pragma unroll
+        for (int i = 0; i < SM_REGS; ++i) {
+            const int t = tid + 256 * i;
+            x[i] = t < len ? __half2float(__ushort_as_half(row[t])) : -INFINITY;
+            m = fmaxf(m, x[i]);
+        }
+    } else {
+        for (int t = tid; t < len; t += 256) m = fmaxf(m, __half2float(__ushort_as_half(row[t])));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
     if (lane == 0) redf[warp] = m;
@@ -201,7 +224,17 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     __syncthreads();
     // pass 2: sum of exponentials (fp32, as F.softmax(scores.float()) does; model/KVCache_AlignedKV.py:121)
     float sum = 0.f;
-    for (int t = tid; t < len; t += 256) sum += expf(__half2float(__ushort_as_half(row[t])) - m);
+    if (CACHED) {
+#pragma unroll
+        for (int i = 0; i < SM_REGS; ++i) {
+            if (tid + 256 * i < len) {
+                x[i] = expf(x[i] - m);
+                sum += x[i];
+            }
+        }
+    } else {
+        for (int t = tid; t < len; t += 256) sum += expf(__half2float(__ushort_as_half(row[t])) - m);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
     if (lane == 0) redf[warp] = sum;
@@ -217,13 +250,29 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     // tokens with its first position (torch.max over the group axis keeps the first maximum; v_cache_file.py:128-130)
     uint32_t best = 0;
     int32_t best_g = 0;
-    for (int t = tid; t < R; t += 256) {
-        uint16_t pb = 0;   // exp(-inf - m) = 0
-        if (t < len) pb = __half_as_ushort(__float2half_rn(expf(__half2float(__ushort_as_half(row[t])) - m) / sum));
-        row[t] = pb;
-        if (t < qn && pb > best) {   // probabilities are non-negative: their bit patterns order like their values
-            best = pb;
-            best_g = t >> 5;
+    if (CACHED) {
+#pragma unroll
+        for (int i = 0; i < SM_REGS; ++i) {
+            const int t = tid + 256 * i;
+            if (t < R) {
+                uint16_t pb = 0;   // exp(-inf - m) = 0
+                if (t < len) pb = __half_as_ushort(__float2half_rn(x[i] / sum));
+                row[t] = pb;
+                if (t < qn && pb > best) {   // probabilities are non-negative: bit patterns order like values
+                    best = pb;
+                    best_g = t >> 5;
+                }
+            }
+        }
+    } else {
+        for (int t = tid; t < R; t += 256) {
+            uint16_t pb = 0;
+            if (t < len) pb = __half_as_ushort(__float2half_rn(expf(__half2float(__ushort_as_half(row[t])) - m) / sum));
+            row[t] = pb;
+            if (t < qn && pb > best) {
+                best = pb;
+                best_g = t >> 5;
+            }
         }
     }
     cand_v[tid] = best;
@@ -239,6 +288,31 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
         }
         pval[(size_t)bhq * TOPK + tid] = (uint16_t)bv;
         pidx[(size_t)bhq * TOPK + tid] = bi;
+        if (PROBE) {
+            cand_v[tid] = bv;
+            cand_i[tid] = bi;
+        }
+    }
+    if (!PROBE || first8 == nullptr || qn == 0) return;   // (uniform)
+    __syncthreads();
+    // probe: o_test[d] = sum_j |half((first_8[row_j][d] << 8) + 0x80)| * p_j over the class maxima, rows
+    // row_j = class position * 32 + j, accumulated in fp16 in j order; all row gathers go out before the chain starts
+    const uint8_t* F = first8 + (size_t)(bhq / G) * max_seq_len * D;
+    for (int c = tid; c < (D >> 1); c += 256) {
+        uint32_t f[TOPK];
+#pragma unroll
+        for (int j = 0; j < TOPK; ++j) {
+            long long r = (long long)cand_i[j] * TOPK + j;
+            r = r >= max_seq_len ? max_seq_len - 1 : r;
+            f[j] = __ldg(reinterpret_cast<const uint16_t*>(F + (size_t)r * D + 2 * c));
+        }
+        uint32_t acc = 0;
+#pragma unroll
+        for (int j = 0; j < TOPK; ++j) {
+            const uint32_t v = __byte_perm(f[j], 0x80u, 0x1404) & 0x7FFF7FFFu;
+            acc = hfma2_bits(v, cand_v[j] | (cand_v[j] << 16), acc);
+        }
+        reinterpret_cast<uint32_t*>(test_o)[(size_t)bhq * (D >> 1) + c] = acc;
     }
 }
 
@@ -364,26 +438,15 @@ softmax_class_reduce_kernel(const float* __restrict__ cstat, const uint32_t* __r
 }
 
 // ------------------------------------------------------------------ threshold byte per (batch, query head)
-// amin[i] = min_d ((exp(test_o[bb, hp, d]) & 0x1E) + 15 - v_exp[bb, he, d]) mod 256 with i = b*Hq + h read flat from
-// the reference's [B,Hq,Hq,1] tensor: bb = i / (Hq*Hq), hp = (i / Hq) % Hq, he = i % Hq (v_cache_file.py:142,156-160).
-// The exponent maxima are stored per KV head; query head he belongs to KV head he / G (for G > 1 this is the
-// reference's rule applied to the cache with its KV heads repeated G times).
+// One warp per row (v_threshold_warp).  Used when the P.V kernel that follows does not compute the byte itself.
 __global__ void __launch_bounds__(128)
 amin_kernel(const uint16_t* __restrict__ test_o, const uint8_t* __restrict__ v_exp, uint8_t* __restrict__ amin,
             int BHq, int H, int G, int D) {
     pdl_enter();
     const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (i >= BHq) return;
-    const int lane = threadIdx.x & 31, Hq = H * G;
-    const int bb = i / (Hq * Hq), hp = (i / Hq) % Hq, he = i % Hq;
-    uint32_t m = 255;
-    for (int d = lane; d < D; d += 32) {
-        const uint32_t e = (test_o[((size_t)bb * Hq + hp) * D + d] >> 10) & 0x1Eu;
-        const uint32_t a = (e + 15u - v_exp[((size_t)bb * H + he / G) * D + d]) & 0xFFu;
-        m = min(m, a);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    const int lane = threadIdx.x & 31;
+    const uint32_t m = v_threshold_warp(test_o, v_exp, i, H, G, D, lane);
     if (lane == 0) amin[i] = (uint8_t)m;
 }
 
@@ -588,40 +651,66 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
     // one CTA per row while there are enough rows to fill the GPU or the rows are short (three launches cost more
     // than they save below ~16k scores); else the split form
     const int sm_chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
+    bool probed = false;
     if (sm_chunks >= 4 && B * H * G < 2 * sm_count()) {
         dim3 grid(sm_chunks, B * H * G);
+        count_launch();
         softmax_chunk_stats_kernel<<<grid, 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
                                                         static_cast<const __half*>(restk), sc.cstat, H, G, D, R, qn, rest,
                                                         sqrtf((float)D), sm_chunks);
+        count_launch();
         softmax_chunk_write_kernel<<<grid, 256, 0, st>>>(sc.s, sc.cstat, sc.cand_val, sc.cand_idx, R, qn, qn + rest,
                                                         sm_chunks);
+        count_launch();
         softmax_class_reduce_kernel<<<B * H * G, 32, 0, st>>>(sc.cstat, sc.cand_val, sc.cand_idx, sc.pval, sc.pidx,
                                                              sc.stats, sm_chunks);
     } else {
-        launch_chained(softmax_kernel, dim3(B * H * G), dim3(256), 0, st, sc.s, static_cast<const __half*>(q),
-                       static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats, H, G, D, R, qn, rest,
-                       sqrtf((float)D));
+        if (R <= 256 * SM_REGS && B * H * G <= 4 * sm_count()) {
+            // few rows: one pass over the row, and the probe runs inside the softmax CTA of its row
+            launch_chained(softmax_kernel<true, true>, dim3(B * H * G), dim3(256), 0, st, sc.s,
+                           static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
+                           static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn, rest,
+                           sqrtf((float)D));
+            probed = true;
+        } else {
+            launch_chained(softmax_kernel<false, false>, dim3(B * H * G), dim3(256), 0, st, sc.s,
+                           static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
+                           (const uint8_t*)nullptr, (uint16_t*)nullptr, max_seq_len, H, G, D, R, qn, rest,
+                           sqrtf((float)D));
+        }
     }
     if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
     const bool need_tail = rest > 0 || qn == 0 || packed_out != nullptr || order_free;
     if (qn > 0) {
-        rc = launch_v_probe(static_cast<const uint8_t*>(v_first_8), reinterpret_cast<const uint8_t*>(sc.pval),
-                            reinterpret_cast<const uint8_t*>(sc.pidx), reinterpret_cast<uint8_t*>(sc.test_o), B, H, G,
-                            max_seq_len, D, TOPK, st);
-        if (rc != AKV_OK) return rc;
-        launch_chained(amin_kernel, dim3((B * H * G + 3) / 4), dim3(128), 0, st, (const uint16_t*)sc.test_o,
-                       static_cast<const uint8_t*>(v_exp_max), sc.amin, B * H * G, H, G, D);
-        if ((rc = cuda_status(cudaGetLastError(), "decode_step threshold launch")) != AKV_OK) return rc;
+        if (!probed) {
+            rc = launch_v_probe(static_cast<const uint8_t*>(v_first_8), reinterpret_cast<const uint8_t*>(sc.pval),
+                                reinterpret_cast<const uint8_t*>(sc.pidx), reinterpret_cast<uint8_t*>(sc.test_o), B, H,
+                                G, max_seq_len, D, TOPK, st);
+            if (rc != AKV_OK) return rc;
+        }
+        // the exact-order kernel derives the threshold bytes from the probe result in its prologue when it runs its
+        // streaming form; otherwise a small kernel does
+        const bool v_takes_probe = !order_free && v_compute_takes_probe(static_cast<const uint8_t*>(v_first_8),
+            static_cast<const uint8_t*>(v_mid_4), static_cast<const uint8_t*>(v_last_4),
+            reinterpret_cast<const uint8_t*>(sc.s), need_tail ? (const uint8_t*)sc.o_main : (const uint8_t*)out, G, D, R,
+            qn);
+        if (!v_takes_probe) {
+            launch_chained(amin_kernel, dim3((B * H * G + 3) / 4), dim3(128), 0, st, (const uint16_t*)sc.test_o,
+                           static_cast<const uint8_t*>(v_exp_max), sc.amin, B * H * G, H, G, D);
+            if ((rc = cuda_status(cudaGetLastError(), "decode_step threshold launch")) != AKV_OK) return rc;
+        }
         if (ev) cudaEventRecord(ev[2], st);
         if (order_free)
             rc = launch_v_split(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
                                 static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
                                 nullptr, sc.o_main32, sc.partial, B, H, G, max_seq_len, D, R, qn, reference, st);
         else
-            rc = launch_v_compute(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
-                                  static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
-                                  reinterpret_cast<uint8_t*>(need_tail ? (void*)sc.o_main : out), B, H, G, max_seq_len,
-                                  D, R, qn, reference, st);
+            rc = launch_v_compute_probe(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                                        static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s),
+                                        sc.amin, v_takes_probe ? (const uint8_t*)sc.test_o : nullptr,
+                                        static_cast<const uint8_t*>(v_exp_max),
+                                        reinterpret_cast<uint8_t*>(need_tail ? (void*)sc.o_main : out), B, H, G,
+                                        max_seq_len, D, R, qn, reference, st);
         if (ev) cudaEventRecord(ev[3], st);
         if (rc != AKV_OK) return rc;
     } else if (order_free) {

@@ -355,6 +355,7 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
         long long total = (long long)bsz * H * group * nb * d_block;
         long long want = (total + 127) / 128;
         int grid = (int)(want < (long long)sm_count() * 16 ? want : (long long)sm_count() * 16);
+        count_launch();
         k_compute_generic_kernel<<<grid, 128, 0, st>>>(first8, mid4, last4, kq, kqmax,
                                                        reinterpret_cast<const __half*>(q),
                                                        reinterpret_cast<__half*>(s), nb, nmb, D, d_block, group,

@@ -125,6 +125,7 @@ int akv_prefill(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8,
         if (e != cudaSuccess) return cuda_status(e, "prefill smem attribute");
     }
     dim3 grid(tiles, H, B);
+    count_launch(2);
     prefill_kernel<<<grid, 128, smem, st>>>(
         static_cast<uint8_t*>(k_first_8), static_cast<uint8_t*>(k_mid_4), static_cast<uint8_t*>(k_last_4),
         static_cast<uint8_t*>(v_first_8), static_cast<uint8_t*>(v_mid_4), static_cast<uint8_t*>(v_last_4),

@@ -61,6 +61,7 @@ int launch_v_save(uint8_t* first8, uint8_t* mid4, uint8_t* last4, const uint8_t*
     long long want = (total + 255) / 256;
     int grid = (int)(want < (long long)sm_count() * 8 ? want : (long long)sm_count() * 8);
     if (grid < 1) grid = 1;
+    count_launch();
     if (vec)
         v_save_vec_kernel<<<grid, 256, 0, st>>>(first8, mid4, last4, v_new, H, max_seq_len, D, start_pos, seq_len,
                                                 v_new_tokens, total);
@@ -152,12 +153,14 @@ int launch_k_save(uint8_t* first8, uint8_t* mid4, uint8_t* last4, const uint8_t*
             }
             dim3 grid(n_blocks, H, bsz);
             int threads = D < 256 ? ((D + 31) / 32) * 32 : 256;
+            count_launch();
             k_save_block64_kernel<64><<<grid, threads, smem, st>>>(first8, mid4, last4, k_new, H, n_max_blocks, D,
                                                                    blk0, seqlen);
         } else {
             long long total = (long long)bsz * H * n_blocks * D;
             long long want = (total + 127) / 128;
             int grid = (int)(want < (long long)sm_count() * 16 ? want : (long long)sm_count() * 16);
+            count_launch();
             k_save_rows_kernel<<<grid, 128, 0, st>>>(first8, mid4, last4, k_new, H, n_blocks, n_max_blocks, D,
                                                      d_block, blk0, seqlen, total);
         }
@@ -168,6 +171,7 @@ int launch_k_save(uint8_t* first8, uint8_t* mid4, uint8_t* last4, const uint8_t*
         long long total = (long long)bsz * H * D;
         long long want = (total + 127) / 128;
         int grid = (int)(want < (long long)sm_count() * 16 ? want : (long long)sm_count() * 16);
+        count_launch();
         k_save_token_kernel<<<grid, 128, 0, st>>>(first8, mid4, last4, k_new, H, n_max_blocks, D, d_block, blk,
                                                   slot, total);
         return cuda_status(cudaGetLastError(), "k_cache_save launch");

@@ -42,6 +42,12 @@ struct VParams {
     const uint8_t* last4;
     const uint16_t* s;      // probabilities, one row per (batch, query head)
     const uint8_t* amin;    // threshold byte per (batch, query head)
+    // test_o != nullptr: the kernel computes the threshold bytes itself from the probe result [B,Hq,D] and the
+    // exponent maxima [B,H,D] (v_threshold_warp) and stores them to amin_out
+    const uint16_t* test_o;
+    const uint8_t* v_exp;
+    uint8_t* amin_out;
+    int H;                  // KV heads
     uint16_t* o;            // [B, Hq, D]
     int max_seq_len, D, s_last_dim, n, reference;
     int group;              // query heads per KV head (1 = multi-head attention)
@@ -157,45 +163,60 @@ __device__ __forceinline__ void v_store_transposed(const uint4 (&R)[8], uint32_t
     }
 }
 
+// 16-byte shared load that is only issued when `on` is non-zero; otherwise v keeps its value.
+__device__ __forceinline__ void lds128_if(uint4& v, uint32_t a, uint32_t on) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %5, 0;\n@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n}\n"
+                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w) : "r"(a), "r"(on));
+}
+
+// Low words of the run being fetched.  While runs are lean (no token of the run reads a nibble plane for this head)
+// the registers simply keep the constant 0x80 bytes; they are refilled only when a lean run follows one that was not.
+struct VLow {
+    uint4 L[4];
+    uint32_t dirty;
+    __device__ __forceinline__ void fill() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) L[i] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+        dirty = 0;
+    }
+};
+
 // One run of 32 tokens of the chain.  KC / SC: the current run's k~ words [lo_even, f_even, lo_odd, f_odd] and
 // probability words.  KN / SN receive the next run's: its 16-byte loads are written between the first sixteen FMAs and
 // the byte permutes that build k~ between the last sixteen, so that all of it issues in the FMAs' latency shadow and
-// the next run starts with operands that are ready.  FETCH == false: last run, nothing to load.
-template <bool FETCH, bool LEAN>
-__device__ __forceinline__ void v_run_impl(uint32_t& acc, const uint32_t (&KC)[32], const uint4 (&SC)[8],
-                                           uint32_t (&KN)[32], uint4 (&SN)[8], uint32_t hi_a, uint32_t lo_a, uint32_t s_a,
-                                           int c, int k0) {
-    uint4 H[4], L[4];
+// the next run starts with operands that are ready.  FETCH == false: last run, nothing to load.  not_lean == 0
+// (warp-uniform): the loads of the next run's low words are not issued and its low bytes are the constant 0x80 -
+// one code path either way, which keeps the loop small enough for the instruction cache next to the producers' code.
+template <bool FETCH>
+__device__ __forceinline__ void v_run(uint32_t& acc, const uint32_t (&KC)[32], const uint4 (&SC)[8], uint32_t (&KN)[32],
+                                      uint4 (&SN)[8], VLow& low, uint32_t hi_a, uint32_t lo_a, uint32_t s_a, int c,
+                                      int k0, uint32_t not_lean) {
+    uint4 H[4];
     // v_chunk(c, k) = v_chunk(c, 0) ^ (k << 4): the arrays are 128-byte aligned, so one XOR per load addresses a chunk
     const uint32_t hx = hi_a + v_chunk(c, 0), lx = lo_a + v_chunk(c, 0);
+    if (FETCH) {
+        if (not_lean == 0 && low.dirty) low.fill();   // (warp-uniform, rare)
+        low.dirty |= not_lean;
+    }
 #pragma unroll
     for (int v = 0; v < 8; ++v) {          // 4 tokens per step
         if (FETCH) {
             SN[v] = lds128(s_a + v * 16);
             if (v < 4) {
                 H[v] = lds128(hx ^ (uint32_t)((k0 + v) << 4));
-                L[v] = LEAN ? make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u)
-                            : lds128(lx ^ (uint32_t)((k0 + v) << 4));
+                lds128_if(low.L[v], lx ^ (uint32_t)((k0 + v) << 4), not_lean);
             } else {
                 const int i = v - 4;       // chunk i: word m holds tokens 8i+2m, 8i+2m+1
 #pragma unroll
                 for (int m = 0; m < 4; ++m) {
-                    KN[8 * i + 2 * m] = __byte_perm(u4w(H[i], m), u4w(L[i], m), 0x1504);
-                    KN[8 * i + 2 * m + 1] = __byte_perm(u4w(H[i], m), u4w(L[i], m), 0x3726);
+                    KN[8 * i + 2 * m] = __byte_perm(u4w(H[i], m), u4w(low.L[i], m), 0x1504);
+                    KN[8 * i + 2 * m + 1] = __byte_perm(u4w(H[i], m), u4w(low.L[i], m), 0x3726);
                 }
             }
         }
 #pragma unroll
         for (int w = 0; w < 4; ++w) acc = hfma2_bits(KC[4 * v + w], u4w(SC[v], w), acc);
     }
-}
-
-template <bool FETCH>
-__device__ __forceinline__ void v_run(uint32_t& acc, const uint32_t (&KC)[32], const uint4 (&SC)[8], uint32_t (&KN)[32],
-                                      uint4 (&SN)[8], uint32_t hi_a, uint32_t lo_a, uint32_t s_a, int c, int k0,
-                                      uint32_t not_lean) {
-    if (!FETCH || not_lean == 0) v_run_impl<FETCH, true>(acc, KC, SC, KN, SN, hi_a, lo_a, s_a, c, k0);   // (warp-uniform)
-    else v_run_impl<FETCH, false>(acc, KC, SC, KN, SN, hi_a, lo_a, s_a, c, k0);
 }
 
 template <int D, int G, int NF, int NR, int NML>
@@ -233,6 +254,8 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
         uint32_t acc = 0;
         uint32_t kA[32], kB[32];
         uint4 sA[8], sB[8];
+        VLow low;
+        low.fill();
 #pragma unroll
         for (int u = 0; u < 32; ++u) kA[u] = kB[u] = 0;
 #pragma unroll
@@ -249,7 +272,7 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
             alive = mbar_wait(bar_ready, 0);
             if (alive) {   // (a chain over zeros) fetch run 0 of stage 0
                 fl1 = flag(0, 1);
-                v_run<true>(acc, kB, sB, kA, sA, rdy(0), rdy(0) + P::R_LO + g * P::W_BYTES,
+                v_run<true>(acc, kB, sB, kA, sA, low, rdy(0), rdy(0) + P::R_LO + g * P::W_BYTES,
                             pend(0) + P::P_S2 + g * TOK * 4, c, 0, flag(0, 0));
             }
         }
@@ -257,7 +280,7 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
             const int nrs = rs + 1 == NR ? 0 : rs + 1, nfs = fs + 1 == NF ? 0 : fs + 1;
             const uint32_t nphase = rs + 1 == NR ? phase ^ 1 : phase;
             // first run of stage j while its second run is fetched
-            v_run<true>(acc, kA, sA, kB, sB, rdy(rs), rdy(rs) + P::R_LO + g * P::W_BYTES,
+            v_run<true>(acc, kA, sA, kB, sB, low, rdy(rs), rdy(rs) + P::R_LO + g * P::W_BYTES,
                         pend(fs) + P::P_S2 + (g * TOK + vc::RUN) * 4, c, 4, fl1);
             // both runs of the stage are in registers: hand the ready slot (and with it the F slot's records and
             // probability words) back
@@ -270,10 +293,10 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
                 alive = mbar_wait(bar_ready + nrs * 8, nphase);
                 if (!alive) break;
                 fl1 = flag(nfs, 1);
-                v_run<true>(acc, kB, sB, kA, sA, rdy(nrs), rdy(nrs) + P::R_LO + g * P::W_BYTES,
+                v_run<true>(acc, kB, sB, kA, sA, low, rdy(nrs), rdy(nrs) + P::R_LO + g * P::W_BYTES,
                             pend(nfs) + P::P_S2 + g * TOK * 4, c, 0, flag(nfs, 0));
             } else
-                v_run<false>(acc, kB, sB, kA, sA, 0, 0, 0, c, 0, 0);
+                v_run<false>(acc, kB, sB, kA, sA, low, 0, 0, 0, c, 0, 0);
             rs = nrs; fs = nfs; phase = nphase;
         }
         if (tail > 0 && alive) {
@@ -303,7 +326,16 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
     const uint16_t* s_rows = p.s + (size_t)bh * G * p.s_last_dim;
     uint32_t A[G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) A[g] = ((uint32_t)p.amin[bh * G + g] << 10) & 0xFFFFu;
+    for (int g = 0; g < G; ++g) {
+        uint32_t a;
+        if (p.test_o) {
+            a = v_threshold_warp(p.test_o, p.v_exp, bh * G + g, p.H, G, D, lane);
+            if (pt == 0) p.amin_out[bh * G + g] = (uint8_t)a;
+        } else {
+            a = p.amin[bh * G + g];
+        }
+        A[g] = (a << 10) & 0xFFFFu;
+    }
     // probability chunk c (stages 16c .. 16c+15 of every head) -> buffer c % 3; issued by one thread
     auto request_s = [&](int c) {
         const int t0 = c * vc::SCH * TOK;
@@ -498,22 +530,32 @@ static int launch_v_fast(const VParams& p, int BH, cudaStream_t st) {
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
 }
 
+// true when launch_v_compute_probe runs the streaming kernel, which can compute the threshold bytes itself
+bool v_compute_takes_probe(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                           const uint8_t* o, int group, int D, int s_last_dim, int n) {
+    return D == 128 && (group == 1 || group == 2 || group == 4) && aligned16(first8) && aligned16(mid4) &&
+           aligned16(last4) && (n == 0 || (aligned16(s) && s_last_dim % 8 == 0 && ((n + 7) & ~7) <= s_last_dim)) &&
+           ((reinterpret_cast<uintptr_t>(o) & 3u) == 0);
+}
+
 // P.V over n quantized tokens.  H = KV heads, group = query heads per KV head; s rows, amin bytes and output rows
-// are per (batch, query head) with query head = KV head * group + g.
-int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
-                     const uint8_t* amin, uint8_t* o, int bsz, int H, int group, int max_seq_len, int D,
-                     int s_last_dim, int n, int reference, cudaStream_t st) {
+// are per (batch, query head) with query head = KV head * group + g.  test_o != nullptr (only when
+// v_compute_takes_probe() holds): the threshold bytes are computed in the kernel from the probe result and the
+// exponent maxima v_exp and written to amin_out; otherwise they are read from amin.
+int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                           uint8_t* amin, const uint8_t* test_o, const uint8_t* v_exp, uint8_t* o, int bsz, int H,
+                           int group, int max_seq_len, int D, int s_last_dim, int n, int reference, cudaStream_t st) {
     VParams p;
     p.first8 = first8; p.mid4 = mid4; p.last4 = last4;
     p.s = reinterpret_cast<const uint16_t*>(s);
     p.amin = amin;
+    p.test_o = reinterpret_cast<const uint16_t*>(test_o); p.v_exp = v_exp; p.amin_out = amin; p.H = H;
     p.o = reinterpret_cast<uint16_t*>(o);
     p.max_seq_len = max_seq_len; p.D = D; p.s_last_dim = s_last_dim; p.n = n; p.reference = reference;
     p.group = group;
     const int BH = bsz * H;
-    const bool fast = D == 128 && aligned16(first8) && aligned16(mid4) && aligned16(last4) &&
-                      (n == 0 || (aligned16(s) && s_last_dim % 8 == 0 && ((n + 7) & ~7) <= s_last_dim)) &&
-                      ((reinterpret_cast<uintptr_t>(o) & 3u) == 0);
+    const bool fast = v_compute_takes_probe(first8, mid4, last4, s, o, group, D, s_last_dim, n);
+    AKV_REQUIRE(fast || !test_o, AKV_ERR_SHAPE, "v_cache_compute: the probe form needs the streaming kernel");
     if (fast && group == 1) return launch_v_fast<1, 6, 2, 1>(p, BH, st);
     if (fast && group == 2) return launch_v_fast<2, 6, 2, 2>(p, BH, st);
     if (fast && group == 4) return launch_v_fast<4, 6, 2, 2>(p, BH, st);
@@ -521,8 +563,16 @@ int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     long long want = (total + 127) / 128;
     int grid = (int)(want < (long long)sm_count() * 16 ? want : (long long)sm_count() * 16);
     if (grid < 1) grid = 1;
+    count_launch();
     v_compute_generic_kernel<<<grid, 128, 0, st>>>(p, BH * group);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
+}
+
+int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                     const uint8_t* amin, uint8_t* o, int bsz, int H, int group, int max_seq_len, int D,
+                     int s_last_dim, int n, int reference, cudaStream_t st) {
+    return launch_v_compute_probe(first8, mid4, last4, s, const_cast<uint8_t*>(amin), nullptr, nullptr, o, bsz, H, group,
+                                  max_seq_len, D, s_last_dim, n, reference, st);
 }
 
 // ================================================================== probe

@@ -214,6 +214,7 @@ int launch_v_split(const uint8_t* first8, const uint8_t* mid4, const uint8_t* la
     p.max_seq_len = max_seq_len; p.s_last_dim = s_last_dim; p.n = n; p.reference = reference;
     split_plan(bsz * H, n, &p.chunk_tokens, &p.chunks);
     dim3 grid(p.chunks, bsz * H);
+    count_launch(2);   // the split pass and the combine
     if (group == 1) v_split_kernel<1><<<grid, 128, 0, st>>>(p);
     else if (group == 2) v_split_kernel<2><<<grid, 128, 0, st>>>(p);
     else if (group == 4) v_split_kernel<4><<<grid, 128, 0, st>>>(p);
@@ -254,6 +255,7 @@ lse_merge_kernel(const float* __restrict__ packed, __half* __restrict__ out, int
 }
 
 int launch_lse_merge(const float* packed, uint8_t* out, int R, int rows, int D, cudaStream_t st) {
+    count_launch();
     lse_merge_kernel<<<rows, 128, 0, st>>>(packed, reinterpret_cast<__half*>(out), R, rows, D);
     return cuda_status(cudaGetLastError(), "lse_merge launch");
 }

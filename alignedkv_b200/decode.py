@@ -75,6 +75,16 @@ class DecodeLayer:
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.launches = 0
 
+    @property
+    def launches(self) -> int:
+        """Kernels the library has launched (process-wide) since the counter was last set; `layer.launches = 0`
+        resets it.  The count comes from the library's own launch sites, not from arithmetic on this side."""
+        return int(self.lib.akv_launch_count()) - self._launch_base
+
+    @launches.setter
+    def launches(self, value: int) -> None:
+        self._launch_base = int(self.lib.akv_launch_count()) - int(value)
+
     def _flags(self, append: bool = True) -> int:
         return (AKV_STEP_REFERENCE if getattr(self, "reference", False) else 0) | \
                (AKV_STEP_ORDER_FREE if self.v_mode == "order_free" else 0) | (0 if append else AKV_STEP_NO_APPEND)
@@ -102,7 +112,6 @@ class DecodeLayer:
                     k.data_ptr(), v.data_ptr(), ws.data_ptr(), nbytes, B, H, D, self.L, S,
                     torch.cuda.current_stream(self.device).cuda_stream)
             _lib.check("prefill", rc)
-            self.launches += 2
         elif S > 0:
             # head sizes the fused kernel does not cover: the operator-by-operator route
             self.k_exp_max.copy_(exponent_field(torch.max(k, dim=1, keepdim=True).values))
@@ -111,7 +120,6 @@ class DecodeLayer:
                                      S // column_block, cdiv(self.L, column_block), D, column_block, 0, S)
             cuda_module.v_cache_save(self.v_first_8, self.v_mid_4, self.v_last_4, v.view(torch.uint8), B, H, self.L, D,
                                      0, full)
-            self.launches += 2 if full else 0
             self.restk[:, :S - full] = k[:, full:]
             self.restv[:, :S - full] = v[:, full:]
         self.rest_len = S % column_block
@@ -150,13 +158,6 @@ class DecodeLayer:
         flush = append and self.rest_len + 1 == column_block
         qn = self.rest_start + (column_block if flush else 0)
         rest = 0 if flush else self.rest_len + (1 if append else 0)
-        tail = rest > 0 or qn == 0 or packed or self.v_mode == "order_free"
-        # kernels of this library launched by the call: append (+ flush in the same launch; 2 more launches when the
-        # head is too wide for that), q.K^T, softmax, probe, threshold, P.V (2 for the order-free form), tail
-        R = (qn // column_block + 1) * column_block
-        split_softmax = R > 3 * 4096 and B * Hq < 2 * self._sm_count     # rows cut into 4096-score chunks: 3 launches
-        self.launches += 1 + (2 if flush and D > 256 else 0) + (1 if qn else 0) + (3 if split_softmax else 1) + \
-            ((3 + (1 if self.v_mode == "order_free" else 0)) if qn else 0) + (1 if tail else 0)
         self.rest_len, self.rest_start = rest, qn
         if append:
             self.cache_len += 1
@@ -184,7 +185,6 @@ class DecodeLayer:
                                        self.B, self.H, self.D, self.L, first_blk, max(0, last_blk - first_blk),
                                        torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check("rollback", rc)
-        self.launches += 1
         self.rest_len, self.rest_start, self.cache_len = snap["rest_len"], snap["rest_start"], snap["cache_len"]
 
     def reset_counters(self) -> None:

@@ -296,9 +296,7 @@ def run_ours(args):
     if sampler:
         sampler.start()
     ms, t0, t1 = timed(step_resident, args.steps, warm)    # the headline: no instrumentation inside the steps
-    launches = layer.launches // (args.steps + warm)       # kernels of this library per step
-    if seq is not None:
-        launches += 1                                      # the merge kernel
+    launches = layer.launches // (args.steps + warm)       # kernels of this library per step (its own counter)
     # the same steps again with CUDA events recorded around the two streaming kernels (the events cost ~10 us per
     # step, which is why they stay out of the headline pass)
     layer.reset_counters()
@@ -441,8 +439,7 @@ def run_decoder(args):
         return ms, t0, t1
 
     sampler = ClockSampler(local) if rank == 0 else None
-    for c in model.caches:
-        c.launches = 0
+    model.caches[0].launches = 0                         # (the counter is the library's, shared by all layers)
     lib.akv_set_tuning(b"timing", 1)
     lib.akv_timing_reset()
     if sampler:
@@ -450,7 +447,7 @@ def run_decoder(args):
     ms, t0, t1 = timed(step_resident, args.steps, warm)
     clocks = sampler.stop(t0, t1) if sampler else None
     kern = model.caches[0].kernel_times()                 # medians over every layer's launches in the timed steps
-    launches = sum(c.launches for c in model.caches) // (args.steps + warm)
+    launches = model.caches[0].launches // (args.steps + warm)
     acct = {"k_compute": 0.0, "v_compute": 0.0, "read": 0.0, "dense": 0.0}
     for c in model.caches:                                # the last step's read decisions, every layer
         a = c.bytes_accounting()

@@ -241,6 +241,12 @@ int akv_decode_step_noalloc(void* k_first_8, void* k_mid_4, void* k_last_4, void
 int akv_timing_reset(void);
 int akv_timing_read(double* k_us, double* v_us);
 
+/*
+ * Number of kernels this library has launched in this process so far (no counterpart in the reference); a caller
+ * takes the difference around a region to know how many of the library's kernels ran in it.
+ */
+long long akv_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif
