@@ -88,6 +88,7 @@ int akv_set_tuning(const char* key, int value) {
     if (!strcmp(key, "k_kch") && (value == 8 || value == 16)) t.k_kch = value;
     else if (!strcmp(key, "k_stages") && value >= 3 && value <= 6) t.k_stages = value;
     else if (!strcmp(key, "pdl") && (value == 0 || value == 1)) t.pdl = value;
+    else if (!strcmp(key, "k_gqa_kch") && (value == 8 || value == 16)) t.k_gqa_kch = value;
     else if (!strcmp(key, "timing") && (value == 0 || value == 1)) t.timing = value;
     else if (!strcmp(key, "k_wpc") && value >= 0 && value <= 16) t.k_wpc = value;
     else {

@@ -22,6 +22,7 @@ struct Tuning {
     int timing = 0;     // 1: akv_decode_step records CUDA events around its two streaming kernels
     int k_wpc = 0;      // cap on warps per CTA of the q.K^T kernel (0 = as many as shared memory allows)
     int pdl = 1;        // 1: the kernels of a decode step are chained with programmatic dependent launch
+    int k_gqa_kch = 8;  // channels per stage of the q.K^T kernel when query heads share KV heads (8 or 16)
 };
 Tuning& tuning();
 
@@ -92,6 +93,10 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ uint32_t u4w(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 __device__ __forceinline__ uint32_t lds16(uint32_t a) {
     uint16_t v;
     asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(a));

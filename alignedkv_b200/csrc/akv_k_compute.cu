@@ -16,8 +16,15 @@
 // Grouped-query attention (G query heads per KV head): a row is fetched when ANY head of the group needs it, every
 // staged row is read from shared memory once and applied to the G heads in turn, each head substituting the
 // reference's constants where its own code skips the plane - so plane bytes cross HBM once per group and the
-// results equal G independent multi-head passes.  With G == 1 the producer writes the constants into the skipped
-// rows' slots instead, and the consumer has no per-row selects.
+// results equal G independent multi-head passes.  The byte shuffles that assemble a token's low byte from the
+// nibble planes run on the half-rate integer pipe, and with them done per head the kernel was bound by that pipe
+// (2.1 TB/s at G = 4).  So per row each lane assembles the low bytes once per alignment code (mid only / both planes;
+// "neither" is a constant) and parks them in a private 8-byte slot per code of a small per-warp scratch; a head then
+// fetches the pair of its own code with one 8-byte load whose offset (code x 256) was tabulated per (head, channel)
+// when the (batch, KV head) started: one add and one load per head and row instead of selects and shuffles.  The
+// rows are software-pipelined by one (two scratch buffers), so the store -> load round trip of a row overlaps the
+// arithmetic of the previous one.  With G == 1 the producer writes the constants into the skipped rows' slots
+// instead, and the consumer has neither selects nor scratch.
 #include "akv_common.cuh"
 
 namespace akv {
@@ -32,9 +39,13 @@ __host__ __device__ constexpr int stage_bytes(int kch) { return TILES * f_tile(k
 }  // namespace kc
 
 namespace kc {
-// per (batch, KV head) metadata slot: union masks (16 words), then per query head masks (16 words) + q words
-__host__ __device__ constexpr int head_meta(int D) { return 64 + 4 * D; }
+// per (batch, KV head) metadata slot: union masks (16 words), then per query head D offset words (code x 256: which
+// scratch slot holds the low bytes of the head's alignment code on that channel; used when G > 1) + D q words
+__host__ __device__ constexpr int head_meta(int D) { return 8 * D; }
 __host__ __device__ constexpr int meta_bytes(int D, int G) { return 64 + G * head_meta(D); }
+// per-warp scratch of the grouped-query consumer: 2 row buffers x 3 codes x 32 lanes x 8 bytes
+constexpr int SCR_CODE = 256, SCR_ROW = 3 * SCR_CODE, SCR_BYTES = 2 * SCR_ROW;
+__host__ __device__ constexpr int scratch_bytes(int G) { return G > 1 ? SCR_BYTES : 0; }
 }  // namespace kc
 
 struct KParams {
@@ -84,7 +95,7 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     const size_t tile_f = (size_t)p.D * 64, tile_n = (size_t)p.D * 32;
     const int META = meta_bytes(p.D, G), HMETA = head_meta(p.D);
 
-    uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META);
+    uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META + scratch_bytes(G));
     uint8_t* meta0 = ring + STAGES * STAGE;
     const uint32_t ring_a = smem_u32(ring);
 
@@ -124,8 +135,8 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             const long long bhq = bh * G + g;
-            uint32_t* masks = reinterpret_cast<uint32_t*>(meta0 + (size_t)slot * META + 64 + (size_t)g * HMETA);
-            uint32_t* q2 = masks + 16;
+            uint32_t* offw = reinterpret_cast<uint32_t*>(meta0 + (size_t)slot * META + 64 + (size_t)g * HMETA);
+            uint32_t* q2 = offw + p.D;
             const uint32_t top = __ldg(p.kqmax + bhq);
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
@@ -137,14 +148,10 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
                     qh = __ldg(reinterpret_cast<const uint16_t*>(p.q) + (size_t)bhq * p.D + d);
                     q2[d] = qh | (qh << 16);
                 }
-                const uint32_t mm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 8);
-                const uint32_t lm = __ballot_sync(0xFFFFFFFFu, p.reference || diff < 4);
-                u_mm[r] |= mm;
-                u_lm[r] |= lm;
-                if (lane == 0) {
-                    masks[r] = mm;
-                    masks[8 + r] = lm;
-                }
+                const bool m = p.reference || diff < 8, l = p.reference || diff < 4;
+                if (G > 1 && d < p.D) offw[d] = (uint32_t)((m ? 1 : 0) + (l ? 1 : 0)) * SCR_CODE;
+                u_mm[r] |= __ballot_sync(0xFFFFFFFFu, m);
+                u_lm[r] |= __ballot_sync(0xFFFFFFFFu, l);
             }
         }
         if (lane == 0) {
@@ -200,6 +207,12 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
     }
 
     const int tile = lane >> 3, li = lane & 7;
+    // grouped-query scratch: this lane's 8-byte slot of code 0 ("neither plane": low bytes 0x80) never changes
+    const uint32_t scr_a = smem_u32(meta0 + NMETA * META) + lane * 8;
+    if (G > 1) {
+        sts64(scr_a, 0x80808080u, 0x80808080u);
+        sts64(scr_a + SCR_ROW, 0x80808080u, 0x80808080u);
+    }
     uint32_t acc[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0;
@@ -218,67 +231,73 @@ __global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
         const uint32_t* lp = reinterpret_cast<const uint32_t*>(stp + F_BYTES + N_BYTES + tile * N_TILE + li * 4);
         const uint8_t* hm0 = meta0 + (size_t)ck.slot * META + 64;
         const int ch0 = ck.c * KCH;                       // first channel of the stage
-        // per head (and for the union): the stage's KCH mask bits of each plane, shifted down to bit 0; `dis` marks the
-        // rows on which some head's code differs from the union's
-        uint32_t mmw[G], lmw[G], ummw = 0, ulmw = 0, dis = 0;
-        if (G > 1) {
-            const uint32_t* um = reinterpret_cast<const uint32_t*>(meta0 + (size_t)ck.slot * META);
-            ummw = um[ch0 >> 5] >> (ch0 & 31);
-            ulmw = um[8 + (ch0 >> 5)] >> (ch0 & 31);
-        }
+        if (G == 1) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const uint32_t* masks = reinterpret_cast<const uint32_t*>(hm0 + (size_t)g * HMETA);
-            mmw[g] = masks[ch0 >> 5] >> (ch0 & 31);
-            lmw[g] = masks[8 + (ch0 >> 5)] >> (ch0 & 31);
-            dis |= (mmw[g] ^ ummw) | (lmw[g] ^ ulmw);
-        }
+            for (int r4 = 0; r4 < KCH / 4; ++r4) {
+                const uint4 qv = *reinterpret_cast<const uint4*>(hm0 + (size_t)p.D * 4 + (size_t)(ch0 + r4 * 4) * 4);
 #pragma unroll
-        for (int r4 = 0; r4 < KCH / 4; ++r4) {
-            uint4 qv[G];
+                for (int rr = 0; rr < 4; ++rr) {
+                    // the producer has written the substitutes into the rows it did not fetch
+                    const int r = r4 * 4 + rr;
+                    const uint2 f = fp[r * 8];
+                    const uint32_t M = mp[r * 8], L = lp[r * 8];
+                    const uint32_t lbe = (M & 0xF0F0F0F0u) | ((L >> 4) & 0x0F0F0F0Fu);   // low bytes, tokens 0,2,4,6
+                    const uint32_t lbo = ((M << 4) & 0xF0F0F0F0u) | (L & 0x0F0F0F0Fu);   // low bytes, tokens 1,3,5,7
+                    const uint32_t q2 = rr == 0 ? qv.x : rr == 1 ? qv.y : rr == 2 ? qv.z : qv.w;
+                    acc[0][0] = hfma2_bits(__byte_perm(lbe, f.x, 0x6140), q2, acc[0][0]);
+                    acc[0][1] = hfma2_bits(__byte_perm(lbo, f.x, 0x7150), q2, acc[0][1]);
+                    acc[0][2] = hfma2_bits(__byte_perm(lbe, f.y, 0x6342), q2, acc[0][2]);
+                    acc[0][3] = hfma2_bits(__byte_perm(lbo, f.y, 0x7352), q2, acc[0][3]);
+                }
+            }
+        } else {
+            // Row r: (a) this lane's low bytes for the codes "mid only" and "both" go to its slots of scratch buffer
+            // r & 1 (a plane the union did not fetch leaves garbage there that no head's offset points at), and every
+            // head's pair is fetched back through its offset; (b) a row later the pairs are shuffled with the
+            // high bytes into k~ words and multiplied.  Only this lane reads what it wrote, so no warp
+            // synchronisation is involved; the volatile accesses keep their order.
+            const uint32_t hm_a = smem_u32(hm0);
+            uint2 fprev = make_uint2(0u, 0u), lbprev[G];
+            uint4 ofv[G], qv[G], qprev[G];
 #pragma unroll
-            for (int g = 0; g < G; ++g)
-                qv[g] = *reinterpret_cast<const uint4*>(hm0 + (size_t)g * HMETA + 64 + (size_t)(ch0 + r4 * 4) * 4);
+            for (int r = 0; r <= KCH; ++r) {
+                uint2 fcur = make_uint2(0u, 0u), lbcur[G];
 #pragma unroll
-            for (int rr = 0; rr < 4; ++rr) {
-                const int r = r4 * 4 + rr;
-                const uint2 f = fp[r * 8];
-                const uint32_t M = mp[r * 8], L = lp[r * 8];
-                if (G == 1 || !((dis >> r) & 1u)) {
-                    // one reassembly serves every head of the group (warp-uniform branch): with G == 1 the producer
-                    // has written the substitutes, else the union's code (= every head's code on this row) picks them
-                    uint32_t Mu = M, Lu = L;
-                    if (G > 1) {
-                        const bool m = (ummw >> r) & 1u, l = (ulmw >> r) & 1u;
-                        Mu = m ? M : 0x88888888u;
-                        Lu = l ? L : (m ? 0x88888888u : 0u);
+                for (int g = 0; g < G; ++g) lbcur[g] = make_uint2(0u, 0u);
+                if (r < KCH) {
+                    if ((r & 3) == 0) {
+#pragma unroll
+                        for (int g = 0; g < G; ++g) {
+                            ofv[g] = lds128(hm_a + g * HMETA + (ch0 + r) * 4);
+                            qv[g] = lds128(hm_a + g * HMETA + p.D * 4 + (ch0 + r) * 4);
+                        }
                     }
-                    const uint32_t lbe = (Mu & 0xF0F0F0F0u) | ((Lu >> 4) & 0x0F0F0F0Fu);   // low bytes, tokens 0,2,4,6
-                    const uint32_t lbo = ((Mu << 4) & 0xF0F0F0F0u) | (Lu & 0x0F0F0F0Fu);   // low bytes, tokens 1,3,5,7
-                    const uint32_t k0 = __byte_perm(lbe, f.x, 0x6140), k1 = __byte_perm(lbo, f.x, 0x7150);
-                    const uint32_t k2 = __byte_perm(lbe, f.y, 0x6342), k3 = __byte_perm(lbo, f.y, 0x7352);
+                    fcur = fp[r * 8];
+                    const uint32_t M = mp[r * 8], L = lp[r * 8];
+                    const uint32_t me = M & 0xF0F0F0F0u, mo = (M << 4) & 0xF0F0F0F0u;
+                    const uint32_t sb = scr_a + (r & 1) * SCR_ROW;
+                    sts64(sb + SCR_CODE, me | 0x08080808u, mo | 0x08080808u);                         // mid only
+                    sts64(sb + 2 * SCR_CODE, me | ((L >> 4) & 0x0F0F0F0Fu), mo | (L & 0x0F0F0F0Fu));   // both planes
+#pragma unroll
+                    for (int g = 0; g < G; ++g) lbcur[g] = lds64(sb + u4w(ofv[g], r & 3));
+                }
+                if (r > 0) {
+                    const int rr = (r - 1) & 3;
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
-                        const uint32_t q2 = rr == 0 ? qv[g].x : rr == 1 ? qv[g].y : rr == 2 ? qv[g].z : qv[g].w;
-                        acc[g][0] = hfma2_bits(k0, q2, acc[g][0]);
-                        acc[g][1] = hfma2_bits(k1, q2, acc[g][1]);
-                        acc[g][2] = hfma2_bits(k2, q2, acc[g][2]);
-                        acc[g][3] = hfma2_bits(k3, q2, acc[g][3]);
+                        const uint4& qq = rr == 3 ? qprev[g] : qv[g];   // (row 3 of a quad is consumed after the reload)
+                        const uint32_t q2 = rr == 0 ? qq.x : rr == 1 ? qq.y : rr == 2 ? qq.z : qq.w;
+                        acc[g][0] = hfma2_bits(__byte_perm(lbprev[g].x, fprev.x, 0x6140), q2, acc[g][0]);
+                        acc[g][1] = hfma2_bits(__byte_perm(lbprev[g].y, fprev.x, 0x7150), q2, acc[g][1]);
+                        acc[g][2] = hfma2_bits(__byte_perm(lbprev[g].x, fprev.y, 0x6342), q2, acc[g][2]);
+                        acc[g][3] = hfma2_bits(__byte_perm(lbprev[g].y, fprev.y, 0x7352), q2, acc[g][3]);
                     }
-                } else {
+                }
+                fprev = fcur;
 #pragma unroll
-                    for (int g = 0; g < G; ++g) {   // this head's own code: the staged bytes or the substitutes
-                        const bool m = (mmw[g] >> r) & 1u, l = (lmw[g] >> r) & 1u;
-                        const uint32_t Mg = m ? M : 0x88888888u;
-                        const uint32_t Lg = l ? L : (m ? 0x88888888u : 0u);
-                        const uint32_t q2 = rr == 0 ? qv[g].x : rr == 1 ? qv[g].y : rr == 2 ? qv[g].z : qv[g].w;
-                        const uint32_t lbe = (Mg & 0xF0F0F0F0u) | ((Lg >> 4) & 0x0F0F0F0Fu);
-                        const uint32_t lbo = ((Mg << 4) & 0xF0F0F0F0u) | (Lg & 0x0F0F0F0Fu);
-                        acc[g][0] = hfma2_bits(__byte_perm(lbe, f.x, 0x6140), q2, acc[g][0]);
-                        acc[g][1] = hfma2_bits(__byte_perm(lbo, f.x, 0x7150), q2, acc[g][1]);
-                        acc[g][2] = hfma2_bits(__byte_perm(lbe, f.y, 0x6342), q2, acc[g][2]);
-                        acc[g][3] = hfma2_bits(__byte_perm(lbo, f.y, 0x7352), q2, acc[g][3]);
-                    }
+                for (int g = 0; g < G; ++g) {
+                    lbprev[g] = lbcur[g];
+                    if ((r & 3) == 3) qprev[g] = qv[g];
                 }
             }
         }
@@ -380,12 +399,12 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     // (channels per stage, ring depth): the instantiated combinations; anything else falls back to the default of
     // its group size, and the shared-memory budget below is computed from what is actually launched
     // groups: 8-channel stages (smaller rings, more warps per SM: the consumer does G times the arithmetic per byte)
-    const int kch = group > 1 ? 8 : tuning().k_kch;
+    const int kch = group > 1 ? (tuning().k_gqa_kch == 16 ? 16 : 8) : tuning().k_kch;
     int stages = tuning().k_stages;
-    if (group > 1) stages = 4;
+    if (group > 1) stages = kch == 8 ? 4 : 3;
     else if (!((kch == 8 && (stages == 3 || stages == 4 || stages == 6)) || (kch == 16 && stages >= 3 && stages <= 5)))
         stages = (kch == 8) ? 4 : 3;
-    const int per_warp = stages * stage_bytes(kch) + NMETA * meta_bytes(D, group);
+    const int per_warp = stages * stage_bytes(kch) + NMETA * meta_bytes(D, group) + scratch_bytes(group);
     int wmax = budget / per_warp;
     if (wmax > 16) wmax = 16;
     if (tuning().k_wpc > 0 && tuning().k_wpc < wmax) wmax = tuning().k_wpc;

@@ -147,7 +147,6 @@ __device__ __forceinline__ uint32_t v_chunk(int c, int k) {
 __device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
-__device__ __forceinline__ uint32_t u4w(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 // 8 tokens x 8 pairs tile: R[j] = four words of token j (word i = pairs 2i, 2i+1, two bytes each) -> for pair q the
 // 16 bytes of its 8 tokens, stored at the pair's swizzled chunk.  dst = array base; c0 = first pair, k = chunk index.

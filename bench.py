@@ -41,6 +41,9 @@ WORKLOADS = {
                                       sharding="replicate", v_mode="exact"),
     "llama3-8b-gqa-decode": dict(batch=64, heads=32, kv_heads=8, head_dim=128, cache_len=8192, sharding="batch",
                                  v_mode="exact"),
+    # a quarter of that batch, for profiler captures (planes 2 x 256 MiB, larger than L2)
+    "llama3-8b-gqa-decode-b16": dict(batch=16, heads=32, kv_heads=8, head_dim=128, cache_len=8192, sharding="batch",
+                                     v_mode="exact"),
     "long-context-decode": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072, sharding="sequence",
                                 v_mode="order_free"),
     # full random-init Llama-2-7B decoder, AlignedKV cache on every layer: prompt of 1024 uniform-random ids, then greedy

@@ -46,7 +46,7 @@ const char* akv_last_error(void);
 int akv_device_error_flag(void);
 
 /*
- * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16,
+ * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16, "k_gqa_kch" 8|16,
  * "timing" 0|1, "pdl" 0|1: chain the kernels of a decode step with programmatic dependent launch).
  * Process-wide; results never depend on them.  No counterpart in the reference.
  */
