@@ -74,7 +74,7 @@ struct KCursor {
 };
 
 template <int KCH, int STAGES, int G>
-__global__ void __launch_bounds__(512, 1) k_compute_kernel(const KParams p) {
+__global__ void __launch_bounds__(G > 1 ? 256 : 512, 1) k_compute_kernel(const KParams p) {
     using namespace kc;
     constexpr int F_TILE = f_tile(KCH), N_TILE = n_tile(KCH);
     constexpr int F_BYTES = TILES * F_TILE, N_BYTES = TILES * N_TILE, STAGE = F_BYTES + 2 * N_BYTES;
@@ -406,7 +406,7 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
         stages = (kch == 8) ? 4 : 3;
     const int per_warp = stages * stage_bytes(kch) + NMETA * meta_bytes(D, group) + scratch_bytes(group);
     int wmax = budget / per_warp;
-    if (wmax > 16) wmax = 16;
+    if (wmax > (group > 1 ? 8 : 16)) wmax = group > 1 ? 8 : 16;   // (the grouped-query kernels are compiled for 256 threads)
     if (tuning().k_wpc > 0 && tuning().k_wpc < wmax) wmax = tuning().k_wpc;
     AKV_REQUIRE(wmax >= 1, AKV_ERR_CUDA, "k_cache_compute: %d bytes of shared memory are too few", budget);
     int wpc = wmax;
