@@ -372,7 +372,9 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
         int ucode = 2;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            sb[g] = (tok < cnt) ? lds16(sbase + g * P::SB_HEAD) : 0u;
+            // (beyond the last token the buffer holds stale but readable bytes; the code below ignores them)
+            sb[g] = lds16(sbase + g * P::SB_HEAD);
+            if (tok >= cnt) sb[g] = 0u;
             const int diff = (int)(int16_t)(uint16_t)(A[g] - sb[g]);
             int code = p.reference ? 0 : (diff >= 0x0800 ? 2 : (diff >= 0x0400 ? 1 : 0));
             if (tok >= cnt) code = 2;
@@ -380,7 +382,9 @@ __global__ void __launch_bounds__(64 * G + 128) v_compute_kernel(const VParams p
             lm[g] = __ballot_sync(0xFFFFFFFFu, code == 0);
             ucode = code < ucode ? code : ucode;
         }
-        const uint32_t umm = __ballot_sync(0xFFFFFFFFu, ucode < 2), ulm = __ballot_sync(0xFFFFFFFFu, ucode == 0);
+        // union over the heads of the group (with one head it is that head's masks)
+        const uint32_t umm = G == 1 ? mm[0] : __ballot_sync(0xFFFFFFFFu, ucode < 2);
+        const uint32_t ulm = G == 1 ? lm[0] : __ballot_sync(0xFFFFFFFFu, ucode == 0);
         int ms = -1;
         uint32_t bytes = (half == 0) ? (uint32_t)cnt * D : 0u;
         if (umm) {
