@@ -139,6 +139,9 @@ def test_k_compute_gqa(akv_lib, B, H, G, nb, nmb, reference):
     (1, 2, 4, 29, 2, 64, "exact"),             # nothing quantized yet
     (1, 4, 1, 12400, 3, 12480, "exact"),       # few long rows: the softmax is split across CTAs (4 chunks)
     (1, 2, 2, 12350, 2, 12416, "order_free"),  # split softmax with a residual tail in the last chunk
+    (1, 4, 1, 9000, 2, 9088, "exact"),         # rows too long for the register-cached softmax, too short to split:
+                                               # plain softmax + separate probe and threshold launches
+    (10, 8, 8, 100, 2, 128, "exact"),          # many rows (640): the probe is not fused into the softmax CTAs
 ])
 def test_decode_step_ex(akv_lib, B, H, G, prompt, steps, max_len, v_mode):
     """DecodeLayer (akv_decode_step_ex) with a group and either P.V kernel against the oracle pipeline: planes
@@ -174,6 +177,21 @@ def test_decode_step_ex(akv_lib, B, H, G, prompt, steps, max_len, v_mode):
                                                           "v_last_4")):
         assert np.array_equal(g_, w_), f"plane {name} differs from the oracle"
     assert akv_lib.akv_device_error_flag() == 0
+
+
+def test_launch_count(akv_lib):
+    """The library counts its own kernel launches: a decode step with one quantized block, no flush and a residual
+    tail is append, q.K^T, softmax (+ probe), P.V (+ threshold), tail = 5 launches."""
+    from alignedkv_b200.decode import DecodeLayer
+    B, H, D = 1, 2, 128
+    k, v, q = make_kvq(97, B, 80, H, D)
+    layer = DecodeLayer(B, 128, H, D, "cuda:0")
+    layer.prefill(dev(k[:, :70]), dev(v[:, :70]))
+    before = akv_lib.akv_launch_count()
+    layer.launches = 0
+    layer.decode(dev(q), dev(k[:, 70:71]), dev(v[:, 70:71]))
+    torch.cuda.synchronize()
+    assert layer.launches == 5 and akv_lib.akv_launch_count() - before == 5
 
 
 @pytest.mark.parametrize("B,H,D,S,max_len", [(2, 4, 128, 200, 256), (1, 8, 128, 640, 640), (2, 2, 64, 70, 128),
