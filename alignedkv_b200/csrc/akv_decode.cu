@@ -90,7 +90,8 @@ static size_t carve(Scratch* sc, uint8_t* base, int B, int H, int G, int D, int 
 // One launch, three roles by block index (128 threads each):
 //   [0, BH)            append: residual buffers, per-channel exponent maxima, alignment inputs kq / kqmax of the G
 //                      query heads.  With append == 0 nothing is stored (the token belongs to another shard of the
-//                      sequence) and only the alignment inputs are built.
+//                      sequence) and only the alignment inputs are built; with append == 2 the token is not stored
+//                      either but the exponent maxima take it in (a shard that keeps the maxima of the whole sequence).
 //   [BH, 2BH)          (flush only) K block writer: the 63 buffered tokens plus the new one -> planes, block qn/64
 //   [2BH, 2BH+BH*D/64) (flush only) V row writer for the same 64 tokens
 // The writers take token 63 straight from k_new / v_new, so they do not depend on the append role's stores.
@@ -117,8 +118,10 @@ append_flush_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, 
                     if (append) {
                         const size_t rrow = (((size_t)b * BLK + rest_len) * H + h) * hd + c;   // [B,64,H,D] in words
                         const uint32_t kw = k_new[row], vw = v_new[row];
-                        restk[rrow] = kw;
-                        restv[rrow] = vw;
+                        if (append == 1) {
+                            restk[rrow] = kw;
+                            restv[rrow] = vw;
+                        }
                         // running per-channel maxima of the exponent fields (k_cache_file.py:98-99, v_cache_file.py:98-99)
                         k_exp[row] = (uint16_t)(__vmaxu4(k_exp[row], exps(kw)) & 0xFFFFu);
                         v_exp[row] = (uint16_t)(__vmaxu4(v_exp[row], exps(vw)) & 0xFFFFu);
@@ -371,18 +374,22 @@ softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ 
 
 __global__ void __launch_bounds__(256)
 softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ cstat, uint32_t* __restrict__ cand_val,
-                           int32_t* __restrict__ cand_idx, int R, int qn, int len, int chunks) {
+                           int32_t* __restrict__ cand_idx, int R, int qn, int len, int chunks, int stat_chunks,
+                           int t_base) {
+    // chunks: chunks of this row held here (the grid); stat_chunks >= chunks: chunks whose statistics make up the
+    // row's (they include the other shards' when the sequence is sharded); t_base: position of local token 0 in the
+    // whole sequence (a multiple of 32, so residue classes are the same locally and globally)
     __shared__ uint32_t cand_v[256];
     __shared__ int32_t cand_i[256];
     const int bhq = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
     uint16_t* row = s + (size_t)bhq * R;
     // row statistics from the chunk statistics, in chunk order (every CTA of the row computes the same values)
     float m = -INFINITY;
-    for (int c = 0; c < chunks; ++c) m = fmaxf(m, cstat[((size_t)bhq * chunks + c) * 2]);
+    for (int c = 0; c < stat_chunks; ++c) m = fmaxf(m, cstat[((size_t)bhq * stat_chunks + c) * 2]);
     float sum = 0.f;
-    for (int c = 0; c < chunks; ++c) {
-        const float mc = cstat[((size_t)bhq * chunks + c) * 2];
-        if (mc > -INFINITY) sum += cstat[((size_t)bhq * chunks + c) * 2 + 1] * expf(mc - m);
+    for (int c = 0; c < stat_chunks; ++c) {
+        const float mc = cstat[((size_t)bhq * stat_chunks + c) * 2];
+        if (mc > -INFINITY) sum += cstat[((size_t)bhq * stat_chunks + c) * 2 + 1] * expf(mc - m);
     }
     const int t0 = ch * SM_CHUNK, t1 = min(R, t0 + SM_CHUNK);
     uint32_t best = 0;
@@ -393,7 +400,7 @@ softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ c
         row[t] = pb;
         if (t < qn && pb > best) {
             best = pb;
-            best_g = t >> 5;
+            best_g = (t_base + t) >> 5;
         }
     }
     cand_v[tid] = best;
@@ -425,7 +432,7 @@ softmax_class_reduce_kernel(const float* __restrict__ cstat, const uint32_t* __r
     }
     pval[(size_t)bhq * TOPK + tid] = (uint16_t)bv;
     pidx[(size_t)bhq * TOPK + tid] = bi;
-    if (tid == 0) {
+    if (tid == 0 && cstat != nullptr) {
         float m = -INFINITY, sum = 0.f;
         for (int c = 0; c < chunks; ++c) m = fmaxf(m, cstat[((size_t)bhq * chunks + c) * 2]);
         for (int c = 0; c < chunks; ++c) {
@@ -479,6 +486,41 @@ tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_mai
     }
 }
 
+// ------------------------------------------------------------------ magnitude probe across sequence shards
+// The 32 winning tokens of a row can lie on any shard.  Each shard writes the high-byte rows of the winners it holds
+// (zeros for the others) - rows[bhq][j][0..D) for token pidx[bhq][j]*32 + j of the whole sequence - the shards' buffers
+// are added up, and every shard then runs the same fp16 chain over the same bytes (V_cache.cu:104-119).
+__global__ void __launch_bounds__(128)
+probe_rows_gather_kernel(const uint8_t* __restrict__ first8, const int32_t* __restrict__ pidx, uint8_t* __restrict__ rows,
+                         int G, int D, int max_seq_len, int qn, int t_base) {
+    const long long bhq = blockIdx.x;
+    const uint8_t* F = first8 + (size_t)(bhq / G) * max_seq_len * D;
+    const int wpr = D >> 2;                                  // 32-bit words per row
+    for (int i = threadIdx.x; i < TOPK * wpr; i += blockDim.x) {
+        const int j = i / wpr, w = i - j * wpr;
+        const long long local = (long long)pidx[bhq * TOPK + j] * TOPK + j - t_base;
+        uint32_t v = 0;
+        if (local >= 0 && local < qn) v = reinterpret_cast<const uint32_t*>(F + (size_t)local * D)[w];
+        reinterpret_cast<uint32_t*>(rows + ((size_t)bhq * TOPK + j) * D)[w] = v;
+    }
+}
+
+__global__ void __launch_bounds__(128)
+probe_from_rows_kernel(const uint8_t* __restrict__ rows, const uint16_t* __restrict__ pval, uint16_t* __restrict__ test_o,
+                       int D) {
+    const long long bhq = blockIdx.x;
+    for (int c = threadIdx.x; c < (D >> 1); c += blockDim.x) {
+        uint32_t acc = 0;
+#pragma unroll 8
+        for (int j = 0; j < TOPK; ++j) {
+            const uint32_t f = reinterpret_cast<const uint16_t*>(rows + ((size_t)bhq * TOPK + j) * D)[c];
+            const uint32_t sv = pval[bhq * TOPK + j];
+            acc = hfma2_bits(__byte_perm(f, 0x80u, 0x1404) & 0x7FFF7FFFu, sv | (sv << 16), acc);
+        }
+        reinterpret_cast<uint32_t*>(test_o)[(size_t)bhq * (D >> 1) + c] = acc;
+    }
+}
+
 // ------------------------------------------------------------------ rollback of appended tokens
 // Undo appends: the exponent maxima are put back from copies the caller took earlier, and the K nibble planes of
 // blocks that were written since are cleared (the K writer ADDS nibbles, extension/csrc/K_cache.cu:52-56, so a block
@@ -510,6 +552,7 @@ struct Timing {
     int created = 0, used = 0;
 };
 static Timing g_timing;
+static cudaEvent_t* g_shard_timing = nullptr;   // slot of the sharded step in progress (akv_shard_step)
 
 static cudaEvent_t* timing_slot() {
     if (!tuning().timing) return nullptr;
@@ -660,7 +703,7 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
                                                         sqrtf((float)D), sm_chunks);
         count_launch();
         softmax_chunk_write_kernel<<<grid, 256, 0, st>>>(sc.s, sc.cstat, sc.cand_val, sc.cand_idx, R, qn, qn + rest,
-                                                        sm_chunks);
+                                                        sm_chunks, sm_chunks, 0);
         count_launch();
         softmax_class_reduce_kernel<<<B * H * G, 32, 0, st>>>(sc.cstat, sc.cand_val, sc.cand_idx, sc.pval, sc.pidx,
                                                              sc.stats, sm_chunks);
@@ -727,6 +770,135 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
         if ((rc = cuda_status(cudaGetLastError(), "decode_step tail launch")) != AKV_OK) return rc;
     }
     return AKV_OK;
+}
+
+// ------------------------------------------------------------------ decode step over a sequence shard, decision-exact
+// One decode step of a cache whose sequence is split across devices, cut into four phases with an exchange between
+// them, so that every shard takes the read decisions a single device holding the whole sequence would take:
+//   phase 1  append (last shard) or take the new token into the exponent maxima only (AKV_STEP_NO_APPEND |
+//            AKV_STEP_TRACK_MAXIMA), q.K^T over the local blocks, per 4096-score chunk the maximum and the sum of
+//            exponentials                          -> exch_out: float [rows][local chunks][2]
+//   phase 2  exch_in: float [rows][chunks_total][2], every shard's chunk statistics in sequence order.  Probabilities
+//            with the whole row's maximum and sum, and per local chunk the candidates of the 32 residue classes with
+//            positions in the whole sequence (token_base = position of local token 0, a multiple of 4096)
+//                                                  -> exch_out: u32 value [rows][local chunks][32], then i32 position/32
+//   phase 3  exch_in: the same two arrays over chunks_total.  Winners per class (largest probability, first
+//            position); the high-byte rows of the winners this shard holds
+//                                                  -> exch_out: bytes [rows][32][head_dim], zeros for rows held elsewhere
+//   phase 4  exch_in: the shards' row buffers added up.  Probe, threshold bytes, order-free P.V over the local
+//            tokens, residual tokens (last shard)  -> exch_out: float [rows][head_dim + 2], words 2.. = this shard's
+//            part of the output (the parts add up to the output; words 0, 1 are unused)
+// rows = bsz * n_kv_heads * group.  The chunk grid is the one a single device uses for its split softmax, and the sums
+// are combined in the same order, so probabilities - and with them every read decision - come out bit-identical to a
+// single device that takes the split path; the P.V partial sums differ only in how the fp32 additions are grouped.
+// All phases take the state BEFORE the step (rest_len, rest_start); the caller updates it after phase 4 as for
+// akv_decode_step_ex.  The workspace is the one of akv_decode_scratch_bytes_ex(..., AKV_STEP_ORDER_FREE).
+int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                   void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                   const void* v_new, const void* exch_in, void* exch_out, void* scratch, long long scratch_bytes,
+                   int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
+                   int token_base, int chunks_total, int flags, int phase, void* stream) {
+    set_error("");
+    const int B = bsz, H = n_kv_heads, G = group, D = head_dim;
+    const bool reference = (flags & AKV_STEP_REFERENCE) != 0, append = (flags & AKV_STEP_NO_APPEND) == 0;
+    const bool track = (flags & AKV_STEP_TRACK_MAXIMA) != 0;
+    AKV_REQUIRE(k_first_8 && k_mid_4 && k_last_4 && v_first_8 && v_mid_4 && v_last_4 && k_exp_max && v_exp_max && restk &&
+                restv && q && exch_out && scratch && (!(append || track) || (k_new && v_new)) && (phase == 1 || exch_in),
+                AKV_ERR_NULL, "shard_step: null pointer");
+    AKV_REQUIRE(B > 0 && H > 0 && G > 0 && G <= 8 && D == 128 && max_seq_len > 0 && phase >= 1 && phase <= 4 &&
+                token_base >= 0 && token_base % SM_CHUNK == 0, AKV_ERR_SHAPE,
+                "shard_step: unsupported extent (bsz %d, kv heads %d, group %d, head_dim %d [128], phase %d, token_base "
+                "%d [multiple of %d])", B, H, G, D, phase, token_base, SM_CHUNK);
+    AKV_REQUIRE(rest_len >= 0 && rest_len < BLK && rest_start >= 0 && rest_start % BLK == 0 &&
+                rest_start + rest_len + (append ? 1 : 0) <= max_seq_len, AKV_ERR_SHAPE,
+                "shard_step: residual state (start %d, length %d) does not fit max_seq_len %d", rest_start, rest_len,
+                max_seq_len);
+    AKV_REQUIRE(scratch_bytes >= akv_decode_scratch_bytes_ex(B, H, G, D, max_seq_len, AKV_STEP_ORDER_FREE), AKV_ERR_SHAPE,
+                "shard_step: scratch of %lld bytes is too small", scratch_bytes);
+    AKV_REQUIRE(aligned16(scratch) && aligned16(q) && aligned16(exch_out) && (!exch_in || aligned16(exch_in)) &&
+                aligned16(restk) && aligned16(restv) && aligned16(k_exp_max) && aligned16(v_exp_max) &&
+                (!k_new || aligned16(k_new)) && (!v_new || aligned16(v_new)) && aligned16(k_first_8) &&
+                aligned16(k_mid_4) && aligned16(k_last_4) && aligned16(v_first_8) && aligned16(v_mid_4) &&
+                aligned16(v_last_4), AKV_ERR_ALIGN, "shard_step: pointers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Scratch sc;
+    carve(&sc, static_cast<uint8_t*>(scratch), B, H, G, D, max_seq_len, true);
+    const int nmb = (max_seq_len + BLK - 1) / BLK, rows = B * H * G;
+    int rest = rest_len + (append ? 1 : 0), qn = rest_start;
+    const bool flush = rest == BLK;
+    if (flush) { qn += BLK; rest = 0; }
+    const int nb = qn / BLK, R = (nb + 1) * BLK;
+    const int chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
+    AKV_REQUIRE(phase == 1 || chunks_total >= chunks, AKV_ERR_SHAPE, "shard_step: chunks_total %d < local chunks %d",
+                chunks_total, chunks);
+    int rc;
+    if (phase == 1) {
+        const int blocks = flush ? B * H * (2 + D / 64) : B * H;
+        launch_chained(append_flush_kernel, dim3(blocks), dim3(128), flush ? (size_t)BLK * 2 * D : 0, st,
+            static_cast<uint32_t*>(restk), static_cast<uint32_t*>(restv), static_cast<uint16_t*>(k_exp_max),
+            static_cast<uint16_t*>(v_exp_max), static_cast<const uint32_t*>(q), static_cast<const uint32_t*>(k_new),
+            static_cast<const uint32_t*>(v_new), reinterpret_cast<uint16_t*>(sc.kq), sc.kqmax,
+            static_cast<uint8_t*>(k_first_8), static_cast<uint8_t*>(k_mid_4), static_cast<uint8_t*>(k_last_4),
+            static_cast<uint8_t*>(v_first_8), static_cast<uint8_t*>(v_mid_4), static_cast<uint8_t*>(v_last_4), B, H, G, D,
+            rest_len, append ? 1 : (track ? 2 : 0), nmb, max_seq_len, rest_start);
+        if ((rc = cuda_status(cudaGetLastError(), "shard_step append launch")) != AKV_OK) return rc;
+        cudaEvent_t* slot = timing_slot();      // (timing: phase 4 of the same step records into the slot phase 1 took)
+        g_shard_timing = slot;
+        if (slot) cudaEventRecord(slot[0], st);
+        if (nb > 0) {
+            rc = launch_k_compute(static_cast<const uint8_t*>(k_first_8), static_cast<const uint8_t*>(k_mid_4),
+                                  static_cast<const uint8_t*>(k_last_4), sc.kq, sc.kqmax, static_cast<const uint8_t*>(q),
+                                  reinterpret_cast<uint8_t*>(sc.s), B, H, G, nb, nmb, D, BLK, 1.0f / sqrtf((float)D),
+                                  reference, st);
+            if (rc != AKV_OK) return rc;
+        }
+        if (slot) cudaEventRecord(slot[1], st);
+        count_launch();
+        softmax_chunk_stats_kernel<<<dim3(chunks, rows), 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
+            static_cast<const __half*>(restk), static_cast<float*>(exch_out), H, G, D, R, qn, rest, sqrtf((float)D), chunks);
+        return cuda_status(cudaGetLastError(), "shard_step statistics launch");
+    }
+    if (phase == 2) {
+        uint32_t* val = static_cast<uint32_t*>(exch_out);
+        count_launch();
+        softmax_chunk_write_kernel<<<dim3(chunks, rows), 256, 0, st>>>(sc.s, static_cast<const float*>(exch_in), val,
+            reinterpret_cast<int32_t*>(val + (size_t)rows * chunks * TOPK), R, qn, qn + rest, chunks, chunks_total,
+            token_base);
+        return cuda_status(cudaGetLastError(), "shard_step probabilities launch");
+    }
+    if (phase == 3) {
+        const uint32_t* val = static_cast<const uint32_t*>(exch_in);
+        count_launch(2);
+        softmax_class_reduce_kernel<<<rows, 32, 0, st>>>(nullptr, val,
+            reinterpret_cast<const int32_t*>(val + (size_t)rows * chunks_total * TOPK), sc.pval, sc.pidx, sc.stats,
+            chunks_total);
+        probe_rows_gather_kernel<<<rows, 128, 0, st>>>(static_cast<const uint8_t*>(v_first_8), sc.pidx,
+            static_cast<uint8_t*>(exch_out), G, D, max_seq_len, qn, token_base);
+        return cuda_status(cudaGetLastError(), "shard_step winners launch");
+    }
+    // phase 4
+    count_launch();
+    probe_from_rows_kernel<<<rows, 64, 0, st>>>(static_cast<const uint8_t*>(exch_in), sc.pval, sc.test_o, D);
+    launch_chained(amin_kernel, dim3((rows + 3) / 4), dim3(128), 0, st, (const uint16_t*)sc.test_o,
+                   static_cast<const uint8_t*>(v_exp_max), sc.amin, rows, H, G, D);
+    if ((rc = cuda_status(cudaGetLastError(), "shard_step threshold launch")) != AKV_OK) return rc;
+    cudaEvent_t* slot4 = tuning().timing ? g_shard_timing : nullptr;
+    if (slot4) cudaEventRecord(slot4[2], st);
+    if (qn > 0) {
+        rc = launch_v_split(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                            static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
+                            nullptr, sc.o_main32, sc.partial, B, H, G, max_seq_len, D, R, qn, reference, st);
+        if (rc != AKV_OK) return rc;
+    } else {
+        rc = cuda_status(cudaMemsetAsync(sc.o_main32, 0, (size_t)rows * D * sizeof(float), st), "shard_step clear");
+        if (rc != AKV_OK) return rc;
+    }
+    if (slot4) cudaEventRecord(slot4[3], st);
+    g_shard_timing = nullptr;
+    launch_chained(tail_kernel, dim3(rows), dim3(128), 0, st, (const uint16_t*)nullptr, (const float*)sc.o_main32,
+                   (const uint16_t*)sc.s, static_cast<const __half*>(restv), static_cast<__half*>(nullptr),
+                   (const float*)sc.stats, static_cast<float*>(exch_out), H, G, D, R, qn, rest);
+    return cuda_status(cudaGetLastError(), "shard_step tail launch");
 }
 
 int akv_decode_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,

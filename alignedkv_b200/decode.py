@@ -19,7 +19,7 @@ from .extension.KV_cache_cpp_extention import cuda_module
 __all__ = ["DecodeLayer"]
 
 
-AKV_STEP_REFERENCE, AKV_STEP_ORDER_FREE, AKV_STEP_NO_APPEND = 1, 2, 4
+AKV_STEP_REFERENCE, AKV_STEP_ORDER_FREE, AKV_STEP_NO_APPEND, AKV_STEP_TRACK_MAXIMA = 1, 2, 4, 8
 
 
 class DecodeLayer:

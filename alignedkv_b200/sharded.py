@@ -11,6 +11,10 @@ Two ways to shard, neither of which exists in the reference (it is single-device
   a log-sum-exp merge kernel gives every rank the full attention output.  New tokens are appended on the last rank.
   Read decisions are taken from each shard's own softmax and magnitude probe, so they can differ from a
   single-device run over the whole sequence; the merged output is compared against fp32 dense attention.
+* the same split, decision-exact - `DecisionExactShardedDecoder`: the step is cut into four phases
+  (`akv_shard_step`) with a small exchange after each - chunk statistics of the softmax, residue-class candidates
+  of the magnitude probe, the winners' high-byte rows, the partial outputs - so that probabilities, thresholds and
+  with them every plane-read decision are those of one device holding the whole sequence.
 """
 from __future__ import annotations
 
@@ -18,7 +22,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["shard_bounds", "shard_batch", "SequenceShardedDecoder"]
+__all__ = ["shard_bounds", "shard_batch", "chunk_bounds", "SequenceShardedDecoder", "DecisionExactShardedDecoder"]
 
 BLOCK = 64
 
@@ -110,3 +114,220 @@ class SequenceShardedDecoder:
             self.dist.all_gather_into_tensor(flat, rec.contiguous(), group=self.group)   # rank-major concatenation
             gathered = flat.view(self.world, rows, self.D + 2)
         return self.backend.merge(gathered, rows, self.D).reshape(self.B, 1, self.Hq, self.D)
+
+
+SM_CHUNK = 4096     # scores per chunk of the split softmax (the granularity of decision-exact shards)
+
+
+def chunk_bounds(n_tokens: int, world: int, chunk: int = SM_CHUNK):
+    """Contiguous token ranges [lo, hi) per rank whose starts are multiples of `chunk`: whole chunks, as even as
+    possible, everything that is left (a partial chunk included) on the last rank."""
+    nchunk = n_tokens // chunk
+    per, extra = divmod(nchunk, world)
+    bounds, lo = [], 0
+    for r in range(world):
+        hi = lo + (per + (1 if r < extra else 0)) * chunk
+        bounds.append((lo, hi))
+        lo = hi
+    bounds[-1] = (bounds[-1][0], n_tokens)
+    return bounds
+
+
+def local_chunks(quantized_tokens: int, chunk: int = SM_CHUNK) -> int:
+    """Chunks of a shard's score row: the row holds the quantized tokens plus one block for the residual tokens."""
+    return -(-((quantized_tokens // BLOCK + 1) * BLOCK) // chunk)
+
+
+def pad_chunks(x: torch.Tensor, cmax: int, fill: float):
+    """[rows, chunks, ...] -> [rows, cmax, ...], the missing chunks filled with `fill` (an empty chunk)."""
+    if x.shape[1] == cmax:
+        return x.contiguous()
+    pad = torch.full((x.shape[0], cmax - x.shape[1]) + tuple(x.shape[2:]), fill, dtype=x.dtype, device=x.device)
+    return torch.cat([x, pad], dim=1).contiguous()
+
+
+def pad_stats(x: torch.Tensor, cmax: int) -> torch.Tensor:
+    """Chunk statistics [rows, chunks, 2] -> [rows, cmax, 2]; an empty chunk is (maximum -inf, sum 0)."""
+    return torch.cat([pad_chunks(x[:, :, 0:1], cmax, float("-inf")), pad_chunks(x[:, :, 1:2], cmax, 0.0)], dim=2).contiguous()
+
+
+def sequence_order(gathered: torch.Tensor) -> torch.Tensor:
+    """[world, rows, cmax, ...] as gathered rank by rank -> [rows, world * cmax, ...]: every row's chunks in the order
+    of the sequence (padding chunks stay where they are; they are empty and take no part in any reduction)."""
+    w, rows, cmax = gathered.shape[:3]
+    return gathered.transpose(0, 1).reshape((rows, w * cmax) + tuple(gathered.shape[3:])).contiguous()
+
+
+class TorchComm:
+    """The three collectives the protocol needs, over torch.distributed (NCCL on GPUs, gloo on CPU tensors)."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """-> [world, *x.shape], rank-major."""
+        if self.world == 1:
+            return x.unsqueeze(0)
+        flat = torch.empty((self.world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        self.dist.all_gather_into_tensor(flat, x.contiguous(), group=self.group)
+        return flat.view((self.world,) + tuple(x.shape))
+
+    def all_reduce(self, x: torch.Tensor, op: str) -> torch.Tensor:
+        if self.world > 1:
+            self.dist.all_reduce(x, op=self.dist.ReduceOp.SUM if op == "sum" else self.dist.ReduceOp.MAX,
+                                 group=self.group)
+        return x
+
+
+class _CudaShardEngine:
+    """A DecodeLayer over the local tokens, stepped through akv_shard_step."""
+
+    def __init__(self, bsz, max_local, n_kv_heads, head_dim, device, n_q_heads, is_last):
+        from .decode import DecodeLayer, AKV_STEP_ORDER_FREE, AKV_STEP_NO_APPEND, AKV_STEP_TRACK_MAXIMA
+        self.layer = DecodeLayer(bsz, max_local, n_kv_heads, head_dim, device, n_q_heads=n_q_heads, v_mode="order_free")
+        self.lib, self.device = self.layer.lib, self.layer.device
+        self.is_last = is_last
+        self.flags = AKV_STEP_ORDER_FREE | (0 if is_last else (AKV_STEP_NO_APPEND | AKV_STEP_TRACK_MAXIMA))
+
+    def prefill(self, k, v):
+        self.layer.prefill(k, v)
+
+    def set_maxima(self, k_exp, v_exp):
+        self.layer.k_exp_max.copy_(k_exp)
+        self.layer.v_exp_max.copy_(v_exp)
+
+    def phase(self, i, exch_in, q, k_new, v_new, chunks, chunks_total, token_base):
+        lay = self.layer
+        rows, D = lay.B * lay.Hq, lay.D
+        shape, dtype = {1: ((rows, chunks, 2), torch.float32), 2: ((2, rows, chunks, 32), torch.int32),
+                        3: ((rows, 32, D), torch.uint8), 4: ((rows, D + 2), torch.float32)}[i]
+        out = torch.empty(shape, dtype=dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            rc = self.lib.akv_shard_step(
+                lay.k_first_8.data_ptr(), lay.k_mid_4.data_ptr(), lay.k_last_4.data_ptr(),
+                lay.v_first_8.data_ptr(), lay.v_mid_4.data_ptr(), lay.v_last_4.data_ptr(),
+                lay.k_exp_max.data_ptr(), lay.v_exp_max.data_ptr(), lay.restk.data_ptr(), lay.restv.data_ptr(),
+                q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), exch_in.data_ptr() if exch_in is not None else None,
+                out.data_ptr(), lay.scratch.data_ptr(), lay.scratch.numel(), lay.B, lay.H, lay.G, D,
+                lay.L, lay.rest_len, lay.rest_start, token_base, chunks_total, self.flags, i,
+                torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check("shard_step", rc)
+        return out
+
+    def finish_step(self):
+        """Advance the residual state after phase 4 (as DecodeLayer.decode does)."""
+        lay = self.layer
+        if self.is_last:
+            if lay.rest_len + 1 == BLOCK:
+                lay.rest_start += BLOCK
+                lay.rest_len = 0
+            else:
+                lay.rest_len += 1
+            lay.cache_len += 1
+
+    def snapshot(self):
+        return self.layer.snapshot()
+
+    def restore(self, snap):
+        self.layer.restore(snap)
+
+
+class DecisionExactShardedDecoder:
+    """One layer's cache with the sequence split across ranks at multiples of 4096 tokens, decoded with the read
+    decisions of a single device (see the module docstring; `akv_shard_step` documents the four phases).
+
+    The exponent maxima every decision starts from are those of the whole sequence on every rank: after the prompt
+    they are reduced across ranks, and every rank takes each new token into them (the token is stored on the last
+    rank only).  `decode` runs the phases with the exchanges of `comm`; a test may also call `phase(i, exch_in, ...)`
+    on several instances in turn and do the exchanges itself.  engine: object with prefill / set_maxima / phase /
+    finish_step / snapshot / restore (default: the CUDA kernels); tests substitute one to exercise the exchanges with
+    gloo on CPU."""
+
+    def __init__(self, bsz: int, prompt_len: int, max_new_tokens: int, n_kv_heads: int, head_dim: int, device,
+                 n_q_heads: int | None = None, comm=None, rank: int | None = None, world: int | None = None,
+                 engine=None):
+        self.comm = comm if comm is not None else TorchComm()
+        self.world = world if world is not None else self.comm.world
+        if rank is None:
+            rank = self.comm.dist.get_rank(self.comm.group) if self.world > 1 else 0
+        self.rank = rank
+        self.B, self.D, self.H = bsz, head_dim, n_kv_heads
+        self.Hq = n_kv_heads if n_q_heads is None else n_q_heads
+        self.rows = bsz * self.Hq
+        self.bounds = chunk_bounds(prompt_len, self.world)
+        lo, hi = self.bounds[rank]
+        self.token_base, self.local_len = lo, hi - lo
+        self.is_last = rank == self.world - 1
+        max_local = self.local_len + (max_new_tokens if self.is_last else 0)
+        max_local = max(BLOCK, -(-max_local // BLOCK) * BLOCK)
+        self.engine = engine if engine is not None else _CudaShardEngine(bsz, max_local, n_kv_heads, head_dim, device,
+                                                                         self.Hq, self.is_last)
+        self.device = torch.device(device)
+        self.appended = 0                     # tokens decoded so far (every rank counts them)
+
+    @property
+    def layer(self):
+        return self.engine.layer
+
+    # ---- geometry every rank can compute for every other rank
+    def _chunks_of(self, r: int, appended: int) -> int:
+        lo, hi = self.bounds[r]
+        n = hi - lo + (appended if r == self.world - 1 else 0)
+        return local_chunks((n // BLOCK) * BLOCK)
+
+    def prefill(self, k_shard, v_shard) -> None:
+        """k_shard, v_shard: this rank's tokens [B, hi-lo, H, D] of the prompt."""
+        from .extension._planes import exponent_field
+        if k_shard.shape[1] != self.local_len:
+            raise ValueError(f"rank {self.rank} owns {self.local_len} tokens, got {k_shard.shape[1]}")
+        if self.local_len:
+            self.engine.prefill(k_shard, v_shard)
+        # maxima of the whole prompt: the reference takes the exponent of the SIGNED maximum (k_cache_file.py:77-78)
+        exps = []
+        for x in (k_shard, v_shard):
+            if self.local_len:
+                mx = torch.max(x, dim=1, keepdim=True).values.float()
+            else:
+                mx = torch.full((self.B, 1, self.H, self.D), float("-inf"), device=x.device)
+            exps.append(exponent_field(self.comm.all_reduce(mx.contiguous(), "max").half()))
+        self.engine.set_maxima(*exps)
+
+    def phase(self, i: int, exch_in, q, k_new, v_new, chunks_total: int = 0):
+        """Run phase i (1..4) of the step in progress and return its exchange buffer (see akv_shard_step)."""
+        return self.engine.phase(i, exch_in, q, k_new, v_new, self._chunks_of(self.rank, self.appended + 1),
+                                 chunks_total, self.token_base)
+
+    def finish_step(self) -> None:
+        self.engine.finish_step()
+        self.appended += 1
+
+    def snapshot(self):
+        """State to come back to with `restore` (see DecodeLayer.snapshot)."""
+        return dict(engine=self.engine.snapshot(), appended=self.appended)
+
+    def restore(self, snap) -> None:
+        self.engine.restore(snap["engine"])
+        self.appended = snap["appended"]
+
+    def decode(self, q, k_new, v_new):
+        """q [B,1,Hq,D], k_new / v_new [B,1,H,D] (needed on every rank: they feed the exponent maxima) -> output
+        [B,1,Hq,D], the same on every rank."""
+        cmax = max(self._chunks_of(r, self.appended + 1) for r in range(self.world))
+        total = self.world * cmax
+        st = pad_stats(self.phase(1, None, q, k_new, v_new), cmax)
+        st_all = sequence_order(self.comm.all_gather(st))                               # [rows, total, 2]
+        cand = self.phase(2, st_all, q, k_new, v_new, total)                            # [2, rows, chunks, 32]
+        cand = torch.stack([pad_chunks(cand[0], cmax, 0), pad_chunks(cand[1], cmax, 0)])
+        g = self.comm.all_gather(cand)                                                  # [world, 2, rows, cmax, 32]
+        cand_all = torch.stack([sequence_order(g[:, 0]), sequence_order(g[:, 1])]).contiguous()
+        win_rows = self.phase(3, cand_all, q, k_new, v_new, total)                      # [rows, 32, D] bytes
+        win_rows = self.comm.all_reduce(win_rows, "sum")       # every byte is non-zero on at most one rank
+        part = self.phase(4, win_rows, q, k_new, v_new, total)                          # [rows, D + 2]
+        parts = self.comm.all_gather(part)[:, :, 2:]                                    # [world, rows, D]
+        out = parts[0].clone()
+        for r in range(1, self.world):                                                  # rank order, fp32
+            out += parts[r]
+        self.finish_step()
+        return out.half().reshape(self.B, 1, self.Hq, self.D)

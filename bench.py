@@ -46,6 +46,9 @@ WORKLOADS = {
                                      v_mode="exact"),
     "long-context-decode": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072, sharding="sequence",
                                 v_mode="order_free"),
+    # the same with the four-phase step whose read decisions are those of one device holding the whole sequence
+    "long-context-decode-exact": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072,
+                                      sharding="sequence_exact", v_mode="order_free"),
     # full random-init Llama-2-7B decoder, AlignedKV cache on every layer: prompt of 1024 uniform-random ids, then greedy
     # decoding; a step = one token per sequence through all 32 layers (cache_len = prompt length, it grows by one per step)
     "llama2-7b-decoder": dict(batch=16, heads=32, kv_heads=32, head_dim=128, cache_len=1024, sharding="replicate",
@@ -211,7 +214,8 @@ def run_ours(args):
     Bt, Hq, H, D, L = (WORKLOAD[k_] for k_ in ("batch", "heads", "kv_heads", "head_dim", "cache_len"))
     sharding = WORKLOAD["sharding"] if world > 1 else "replicate"
     v_mode = args.v_mode or WORKLOAD["v_mode"]
-    from alignedkv_b200.sharded import SequenceShardedDecoder, shard_batch, shard_bounds
+    from alignedkv_b200.sharded import (DecisionExactShardedDecoder, SequenceShardedDecoder, chunk_bounds, shard_batch,
+                                        shard_bounds)
     if sharding == "batch":
         lo, hi = shard_batch(Bt, world, rank)
         B = hi - lo
@@ -234,6 +238,18 @@ def run_ours(args):
         seq.prefill(k[:, :hi - lo].contiguous(), v[:, :hi - lo].contiguous())
         layer = seq.backend.layer
         k_tok, v_tok = k[:, hi - lo:].contiguous(), v[:, hi - lo:].contiguous()
+    elif sharding == "sequence_exact" or WORKLOAD["sharding"] == "sequence_exact":
+        # rank r holds tokens [lo, hi) of the L-1 cached tokens, lo a multiple of 4096; every rank sees the decode token
+        # (it feeds the exponent maxima), the last rank stores it
+        seq = DecisionExactShardedDecoder(B, L - 1, 1, H, D, dev, n_q_heads=Hq)
+        lo, hi = chunk_bounds(L - 1, world)[rank]
+        k, v = draw(hi - lo + 1)
+        seq.prefill(k[:, :hi - lo].contiguous(), v[:, :hi - lo].contiguous())
+        layer = seq.layer
+        k_tok, v_tok = k[:, hi - lo:].contiguous(), v[:, hi - lo:].contiguous()
+        if world > 1:
+            dist.broadcast(k_tok, src=world - 1)
+            dist.broadcast(v_tok, src=world - 1)
     else:
         seq = None
         layer = DecodeLayer(B, L, H, D, dev, n_q_heads=Hq, v_mode=v_mode)
@@ -242,13 +258,14 @@ def run_ours(args):
         k_tok, v_tok = k[:, L - 1:].contiguous(), v[:, L - 1:].contiguous()
     del k, v
     q = torch.randn(B, 1, Hq, D, device=dev, generator=torch.Generator(device=dev).manual_seed(args.seed + 7)).half()
-    snap = layer.snapshot()                                # state before the decode token (63 tokens in the residual)
+    owner = seq if isinstance(seq, DecisionExactShardedDecoder) else layer
+    snap = owner.snapshot()                                # state before the decode token (63 tokens in the residual)
 
     def decode(q_, k_, v_):
         return seq.decode(q_, k_, v_) if seq is not None else layer.decode(q_, k_, v_)
 
     def step_resident():
-        layer.restore(snap)
+        owner.restore(snap)
         return decode(q, k_tok, v_tok)
 
     # end-to-end number: the step's inputs (q | k | v of the new token) lie in ONE pinned host buffer and cross in
@@ -260,7 +277,7 @@ def run_ours(args):
     hout = torch.empty((B, 1, Hq, D), dtype=torch.half).pin_memory()
 
     def step_e2e():
-        layer.restore(snap)
+        owner.restore(snap)
         din.copy_(hin, non_blocking=True)
         out = decode(dq, dk, dv)
         hout.copy_(out, non_blocking=True)
@@ -347,7 +364,12 @@ def run_ours(args):
                        "sharding": {"replicate": "(batch, kv-head) units, no collective; every rank runs the full shape",
                                     "batch": "batch rows split across ranks, no collective",
                                     "sequence": "cached sequence split across ranks; one all-gather of (max, sum, "
-                                                "output) records + log-sum-exp merge"}[sharding],
+                                                "output) records + log-sum-exp merge",
+                                    "sequence_exact": "cached sequence split across ranks at multiples of 4096 tokens; "
+                                                      "four-phase step (akv_shard_step) with exchanges of chunk "
+                                                      "statistics, probe candidates, winner rows and partial outputs: "
+                                                      "read decisions of one device holding the whole sequence"}[
+                                       "sequence_exact" if isinstance(seq, DecisionExactShardedDecoder) else sharding],
                        "step": "rewind to cache_len-1 tokens -> append the last token (flushes a 64-token block through "
                                "the plane writers) -> decode",
                        "l2": "inputs larger than L2 (planes %.0f MiB per GPU)" % (

@@ -149,6 +149,7 @@ long long akv_decode_scratch_bytes(int bsz, int n_heads, int head_dim, int max_s
 #define AKV_STEP_REFERENCE 1
 #define AKV_STEP_ORDER_FREE 2
 #define AKV_STEP_NO_APPEND 4
+#define AKV_STEP_TRACK_MAXIMA 8   /* with AKV_STEP_NO_APPEND (akv_shard_step): the new token still updates the exponent maxima */
 int akv_k_cache_compute_gqa(const void* k_first_8, const void* k_mid_4, const void* k_last_4,
                             const void* kq, const void* kqmax, const void* q, void* s_out,
                             int bsz, int n_kv_heads, int group, int n_blocks, int n_max_blocks, int d_head, int d_block,
@@ -232,6 +233,31 @@ int akv_decode_step_noalloc(void* k_first_8, void* k_mid_4, void* k_last_4, void
                             const void* q, const void* k_new, const void* v_new, void* out,
                             int bsz, int n_heads, int head_dim, int max_seq_len, int rest_len, int rest_start,
                             int reference, void* stream);
+
+/*
+ * One decode step over a shard of a sequence-sharded cache, cut into four phases with an exchange between them so that
+ * every shard takes the read decisions one device holding the whole sequence would take (no counterpart in the
+ * reference, which is single-device).  rows = bsz * n_kv_heads * group; a chunk is 4096 scores; local chunks =
+ * ceil(((quantized local tokens after the step) / 64 + 1) * 64 / 4096).
+ *   phase 1: append (last shard) or, with AKV_STEP_NO_APPEND | AKV_STEP_TRACK_MAXIMA, only take the new token into the
+ *            exponent maxima; q.K^T; chunk statistics            -> exch_out float [rows][local chunks][2]
+ *   phase 2: exch_in float [rows][chunks_total][2] (every shard's statistics, sequence order); probabilities of the
+ *            local tokens and residue-class candidates           -> exch_out u32 [rows][local chunks][32] values, then
+ *                                                                   i32 [rows][local chunks][32] positions / 32
+ *   phase 3: exch_in the same two arrays over chunks_total; winners; high-byte rows of the winners held here
+ *                                                                -> exch_out bytes [rows][32][head_dim]
+ *   phase 4: exch_in the shards' row buffers added up; probe, threshold bytes, order-free P.V, residual tokens
+ *                                                                -> exch_out float [rows][head_dim + 2]; words 2.. are
+ *                                                                   this shard's part of the output (parts add up)
+ * token_base: position of local token 0 in the whole sequence (a multiple of 4096).  All phases take the state before
+ * the step; the caller advances rest_len / rest_start after phase 4 as for akv_decode_step_ex.  scratch: at least
+ * akv_decode_scratch_bytes_ex(..., AKV_STEP_ORDER_FREE) bytes, untouched between the phases.  head_dim 128.
+ */
+int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                   void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                   const void* v_new, const void* exch_in, void* exch_out, void* scratch, long long scratch_bytes,
+                   int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
+                   int token_base, int chunks_total, int flags, int phase, void* stream);
 
 /*
  * Benchmark instrumentation (no counterpart in the reference): with akv_set_tuning("timing", 1), akv_decode_step

@@ -305,3 +305,80 @@ def test_sequence_shards_merge_to_dense_attention(akv_lib):
     err = rel_err(got, truth)
     print(f"sequence-sharded merge vs fp32 dense attention: {err:.2e}")
     assert err <= 6e-2
+
+
+class _LoneComm:
+    """Stands in for the collectives when several shards are driven phase by phase inside one process."""
+    world = 1
+
+    def all_reduce(self, x, op):
+        return x
+
+
+@pytest.mark.parametrize("prompt,steps,world", [(16500, 3, 2), (20470, 4, 3)])
+def test_decision_exact_shards(akv_lib, prompt, steps, world):
+    """Sequence shards decoded with akv_shard_step (exchanges done by hand, all shards on this GPU) against one
+    DecodeLayer over the whole sequence that takes the split-softmax path: probabilities and threshold bytes - hence
+    every plane-read decision - bit-identical, outputs equal up to the grouping of the fp32 partial sums."""
+    from alignedkv_b200.decode import DecodeLayer
+    from alignedkv_b200.extension._planes import exponent_field
+    from alignedkv_b200.sharded import (DecisionExactShardedDecoder, chunk_bounds, pad_chunks, pad_stats,
+                                        sequence_order)
+    B, H, G, D = 1, 4, 1, 128
+    Hq, L = H * G, prompt + steps
+    k, v, _ = make_kvq(71, B, L, H, D)
+    rng = np.random.default_rng(72)
+    qs = rng.standard_normal((steps, B, 1, Hq, D), dtype=np.float32).astype(np.float16)
+    max_len = -(-L // 64) * 64
+    whole = DecodeLayer(B, max_len, H, D, "cuda:0", n_q_heads=Hq, v_mode="order_free")
+    whole.prefill(dev(k[:, :prompt]), dev(v[:, :prompt]))
+    bounds = chunk_bounds(prompt, world)
+    decs = [DecisionExactShardedDecoder(B, prompt, steps, H, D, "cuda:0", n_q_heads=Hq, comm=_LoneComm(), rank=r,
+                                        world=world) for r in range(world)]
+    for r, dec in enumerate(decs):
+        lo, hi = bounds[r]
+        dec.prefill(dev(np.ascontiguousarray(k[:, lo:hi])), dev(np.ascontiguousarray(v[:, lo:hi])))
+        # the exponent maxima of the whole prompt (what the all-reduce gives every rank)
+        dec.layer.k_exp_max.copy_(exponent_field(dev(k[:, :prompt]).max(dim=1, keepdim=True).values))
+        dec.layer.v_exp_max.copy_(exponent_field(dev(v[:, :prompt]).max(dim=1, keepdim=True).values))
+    assert torch.equal(decs[0].layer.k_exp_max, whole.k_exp_max) and torch.equal(decs[0].layer.v_exp_max, whole.v_exp_max)
+    rows = B * Hq
+    for i in range(steps):
+        q, kt, vt = dev(qs[i]), dev(k[:, prompt + i:prompt + i + 1]), dev(v[:, prompt + i:prompt + i + 1])
+        want = whole.decode(q, kt, vt)
+        cmax = max(d_._chunks_of(r, d_.appended + 1) for r, d_ in enumerate(decs))
+        total = world * cmax
+        st = [pad_stats(d_.phase(1, None, q, kt, vt), cmax) for d_ in decs]
+        st_all = sequence_order(torch.stack(st))
+        cand = [d_.phase(2, st_all, q, kt, vt, total) for d_ in decs]
+        g = torch.stack([torch.stack([pad_chunks(c[0], cmax, 0), pad_chunks(c[1], cmax, 0)]) for c in cand])
+        cand_all = torch.stack([sequence_order(g[:, 0]), sequence_order(g[:, 1])]).contiguous()
+        win = [d_.phase(3, cand_all, q, kt, vt, total) for d_ in decs]
+        win_all = win[0].clone()
+        for w_ in win[1:]:
+            assert int(((win_all != 0) & (w_ != 0)).sum()) == 0, "a winner's row came from two shards"
+            win_all += w_
+        parts = [d_.phase(4, win_all, q, kt, vt, total)[:, 2:] for d_ in decs]
+        got = parts[0].clone()
+        for p_ in parts[1:]:
+            got += p_
+        torch.cuda.synchronize()
+        # decisions: threshold bytes and probabilities of every shard against the whole-sequence run
+        a_off = whole._scratch_offset("amin")
+        amin_whole = whole.scratch[a_off:a_off + rows].cpu()
+        qn_whole = whole.rest_start
+        R_whole = (qn_whole // 64 + 1) * 64
+        p_whole = whole.scratch[:rows * R_whole * 2].view(torch.int16).view(rows, R_whole).cpu()
+        for r, d_ in enumerate(decs):
+            lay = d_.layer
+            o = lay._scratch_offset("amin")
+            assert torch.equal(lay.scratch[o:o + rows].cpu(), amin_whole), f"step {i}: threshold bytes of shard {r}"
+            d_.finish_step()
+            qn = lay.rest_start
+            R_loc = (qn // 64 + 1) * 64
+            p_loc = lay.scratch[:rows * R_loc * 2].view(torch.int16).view(rows, R_loc).cpu()
+            n_loc = qn + lay.rest_len
+            assert torch.equal(p_loc[:, :n_loc], p_whole[:, d_.token_base:d_.token_base + n_loc]), \
+                f"step {i}: probabilities of shard {r}"
+        assert rel_err(got.cpu().numpy(), want.float().cpu().numpy().reshape(rows, D)) <= TOL
+    assert akv_lib.akv_device_error_flag() == 0

@@ -1,6 +1,7 @@
-"""Host-side logic of the sharded decoders on CPU: shard arithmetic, and the sequence-sharded protocol
+"""Host-side logic of the sharded decoders on CPU: shard arithmetic, the sequence-sharded protocol
 (local record -> all-gather -> log-sum-exp merge) run as two gloo ranks with the numpy oracle standing in for the
-CUDA kernels."""
+CUDA kernels, and the exchanges of the decision-exact protocol run as two gloo ranks with an engine that checks what
+each phase receives."""
 import os
 import socket
 
@@ -92,3 +93,128 @@ def test_sequence_sharded_protocol_two_gloo_ranks():
     # against fp32 dense attention the aligned path itself is 1e-2 .. 4e-2 off (skipped nibble planes, fp16 scores); the
     # bound only guards the protocol (a wrong merge is off by order 1)
     assert max(errs[0]) <= 6e-2, errs[0]
+
+
+def test_chunk_bounds_and_exchange_layout():
+    from alignedkv_b200.sharded import chunk_bounds, local_chunks, pad_chunks, pad_stats, sequence_order
+    b = chunk_bounds(131071, 8)
+    assert b[0] == (0, 16384) and b[-1] == (114688, 131071) and all(lo % 4096 == 0 for lo, _ in b)
+    assert chunk_bounds(20470, 3) == [(0, 8192), (8192, 12288), (12288, 20470)]
+    assert chunk_bounds(5000, 4) == [(0, 4096), (4096, 4096), (4096, 4096), (4096, 5000)]   # empty shards are allowed
+    assert local_chunks(0) == 1 and local_chunks(4032) == 1 and local_chunks(4096) == 2 and local_chunks(8192) == 3
+    x = torch.arange(2 * 1 * 2, dtype=torch.float32).view(2, 1, 2)
+    p = pad_stats(x, 3)
+    assert p.shape == (2, 3, 2) and torch.isinf(p[:, 1:, 0]).all() and (p[:, 1:, 0] < 0).all() and (p[:, 1:, 1] == 0).all()
+    g = torch.stack([torch.full((2, 3, 1), float(r)) for r in range(4)])      # [world, rows, cmax, 1]
+    s = sequence_order(g)
+    assert s.shape == (2, 12, 1) and s[0, :, 0].tolist() == [0, 0, 0, 1, 1, 1, 2, 2, 2, 3, 3, 3]
+    assert pad_chunks(torch.ones(2, 3, 5), 3, 0).shape == (2, 3, 5)
+
+
+class CheckingEngine:
+    """Stands in for the CUDA kernels: every phase returns a buffer that encodes (rank, chunk) and checks that what it
+    receives is every rank's buffer in sequence order."""
+
+    def __init__(self, rank, world, rows, D, chunks_of):
+        self.rank, self.world, self.rows, self.D, self.chunks_of = rank, world, rows, D, chunks_of
+        self.maxima = None
+        self.steps = 0
+
+    def prefill(self, k, v):
+        pass
+
+    def set_maxima(self, k_exp, v_exp):
+        self.maxima = (k_exp.clone(), v_exp.clone())
+
+    def phase(self, i, exch_in, q, k_new, v_new, chunks, chunks_total, token_base):
+        cmax = max(self.chunks_of)
+        assert chunks == self.chunks_of[self.rank]
+        if i == 1:
+            st = torch.empty(self.rows, chunks, 2)
+            for c in range(chunks):
+                st[:, c, 0] = 100.0 * self.rank + c
+                st[:, c, 1] = self.rank + 1.0
+            return st
+        assert chunks_total == self.world * cmax
+        if i == 2:
+            assert exch_in.shape == (self.rows, chunks_total, 2)
+            for r in range(self.world):
+                for c in range(cmax):
+                    m, l = exch_in[0, r * cmax + c].tolist()
+                    if c < self.chunks_of[r]:
+                        assert (m, l) == (100.0 * r + c, r + 1.0)
+                    else:
+                        assert m == float("-inf") and l == 0.0
+            cand = torch.zeros(2, self.rows, chunks, 32, dtype=torch.int32)
+            cand[0] += 1000 * (self.rank + 1)
+            cand[1] += token_base // 32
+            return cand
+        if i == 3:
+            assert exch_in.shape == (2, self.rows, chunks_total, 32) and exch_in.dtype == torch.int32
+            for r in range(self.world):
+                want = 1000 * (r + 1)
+                assert int(exch_in[0, 0, r * cmax, 0]) == want
+                if self.chunks_of[r] < cmax:
+                    assert int(exch_in[0, 0, r * cmax + cmax - 1, 0]) == 0
+            rows = torch.zeros(self.rows, 32, self.D, dtype=torch.uint8)
+            rows[:, self.rank::self.world] = self.rank + 1          # "the winners this rank holds"
+            return rows
+        assert exch_in.dtype == torch.uint8
+        for j in range(32):
+            assert int(exch_in[0, j, 0]) == j % self.world + 1
+        part = torch.zeros(self.rows, self.D + 2)
+        part[:, 2:] = self.rank + 1.0
+        return part
+
+    def finish_step(self):
+        self.steps += 1
+
+    def snapshot(self):
+        return self.steps
+
+    def restore(self, snap):
+        self.steps = snap
+
+
+def _exact_worker(rank, world, port, results):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from alignedkv_b200.sharded import DecisionExactShardedDecoder, chunk_bounds, local_chunks
+        B, H, D, prompt = 1, 4, 128, 12288 + 200
+        bounds = chunk_bounds(prompt, world)
+        chunks_of = [local_chunks(((hi - lo + (1 if r == world - 1 else 0)) // 64) * 64) for r, (lo, hi) in enumerate(bounds)]
+        eng = CheckingEngine(rank, world, B * H, D, chunks_of)
+        dec = DecisionExactShardedDecoder(B, prompt, 4, H, D, "cpu", engine=eng)
+        lo, hi = bounds[rank]
+        k = torch.full((B, hi - lo, H, D), 1.0 + rank).half()
+        k[:, 0, 0, 0] = -3.0 if rank == 0 else 0.5
+        dec.prefill(k, k.clone())
+        # signed maximum over BOTH ranks' tokens: 2.0 (exponent 16) everywhere
+        assert int(eng.maxima[0].min()) == 16 and int(eng.maxima[0].max()) == 16
+        z = torch.zeros(B, 1, H, D).half()
+        out = dec.decode(z, z, z)
+        assert eng.steps == 1 and dec.appended == 1
+        results[rank] = out.float().flatten()[:4].tolist()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_decision_exact_exchanges_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        procs = [ctx.Process(target=_exact_worker, args=(r, 2, port, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(180)
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+        res = dict(results)
+    assert res[0] == res[1] == [3.0, 3.0, 3.0, 3.0]      # the parts (1 and 2) added up, the same on every rank
