@@ -375,21 +375,28 @@ softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ 
 __global__ void __launch_bounds__(256)
 softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ cstat, uint32_t* __restrict__ cand_val,
                            int32_t* __restrict__ cand_idx, int R, int qn, int len, int chunks, int stat_chunks,
-                           int t_base) {
-    // chunks: chunks of this row held here (the grid); stat_chunks >= chunks: chunks whose statistics make up the
-    // row's (they include the other shards' when the sequence is sharded); t_base: position of local token 0 in the
-    // whole sequence (a multiple of 32, so residue classes are the same locally and globally)
+                           int stat_ranks, int t_base) {
+    // chunks: row stride (in chunks) of the candidate arrays, at least the chunks of this row held here (the grid);
+    // stat_chunks: chunks whose statistics make up the row's (they include the other shards' when the sequence is
+    // sharded), laid out as stat_ranks blocks of [rows][stat_chunks / stat_ranks] as an all-gather leaves them;
+    // t_base: position of local token 0 in the whole sequence (a multiple of 32, so residue classes are the same
+    // locally and globally)
+    const int spr = stat_chunks / stat_ranks;       // chunks per rank block
+    auto stat = [&](int c) {
+        const int r = c / spr;
+        return cstat + (((size_t)r * gridDim.y + blockIdx.y) * spr + (c - r * spr)) * 2;
+    };
     __shared__ uint32_t cand_v[256];
     __shared__ int32_t cand_i[256];
     const int bhq = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
     uint16_t* row = s + (size_t)bhq * R;
     // row statistics from the chunk statistics, in chunk order (every CTA of the row computes the same values)
     float m = -INFINITY;
-    for (int c = 0; c < stat_chunks; ++c) m = fmaxf(m, cstat[((size_t)bhq * stat_chunks + c) * 2]);
+    for (int c = 0; c < stat_chunks; ++c) m = fmaxf(m, stat(c)[0]);
     float sum = 0.f;
     for (int c = 0; c < stat_chunks; ++c) {
-        const float mc = cstat[((size_t)bhq * stat_chunks + c) * 2];
-        if (mc > -INFINITY) sum += cstat[((size_t)bhq * stat_chunks + c) * 2 + 1] * expf(mc - m);
+        const float mc = stat(c)[0];
+        if (mc > -INFINITY) sum += stat(c)[1] * expf(mc - m);
     }
     const int t0 = ch * SM_CHUNK, t1 = min(R, t0 + SM_CHUNK);
     uint32_t best = 0;
@@ -422,13 +429,23 @@ softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ c
 __global__ void __launch_bounds__(32)
 softmax_class_reduce_kernel(const float* __restrict__ cstat, const uint32_t* __restrict__ cand_val,
                             const int32_t* __restrict__ cand_idx, uint16_t* __restrict__ pval,
-                            int32_t* __restrict__ pidx, float* __restrict__ stats, int chunks) {
+                            int32_t* __restrict__ pidx, float* __restrict__ stats, int chunks, int ranks) {
+    // ranks == 1: cand_val / cand_idx are [rows][chunks][32].  ranks > 1 (gathered from the shards of a sequence):
+    // cand_val points at `ranks` blocks of {values [rows][chunks/ranks][32], positions [rows][chunks/ranks][32]} and
+    // cand_idx is unused.
     const int bhq = blockIdx.x, tid = threadIdx.x;
+    const int cpr = chunks / ranks;
+    const size_t block = (size_t)gridDim.x * cpr * TOPK;          // one array of one rank
     uint32_t bv = 0;
     int32_t bi = 0;
     for (int c = 0; c < chunks; ++c) {      // chunks are in position order: a later chunk wins only when larger
-        const uint32_t v = cand_val[((size_t)bhq * chunks + c) * TOPK + tid];
-        if (v > bv) { bv = v; bi = cand_idx[((size_t)bhq * chunks + c) * TOPK + tid]; }
+        const int r = c / cpr;
+        const size_t e = ((size_t)bhq * cpr + (c - r * cpr)) * TOPK + tid;
+        const uint32_t v = ranks == 1 ? cand_val[e] : cand_val[(size_t)r * 2 * block + e];
+        if (v > bv) {
+            bv = v;
+            bi = ranks == 1 ? cand_idx[e] : reinterpret_cast<const int32_t*>(cand_val)[(size_t)r * 2 * block + block + e];
+        }
     }
     pval[(size_t)bhq * TOPK + tid] = (uint16_t)bv;
     pidx[(size_t)bhq * TOPK + tid] = bi;
@@ -703,10 +720,10 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
                                                         sqrtf((float)D), sm_chunks);
         count_launch();
         softmax_chunk_write_kernel<<<grid, 256, 0, st>>>(sc.s, sc.cstat, sc.cand_val, sc.cand_idx, R, qn, qn + rest,
-                                                        sm_chunks, sm_chunks, 0);
+                                                        sm_chunks, sm_chunks, 1, 0);
         count_launch();
         softmax_class_reduce_kernel<<<B * H * G, 32, 0, st>>>(sc.cstat, sc.cand_val, sc.cand_idx, sc.pval, sc.pidx,
-                                                             sc.stats, sm_chunks);
+                                                             sc.stats, sm_chunks, 1);
     } else {
         if (R <= 256 * SM_REGS && B * H * G <= 4 * sm_count()) {
             // few rows: one pass over the row, and the probe runs inside the softmax CTA of its row
@@ -778,6 +795,10 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
 //   phase 1  append (last shard) or take the new token into the exponent maxima only (AKV_STEP_NO_APPEND |
 //            AKV_STEP_TRACK_MAXIMA), q.K^T over the local blocks, per 4096-score chunk the maximum and the sum of
 //            exponentials                          -> exch_out: float [rows][local chunks][2]
+// Layout of what is exchanged: a phase 1 / 2 output has a row stride of out_chunks chunks (0 = the local chunk count;
+// a caller that pads every rank to the same count pre-fills the padding with empty chunks: statistics (-inf, 0),
+// candidates 0).  A phase 2 / 3 input is n_ranks such buffers one after the other, as an all-gather leaves them
+// (chunks_total = n_ranks x the common chunk count), or with n_ranks == 1 one buffer over all chunks.
 //   phase 2  exch_in: float [rows][chunks_total][2], every shard's chunk statistics in sequence order.  Probabilities
 //            with the whole row's maximum and sum, and per local chunk the candidates of the 32 residue classes with
 //            positions in the whole sequence (token_base = position of local token 0, a multiple of 4096)
@@ -797,7 +818,7 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
                    void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
                    const void* v_new, const void* exch_in, void* exch_out, void* scratch, long long scratch_bytes,
                    int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
-                   int token_base, int chunks_total, int flags, int phase, void* stream) {
+                   int token_base, int chunks_total, int n_ranks, int out_chunks, int flags, int phase, void* stream) {
     set_error("");
     const int B = bsz, H = n_kv_heads, G = group, D = head_dim;
     const bool reference = (flags & AKV_STEP_REFERENCE) != 0, append = (flags & AKV_STEP_NO_APPEND) == 0;
@@ -829,8 +850,11 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
     if (flush) { qn += BLK; rest = 0; }
     const int nb = qn / BLK, R = (nb + 1) * BLK;
     const int chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
-    AKV_REQUIRE(phase == 1 || chunks_total >= chunks, AKV_ERR_SHAPE, "shard_step: chunks_total %d < local chunks %d",
-                chunks_total, chunks);
+    AKV_REQUIRE(phase == 1 || (chunks_total >= chunks && n_ranks >= 1 && chunks_total % n_ranks == 0), AKV_ERR_SHAPE,
+                "shard_step: chunks_total %d (local chunks %d) in %d rank blocks", chunks_total, chunks, n_ranks);
+    AKV_REQUIRE(out_chunks == 0 || out_chunks >= chunks, AKV_ERR_SHAPE, "shard_step: out_chunks %d < local chunks %d",
+                out_chunks, chunks);
+    const int oc = out_chunks ? out_chunks : chunks;      // row stride (in chunks) of the phase 1 / 2 outputs
     int rc;
     if (phase == 1) {
         const int blocks = flush ? B * H * (2 + D / 64) : B * H;
@@ -855,14 +879,14 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
         if (slot) cudaEventRecord(slot[1], st);
         count_launch();
         softmax_chunk_stats_kernel<<<dim3(chunks, rows), 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
-            static_cast<const __half*>(restk), static_cast<float*>(exch_out), H, G, D, R, qn, rest, sqrtf((float)D), chunks);
+            static_cast<const __half*>(restk), static_cast<float*>(exch_out), H, G, D, R, qn, rest, sqrtf((float)D), oc);
         return cuda_status(cudaGetLastError(), "shard_step statistics launch");
     }
     if (phase == 2) {
         uint32_t* val = static_cast<uint32_t*>(exch_out);
         count_launch();
         softmax_chunk_write_kernel<<<dim3(chunks, rows), 256, 0, st>>>(sc.s, static_cast<const float*>(exch_in), val,
-            reinterpret_cast<int32_t*>(val + (size_t)rows * chunks * TOPK), R, qn, qn + rest, chunks, chunks_total,
+            reinterpret_cast<int32_t*>(val + (size_t)rows * oc * TOPK), R, qn, qn + rest, oc, chunks_total, n_ranks,
             token_base);
         return cuda_status(cudaGetLastError(), "shard_step probabilities launch");
     }
@@ -871,7 +895,7 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
         count_launch(2);
         softmax_class_reduce_kernel<<<rows, 32, 0, st>>>(nullptr, val,
             reinterpret_cast<const int32_t*>(val + (size_t)rows * chunks_total * TOPK), sc.pval, sc.pidx, sc.stats,
-            chunks_total);
+            chunks_total, n_ranks);
         probe_rows_gather_kernel<<<rows, 128, 0, st>>>(static_cast<const uint8_t*>(v_first_8), sc.pidx,
             static_cast<uint8_t*>(exch_out), G, D, max_seq_len, qn, token_base);
         return cuda_status(cudaGetLastError(), "shard_step winners launch");

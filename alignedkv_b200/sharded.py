@@ -174,6 +174,15 @@ class TorchComm:
         self.dist.all_gather_into_tensor(flat, x.contiguous(), group=self.group)
         return flat.view((self.world,) + tuple(x.shape))
 
+    def all_gather_into(self, out: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """out [world, *x.shape] <- every rank's x, rank-major."""
+        if self.world == 1:
+            out[0].copy_(x)
+        else:
+            self.dist.all_gather_into_tensor(out.view((self.world * x.shape[0],) + tuple(x.shape[1:])), x,
+                                             group=self.group)
+        return out
+
     def all_reduce(self, x: torch.Tensor, op: str) -> torch.Tensor:
         if self.world > 1:
             self.dist.all_reduce(x, op=self.dist.ReduceOp.SUM if op == "sum" else self.dist.ReduceOp.MAX,
@@ -198,12 +207,16 @@ class _CudaShardEngine:
         self.layer.k_exp_max.copy_(k_exp)
         self.layer.v_exp_max.copy_(v_exp)
 
-    def phase(self, i, exch_in, q, k_new, v_new, chunks, chunks_total, token_base):
+    def phase(self, i, exch_in, q, k_new, v_new, chunks, chunks_total, token_base, n_ranks=1, out=None, out_chunks=0):
+        """out: buffer to write (phase 1 / 2: rows of out_chunks chunks, padding left untouched); default: a new tensor
+        over the local chunks.  n_ranks: rank blocks in exch_in (see akv_shard_step)."""
         lay = self.layer
         rows, D = lay.B * lay.Hq, lay.D
-        shape, dtype = {1: ((rows, chunks, 2), torch.float32), 2: ((2, rows, chunks, 32), torch.int32),
-                        3: ((rows, 32, D), torch.uint8), 4: ((rows, D + 2), torch.float32)}[i]
-        out = torch.empty(shape, dtype=dtype, device=self.device)
+        if out is None:
+            shape, dtype = {1: ((rows, chunks, 2), torch.float32), 2: ((2, rows, chunks, 32), torch.int32),
+                            3: ((rows, 32, D), torch.uint8), 4: ((rows, D + 2), torch.float32)}[i]
+            out = torch.empty(shape, dtype=dtype, device=self.device)
+            out_chunks = 0
         with torch.cuda.device(self.device):
             rc = self.lib.akv_shard_step(
                 lay.k_first_8.data_ptr(), lay.k_mid_4.data_ptr(), lay.k_last_4.data_ptr(),
@@ -211,7 +224,7 @@ class _CudaShardEngine:
                 lay.k_exp_max.data_ptr(), lay.v_exp_max.data_ptr(), lay.restk.data_ptr(), lay.restv.data_ptr(),
                 q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), exch_in.data_ptr() if exch_in is not None else None,
                 out.data_ptr(), lay.scratch.data_ptr(), lay.scratch.numel(), lay.B, lay.H, lay.G, D,
-                lay.L, lay.rest_len, lay.rest_start, token_base, chunks_total, self.flags, i,
+                lay.L, lay.rest_len, lay.rest_start, token_base, chunks_total, n_ranks, out_chunks, self.flags, i,
                 torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check("shard_step", rc)
         return out
@@ -294,10 +307,29 @@ class DecisionExactShardedDecoder:
             exps.append(exponent_field(self.comm.all_reduce(mx.contiguous(), "max").half()))
         self.engine.set_maxima(*exps)
 
-    def phase(self, i: int, exch_in, q, k_new, v_new, chunks_total: int = 0):
+    def phase(self, i: int, exch_in, q, k_new, v_new, chunks_total: int = 0, n_ranks: int = 1, out=None,
+              out_chunks: int = 0):
         """Run phase i (1..4) of the step in progress and return its exchange buffer (see akv_shard_step)."""
         return self.engine.phase(i, exch_in, q, k_new, v_new, self._chunks_of(self.rank, self.appended + 1),
-                                 chunks_total, self.token_base)
+                                 chunks_total, self.token_base, n_ranks=n_ranks, out=out, out_chunks=out_chunks)
+
+    def _buffers(self, cmax: int, like):
+        """Exchange buffers for a common chunk count of cmax (kept between steps; the padding chunks of the phase 1 / 2
+        outputs are filled once: the kernels only write the local chunks)."""
+        if getattr(self, "_buf_cmax", None) != cmax or self._buf["st"].device != like.device:
+            dev, W, rows, D = like.device, self.world, self.rows, self.D
+            st = torch.empty((rows, cmax, 2), dtype=torch.float32, device=dev)
+            st[:, :, 0] = float("-inf")
+            st[:, :, 1] = 0.0
+            self._buf = dict(
+                st=st, st_all=torch.empty((W, rows, cmax, 2), dtype=torch.float32, device=dev),
+                cand=torch.zeros((2, rows, cmax, 32), dtype=torch.int32, device=dev),
+                cand_all=torch.empty((W, 2, rows, cmax, 32), dtype=torch.int32, device=dev),
+                win=torch.empty((rows, 32, D), dtype=torch.uint8, device=dev),
+                part=torch.empty((rows, D + 2), dtype=torch.float32, device=dev),
+                parts=torch.empty((W, rows, D + 2), dtype=torch.float32, device=dev))
+            self._buf_cmax = cmax
+        return self._buf
 
     def finish_step(self) -> None:
         self.engine.finish_step()
@@ -308,26 +340,28 @@ class DecisionExactShardedDecoder:
         return dict(engine=self.engine.snapshot(), appended=self.appended)
 
     def restore(self, snap) -> None:
+        before = self._chunks_of(self.rank, self.appended + 1)
         self.engine.restore(snap["engine"])
         self.appended = snap["appended"]
+        if self._chunks_of(self.rank, self.appended + 1) < before:
+            self._buf_cmax = None       # a chunk written earlier is padding again: rebuild the exchange buffers
 
     def decode(self, q, k_new, v_new):
         """q [B,1,Hq,D], k_new / v_new [B,1,H,D] (needed on every rank: they feed the exponent maxima) -> output
         [B,1,Hq,D], the same on every rank."""
-        cmax = max(self._chunks_of(r, self.appended + 1) for r in range(self.world))
-        total = self.world * cmax
-        st = pad_stats(self.phase(1, None, q, k_new, v_new), cmax)
-        st_all = sequence_order(self.comm.all_gather(st))                               # [rows, total, 2]
-        cand = self.phase(2, st_all, q, k_new, v_new, total)                            # [2, rows, chunks, 32]
-        cand = torch.stack([pad_chunks(cand[0], cmax, 0), pad_chunks(cand[1], cmax, 0)])
-        g = self.comm.all_gather(cand)                                                  # [world, 2, rows, cmax, 32]
-        cand_all = torch.stack([sequence_order(g[:, 0]), sequence_order(g[:, 1])]).contiguous()
-        win_rows = self.phase(3, cand_all, q, k_new, v_new, total)                      # [rows, 32, D] bytes
-        win_rows = self.comm.all_reduce(win_rows, "sum")       # every byte is non-zero on at most one rank
-        part = self.phase(4, win_rows, q, k_new, v_new, total)                          # [rows, D + 2]
-        parts = self.comm.all_gather(part)[:, :, 2:]                                    # [world, rows, D]
-        out = parts[0].clone()
-        for r in range(1, self.world):                                                  # rank order, fp32
-            out += parts[r]
+        W = self.world
+        cmax = max(self._chunks_of(r, self.appended + 1) for r in range(W))
+        total = W * cmax
+        buf = self._buffers(cmax, q)
+        # every phase writes straight into the buffer that is exchanged, and reads the gathered buffer as it arrives
+        self.phase(1, None, q, k_new, v_new, out=buf["st"], out_chunks=cmax)
+        self.comm.all_gather_into(buf["st_all"], buf["st"])
+        self.phase(2, buf["st_all"], q, k_new, v_new, total, n_ranks=W, out=buf["cand"], out_chunks=cmax)
+        self.comm.all_gather_into(buf["cand_all"], buf["cand"])
+        self.phase(3, buf["cand_all"], q, k_new, v_new, total, n_ranks=W, out=buf["win"])
+        self.comm.all_reduce(buf["win"], "sum")                # every byte is non-zero on at most one rank
+        self.phase(4, buf["win"], q, k_new, v_new, total, n_ranks=W, out=buf["part"])
+        self.comm.all_gather_into(buf["parts"], buf["part"])
+        out = buf["parts"][:, :, 2:].sum(dim=0)                # the ranks' parts add up (fp32)
         self.finish_step()
         return out.half().reshape(self.B, 1, self.Hq, self.D)

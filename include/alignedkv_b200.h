@@ -249,6 +249,10 @@ int akv_decode_step_noalloc(void* k_first_8, void* k_mid_4, void* k_last_4, void
  *   phase 4: exch_in the shards' row buffers added up; probe, threshold bytes, order-free P.V, residual tokens
  *                                                                -> exch_out float [rows][head_dim + 2]; words 2.. are
  *                                                                   this shard's part of the output (parts add up)
+ * Layout: a phase 1 / 2 output has a row stride of out_chunks chunks (0 = the local count; a caller that pads every
+ * rank to a common count pre-fills the padding with empty chunks: statistics (-inf, 0), candidates 0).  A phase 2 / 3
+ * input is n_ranks such buffers one after the other, as an all-gather leaves them (chunks_total = n_ranks x the common
+ * count), or with n_ranks == 1 one buffer over all chunks in sequence order.
  * token_base: position of local token 0 in the whole sequence (a multiple of 4096).  All phases take the state before
  * the step; the caller advances rest_len / rest_start after phase 4 as for akv_decode_step_ex.  scratch: at least
  * akv_decode_scratch_bytes_ex(..., AKV_STEP_ORDER_FREE) bytes, untouched between the phases.  head_dim 128.
@@ -257,7 +261,7 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
                    void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
                    const void* v_new, const void* exch_in, void* exch_out, void* scratch, long long scratch_bytes,
                    int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
-                   int token_base, int chunks_total, int flags, int phase, void* stream);
+                   int token_base, int chunks_total, int n_ranks, int out_chunks, int flags, int phase, void* stream);
 
 /*
  * Benchmark instrumentation (no counterpart in the reference): with akv_set_tuning("timing", 1), akv_decode_step

@@ -126,45 +126,44 @@ class CheckingEngine:
     def set_maxima(self, k_exp, v_exp):
         self.maxima = (k_exp.clone(), v_exp.clone())
 
-    def phase(self, i, exch_in, q, k_new, v_new, chunks, chunks_total, token_base):
+    def phase(self, i, exch_in, q, k_new, v_new, chunks, chunks_total, token_base, n_ranks=1, out=None, out_chunks=0):
         cmax = max(self.chunks_of)
-        assert chunks == self.chunks_of[self.rank]
+        assert chunks == self.chunks_of[self.rank] and out is not None
         if i == 1:
-            st = torch.empty(self.rows, chunks, 2)
+            assert out.shape == (self.rows, cmax, 2) and out_chunks == cmax
             for c in range(chunks):
-                st[:, c, 0] = 100.0 * self.rank + c
-                st[:, c, 1] = self.rank + 1.0
-            return st
-        assert chunks_total == self.world * cmax
+                out[:, c, 0] = 100.0 * self.rank + c
+                out[:, c, 1] = self.rank + 1.0
+            return out
+        assert chunks_total == self.world * cmax and n_ranks == self.world
         if i == 2:
-            assert exch_in.shape == (self.rows, chunks_total, 2)
+            assert exch_in.shape == (self.world, self.rows, cmax, 2)
             for r in range(self.world):
                 for c in range(cmax):
-                    m, l = exch_in[0, r * cmax + c].tolist()
+                    m, l = exch_in[r, 0, c].tolist()
                     if c < self.chunks_of[r]:
                         assert (m, l) == (100.0 * r + c, r + 1.0)
                     else:
-                        assert m == float("-inf") and l == 0.0
-            cand = torch.zeros(2, self.rows, chunks, 32, dtype=torch.int32)
-            cand[0] += 1000 * (self.rank + 1)
-            cand[1] += token_base // 32
-            return cand
+                        assert m == float("-inf") and l == 0.0          # padding chunk of a shorter shard
+            assert out.shape == (2, self.rows, cmax, 32) and out_chunks == cmax
+            out[0, :, :chunks] = 1000 * (self.rank + 1)
+            out[1, :, :chunks] = token_base // 32
+            return out
         if i == 3:
-            assert exch_in.shape == (2, self.rows, chunks_total, 32) and exch_in.dtype == torch.int32
+            assert exch_in.shape == (self.world, 2, self.rows, cmax, 32) and exch_in.dtype == torch.int32
             for r in range(self.world):
-                want = 1000 * (r + 1)
-                assert int(exch_in[0, 0, r * cmax, 0]) == want
+                assert int(exch_in[r, 0, 0, 0, 0]) == 1000 * (r + 1)
                 if self.chunks_of[r] < cmax:
-                    assert int(exch_in[0, 0, r * cmax + cmax - 1, 0]) == 0
-            rows = torch.zeros(self.rows, 32, self.D, dtype=torch.uint8)
-            rows[:, self.rank::self.world] = self.rank + 1          # "the winners this rank holds"
-            return rows
+                    assert int(exch_in[r, 0, 0, cmax - 1, 0]) == 0      # padding candidates
+            out.zero_()
+            out[:, self.rank::self.world] = self.rank + 1           # "the winners this rank holds"
+            return out
         assert exch_in.dtype == torch.uint8
         for j in range(32):
             assert int(exch_in[0, j, 0]) == j % self.world + 1
-        part = torch.zeros(self.rows, self.D + 2)
-        part[:, 2:] = self.rank + 1.0
-        return part
+        out.zero_()
+        out[:, 2:] = self.rank + 1.0
+        return out
 
     def finish_step(self):
         self.steps += 1
