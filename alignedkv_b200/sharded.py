@@ -159,20 +159,12 @@ def sequence_order(gathered: torch.Tensor) -> torch.Tensor:
 
 
 class TorchComm:
-    """The three collectives the protocol needs, over torch.distributed (NCCL on GPUs, gloo on CPU tensors)."""
+    """The collectives the protocol needs, over torch.distributed (NCCL on GPUs, gloo on CPU tensors)."""
 
     def __init__(self, group=None):
         import torch.distributed as dist
         self.dist, self.group = dist, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-
-    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
-        """-> [world, *x.shape], rank-major."""
-        if self.world == 1:
-            return x.unsqueeze(0)
-        flat = torch.empty((self.world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-        self.dist.all_gather_into_tensor(flat, x.contiguous(), group=self.group)
-        return flat.view((self.world,) + tuple(x.shape))
 
     def all_gather_into(self, out: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """out [world, *x.shape] <- every rank's x, rank-major."""
