@@ -172,6 +172,18 @@ def test_argument_validation_happens_before_any_launch(akv_lib):
     assert b"residual state" in L.akv_last_error()
     assert L.akv_decode_step(*([one] * 15), 16, 1, 4, 128, 64, 0, 0, 0, None) == -2
     assert b"scratch" in L.akv_last_error()
+    # the sharded step: 16 pointers, scratch bytes, bsz, kv heads, group, head_dim, max_seq_len, rest_len, rest_start,
+    # token_base, chunks_total, n_ranks, out_chunks, flags, phase, stream
+    big = 1 << 40
+    assert L.akv_shard_step(*([None] * 16), big, 1, 4, 1, 128, 64, 0, 0, 0, 1, 1, 0, 2, 1, None) == -1
+    assert L.akv_shard_step(*([one] * 16), big, 1, 4, 1, 128, 64, 0, 0, 0, 1, 1, 0, 2, 5, None) == -2       # phase 5
+    assert L.akv_shard_step(*([one] * 16), big, 1, 4, 1, 128, 64, 0, 0, 100, 1, 1, 0, 2, 1, None) == -2     # token_base
+    assert b"token_base" in L.akv_last_error()
+    assert L.akv_shard_step(*([one] * 16), big, 1, 4, 1, 64, 64, 0, 0, 0, 1, 1, 0, 2, 1, None) == -2        # head_dim
+    assert L.akv_shard_step(*([one] * 16), big, 1, 4, 1, 128, 64, 0, 0, 0, 3, 2, 0, 2, 2, None) == -2       # 3 chunks, 2 ranks
+    assert b"rank blocks" in L.akv_last_error()
+    assert L.akv_shard_step(*([one] * 16), 16, 1, 4, 1, 128, 64, 0, 0, 0, 1, 1, 0, 2, 1, None) == -2
+    assert b"scratch" in L.akv_last_error()
     with pytest.raises(_lib.AlignedKVError):
         _lib.check("x", -2)
 
