@@ -132,8 +132,9 @@ class DecodeLayer:
 
     # ------------------------------------------------------------------ one decode token
     def decode(self, q: torch.Tensor, k: torch.Tensor | None = None, v: torch.Tensor | None = None, *,
-               append: bool = True, packed: bool = False):
-        """Append (k, v) of one token per sequence and return the attention output [B,1,Hq,D] (fp16).
+               append: bool = True, packed: bool = False, out: torch.Tensor | None = None):
+        """Append (k, v) of one token per sequence and return the attention output [B,1,Hq,D] (fp16; written into
+        `out` when given).
 
         append=False leaves the cache as it is (the token belongs to another shard of the sequence).  packed=True
         returns instead the fp32 record [B*Hq, D+2] = (max score, sum of exponentials, output) over this cache's
@@ -146,7 +147,11 @@ class DecodeLayer:
                 raise RuntimeError(f"{name}: expected a contiguous CUDA fp16 tensor of shape {(B, 1, heads, D)}")
         if append and self.cache_len + 1 > self.L:
             raise RuntimeError(f"cache is full ({self.L} tokens)")
-        out = None if packed else torch.empty((B, 1, Hq, D), dtype=torch.half, device=self.device)
+        if out is not None and (packed or out.shape != (B, 1, Hq, D) or out.dtype != torch.half or not out.is_cuda or
+                                not out.is_contiguous()):
+            raise RuntimeError(f"out: expected a contiguous CUDA fp16 tensor of shape {(B, 1, Hq, D)}")
+        if out is None and not packed:
+            out = torch.empty((B, 1, Hq, D), dtype=torch.half, device=self.device)
         rec = torch.empty((B * Hq, D + 2), dtype=torch.float32, device=self.device) if packed else None
         with torch.cuda.device(self.device):
             rc = self.lib.akv_decode_step_ex(

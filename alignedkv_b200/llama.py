@@ -127,6 +127,81 @@ class LlamaDecoder:
         gate, up = F.linear(h, p["w_gate_up"]).chunk(2, dim=-1)
         return torch.addmm(x.view(B * S, -1), F.silu(gate).mul_(up).view(B * S, -1), p["w_down"].t()).view(B, S, -1)
 
+    # ------------------------------------------------------------------ decode step with the dense parts as CUDA graphs
+    def _pre(self, i: int, x: torch.Tensor, tables):
+        """Everything of layer i before its attention: norm, q/k/v projection, rotary embedding."""
+        cfg, p = self.cfg, self.layers[i]
+        H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        B = x.shape[0]
+        qkv = F.linear(_rms_norm(x, p["norm1"], cfg.rms_norm_eps), p["wqkv"]).view(B, 1, H + 2 * Hkv, D)
+        qk = _rope(qkv[:, :, :H + Hkv], tables)
+        return qk[:, :, :H].contiguous(), qk[:, :, H:].contiguous(), qkv[:, :, H + Hkv:].contiguous()
+
+    def _post(self, i: int, x: torch.Tensor, o: torch.Tensor) -> torch.Tensor:
+        """Everything of layer i after its attention: output projection, residual, SwiGLU MLP, residual."""
+        cfg, p = self.cfg, self.layers[i]
+        B = x.shape[0]
+        x = torch.addmm(x.view(B, -1), o.reshape(B, -1), p["wo"].t()).view(B, 1, -1)
+        gate, up = F.linear(_rms_norm(x, p["norm2"], cfg.rms_norm_eps), p["w_gate_up"]).chunk(2, dim=-1)
+        return torch.addmm(x.view(B, -1), F.silu(gate).mul_(up).view(B, -1), p["w_down"].t()).view(B, 1, -1)
+
+    @torch.no_grad()
+    def capture_graphs(self) -> None:
+        """Capture the dense parts of a decode step as CUDA graphs: one graph per stretch between two attention calls
+        (embedding + layer 0 up to its attention; the rest of layer i + layer i+1 up to its attention; the rest of the
+        last layer + final norm + logits).  The attention calls stay ordinary launches between the replays - the
+        cache's state (residual length, block count) changes from token to token and is passed by value.  After this,
+        `step` replays: ~35 torch launches per layer become one graph launch, which is what the step was bound by."""
+        assert self.attention == "alignedkv", "only the AlignedKV path is split into graphs"
+        cfg, B, dev = self.cfg, self.B, self.device
+        H, D, n = cfg.num_attention_heads, cfg.head_dim, cfg.num_hidden_layers
+        self._g_ids = torch.zeros(B, dtype=torch.long, device=dev)
+        self._g_pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self._g_o = torch.zeros(B, 1, H, D, dtype=torch.half, device=dev)
+        segs = []          # (graph, outputs) per stretch
+
+        def run(j, x_prev):
+            tables = _rope_tables(self._g_pos, D, cfg.rope_theta)
+            if j == 0:
+                x = self.embed[self._g_ids].view(B, 1, -1)
+            else:
+                x = self._post(j - 1, x_prev, self._g_o)
+            if j == n:
+                x = _rms_norm(x, self.final_norm, cfg.rms_norm_eps)
+                return (F.linear(x, self.lm_head)[:, 0],)
+            return (x,) + self._pre(j, x, tables)
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        x_prev = None
+        with torch.cuda.stream(side):
+            for j in range(n + 1):              # warm-up outside capture (library workspaces, lazy initialisation)
+                outs = run(j, x_prev)
+                x_prev = outs[0]
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        x_prev = None
+        for j in range(n + 1):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                outs = run(j, x_prev)
+            segs.append((g, outs))
+            x_prev = outs[0]
+        self._segs = segs
+
+    def _step_graphs(self, ids: torch.Tensor) -> torch.Tensor:
+        n = self.cfg.num_hidden_layers
+        self._g_ids.copy_(ids.view(-1))
+        self._g_pos.fill_(self.pos)
+        for j in range(n):
+            g, (x, q, k, v) = self._segs[j]
+            g.replay()
+            self.caches[j].decode(q, k, v, out=self._g_o)
+        g, (logits,) = self._segs[n]
+        g.replay()
+        self.pos += 1
+        return logits
+
     def _forward(self, ids: torch.Tensor, prompt: bool) -> torch.Tensor:
         B, S = ids.shape
         pos = _rope_tables(torch.arange(self.pos, self.pos + S, device=self.device), self.cfg.head_dim,
@@ -149,6 +224,8 @@ class LlamaDecoder:
     def step(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [B] (one token per sequence) -> logits [B,V]; appends to every layer's cache."""
         assert self.pos + 1 <= self.L
+        if getattr(self, "_segs", None) is not None:
+            return self._step_graphs(ids)       # (the returned logits are overwritten by the next step)
         return self._forward(ids.view(self.B, 1), False)
 
     @torch.no_grad()

@@ -70,6 +70,8 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--workload", default="llama2-7b-layer-decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="decoder workload: launch the dense parts op by op instead of replaying CUDA graphs")
     ap.add_argument("--v-mode", default=None, choices=["exact", "order_free"],
                     help="P.V kernel: exact = the reference's token order (bit-identical), order_free = split sequence, "
                          "fp32 accumulation (default: per workload)")
@@ -421,6 +423,8 @@ def run_decoder(args):
     ids = torch.randint(0, cfg.vocab_size, (B, S), device=dev,
                         generator=torch.Generator(device=dev).manual_seed(args.seed + 100 + rank))
     tok = model.prefill(ids).argmax(-1)
+    if not args.no_graphs:
+        model.capture_graphs()                           # the dense parts between two attention calls: one graph each
     lib = model.caches[0].lib
 
     def barrier():
@@ -508,6 +512,8 @@ def run_decoder(args):
                        "prompt_len": S, "cache_len_at_end": L_now, "global_batch": tokens, "pv_kernel": v_mode,
                        "step": "one greedy token per sequence through all layers (projections and MLP: fp16 cuBLAS "
                                "through torch; attention: the AlignedKV decode step of every layer)",
+                       "dense_parts": "launched op by op" if args.no_graphs else
+                                      "replayed from CUDA graphs, one per stretch between two attention calls",
                        "l2": "weights 13.5 GB + planes, far larger than L2"},
             "attention_kernels_us_per_layer": {n: round(kv_["us"], 2) for n, kv_ in kern.items()},
             "attention_bytes_read_over_dense": acct["read"] / acct["dense"],

@@ -32,3 +32,23 @@ def test_decoder_matches_dense_attention(akv_lib, kv_heads, v_mode):
     assert worst <= 5e-2
     assert agree >= new - 2
     assert akv_lib.akv_device_error_flag() == 0
+
+
+def test_decoder_graph_replay_matches_eager(akv_lib):
+    """The decode step with its dense parts replayed from CUDA graphs gives the logits of the eager step."""
+    from alignedkv_b200.llama import LlamaConfig, LlamaDecoder
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=4, vocab_size=1000)
+    B, S, new = 2, 100, 5
+    ids = torch.randint(0, cfg.vocab_size, (B, S), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    a = LlamaDecoder(cfg, B, S + new + 1, "cuda:0", seed=2)
+    b = LlamaDecoder(cfg, B, S + new + 1, "cuda:0", seed=2)
+    tok = a.prefill(ids).argmax(-1)
+    assert torch.equal(tok, b.prefill(ids).argmax(-1))
+    b.capture_graphs()
+    for _ in range(new):
+        la, lb = a.step(tok), b.step(tok).clone()
+        err = float((la.float() - lb.float()).abs().max() / la.float().abs().max())
+        assert err <= 1e-3, err
+        tok = la.argmax(-1)
+    assert a.pos == b.pos and akv_lib.akv_device_error_flag() == 0
