@@ -1,7 +1,7 @@
 """Generate tests/golden/wrappers.npz by running the REFERENCE's own Python wrappers on CPU.
 
 The reference's extension/k_cache_file.py, extension/v_cache_file.py and model/KVCache_AlignedKV.py are imported
-unchanged from a reference checkout (default /root/reference); only two things around them are substituted:
+unchanged from a reference checkout (argument, else $AKV_REFERENCE_ROOT); only two things around them are substituted:
   * `extension.KV_cache_cpp_extention.cuda_module` (the reference builds CUDA at import time) becomes the
     oracle-backed stand-in of tests/fake_cuda_module.py, so the kernels' arithmetic comes from oracle/akv_oracle.c;
   * `transformers.cache_utils.Cache` becomes a plain base class (the installed transformers release changed it).
@@ -81,7 +81,7 @@ def run_reference(ref_root: str):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AKV_REFERENCE_ROOT", "/root/reference")
     data = run_reference(ref)
     path = os.path.join(HERE, "wrappers.npz")
     np.savez_compressed(path, **data)
