@@ -41,11 +41,6 @@ __device__ __forceinline__ void v_write32_global(const uint4* __restrict__ src, 
     v_write32(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3), f_dst, m_dst, l_dst);
 }
 
-// One 64-token K block of one (batch, head): the 64 x D fp16 tile is staged in shared memory token-major (as it
-// arrives; row(t) gives the global address of token t's D halves), then thread d gathers channel d of all 64
-// tokens and emits one 64-byte first_8 row and one 32-byte row of each nibble plane with 16-byte accesses.  Nibble
-// rows are read-add-written (bytewise, mod 256) so that the result equals the reference's `+=`
-// (extension/csrc/K_cache.cu:49-56) on any prior plane contents.  `tile` = plane tile index (b*H + h)*nmb + block.
 // Stage a [64 tokens][D] fp16 tile in shared memory, token-major; row(t) = global address of token t's D halves.
 template <class RowPtr>
 __device__ __forceinline__ void stage_tile64(uint8_t* smem, RowPtr row, int D, int tokens = 64) {

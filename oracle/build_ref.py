@@ -8,19 +8,43 @@ lie in the reference checkout; nothing is copied into this repository and the on
 The resulting module is the bit-exact checker that the ``-m gpu`` parity tests and the golden-vector generator
 (tests/golden/make_golden_gpu.py) load when it is present.  It is never imported by the product package.
 
-Usage:  python oracle/build_ref.py [/path/to/reference]
+`vendor()` additionally copies the reference checkout (a dozen small files) to ``baseline/_ref/`` (git-ignored), so that
+the GPU tests can import the reference's own model/KVCache_AlignedKV.py unchanged on a machine that has no checkout.
+
+Usage:  python oracle/build_ref.py [/path/to/reference]      (default: $AKV_REFERENCE_ROOT, else ../reference)
 """
 import os
+import shutil
 import subprocess
 import sys
 import sysconfig
 from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
 OUT = os.path.join(HERE, "_ref")
+VENDOR = os.path.join(ROOT, "baseline", "_ref")
 
 
-def build(ref_root: str = "/root/reference", verbose: bool = True) -> str | None:
+def default_reference_root() -> str | None:
+    """$AKV_REFERENCE_ROOT, else a directory `reference` next to this repository; None when neither exists."""
+    for cand in (os.environ.get("AKV_REFERENCE_ROOT"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "extension", "csrc")):
+            return cand
+    return None
+
+
+def vendor(ref_root: str) -> str:
+    """Copy the reference checkout to baseline/_ref (git-ignored; it travels to the GPU box with the working tree)."""
+    def ignore(_dir, names):
+        return [n for n in names if n in (".git", "__pycache__")]
+    if os.path.isdir(VENDOR):
+        shutil.rmtree(VENDOR)
+    shutil.copytree(ref_root, VENDOR, ignore=ignore)
+    return VENDOR
+
+
+def build(ref_root: str, verbose: bool = True) -> str | None:
     src_dir = os.path.join(ref_root, "extension", "csrc")
     srcs = [os.path.join(src_dir, f) for f in ("K_cache.cu", "V_cache.cu", "KV_cache_ops.cpp")]
     if not all(os.path.exists(s) for s in srcs):
@@ -62,5 +86,8 @@ def build(ref_root: str = "/root/reference", verbose: bool = True) -> str | None
 
 
 if __name__ == "__main__":
-    r = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
-    print("built:", r)
+    root = sys.argv[1] if len(sys.argv) > 1 else default_reference_root()
+    if root is None:
+        raise SystemExit("no reference checkout: pass its path or set AKV_REFERENCE_ROOT")
+    print("built:", build(root))
+    print("vendored:", vendor(root))

@@ -79,4 +79,5 @@ def main(out_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AKV_GOLDEN_OUT", os.path.join(ROOT, "gpurun_out", "golden")))
+    # output directory: argument, else $AKV_GOLDEN_OUT, else beside this script (where the committed fixture lives)
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AKV_GOLDEN_OUT", HERE))

@@ -81,7 +81,10 @@ def run_reference(ref_root: str):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AKV_REFERENCE_ROOT", "/root/reference")
+    from helpers import reference_root
+    ref = sys.argv[1] if len(sys.argv) > 1 else reference_root()
+    if ref is None:
+        raise SystemExit("no reference checkout: pass its path or set AKV_REFERENCE_ROOT")
     data = run_reference(ref)
     path = os.path.join(HERE, "wrappers.npz")
     np.savez_compressed(path, **data)

@@ -58,3 +58,23 @@ def load_reference_extension():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
+
+
+def reference_root():
+    """A checkout of the reference: $AKV_REFERENCE_ROOT, else the vendored copy under baseline/_ref (git-ignored; made
+    by oracle/build_ref.py), else a sibling directory `reference` next to this repository.  None when there is none."""
+    for cand in (os.environ.get("AKV_REFERENCE_ROOT"), os.path.join(ROOT, "baseline", "_ref"),
+                 os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "model", "KVCache_AlignedKV.py")):
+            return cand
+    return None
+
+
+def load_reference_caller():
+    """The reference's own QuantizedCache_AlignedKV (model/KVCache_AlignedKV.py, unchanged) running on this package's
+    operators, or None when no reference checkout is at hand."""
+    root = reference_root()
+    if root is None:
+        return None
+    import alignedkv_b200
+    return alignedkv_b200.load_reference_cache(root)

@@ -1,5 +1,6 @@
-"""Pipeline-level parity on the GPU: the host-side mirror of the reference's cache classes and the one-call decode
-step, against the numpy restatement of the reference pipeline (oracle/pipeline.py) and against each other.
+"""Pipeline-level parity on the GPU: the reference's own caller (model/KVCache_AlignedKV.py, imported unchanged) over
+the host-side mirror of the reference's cache classes, and the one-call decode step, against the numpy restatement
+of the reference pipeline (oracle/pipeline.py) and against each other.
 
 Planes, exponent maxima and residual buffers must be bit-exact.  Attention outputs are compared with the
 max-norm relative error max|a-b| / max|b| <= 1e-3 (the tolerance the parity target states); the softmax and the
@@ -9,7 +10,7 @@ from types import SimpleNamespace
 import numpy as np
 import pytest
 
-from helpers import make_kvq
+from helpers import load_reference_caller, make_kvq
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -39,7 +40,9 @@ def built(akv_lib):
 ])
 @pytest.mark.parametrize("reference", [False, True])
 def test_decode_paths_agree(built, B, H, D, prompt, steps, max_len, reference):
-    from alignedkv_b200.cache import QuantizedCache_AlignedKV
+    QuantizedCache_AlignedKV = load_reference_caller()     # the reference's own caller, imported unchanged
+    if QuantizedCache_AlignedKV is None:
+        pytest.skip("no reference checkout (baseline/_ref, $AKV_REFERENCE_ROOT or ../reference)")
     from alignedkv_b200.decode import DecodeLayer
     from oracle.pipeline import OracleLayerCache, dense_attention_fp32
     L = prompt + steps

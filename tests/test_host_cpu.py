@@ -9,7 +9,7 @@ import types
 import numpy as np
 import pytest
 
-from helpers import ROOT, make_kvq
+from helpers import ROOT, load_reference_caller, make_kvq
 
 torch = pytest.importorskip("torch")
 GOLD = os.path.join(ROOT, "tests", "golden", "wrappers.npz")
@@ -30,7 +30,11 @@ def cpu_mirror(akv_lib, monkeypatch):
 
 @pytest.mark.parametrize("name,B,H,D,prompt,steps,max_len,reference", CASES)
 def test_mirror_matches_reference_wrappers(cpu_mirror, name, B, H, D, prompt, steps, max_len, reference):
-    from alignedkv_b200.cache import QuantizedCache_AlignedKV
+    """The reference's own caller (model/KVCache_AlignedKV.py, imported unchanged) over the mirror classes reproduces
+    what it produced over the reference's own wrapper classes when the fixture was made."""
+    QuantizedCache_AlignedKV = load_reference_caller()
+    if QuantizedCache_AlignedKV is None:
+        pytest.skip("no reference checkout (baseline/_ref, $AKV_REFERENCE_ROOT or ../reference)")
     from oracle.pipeline import OracleLayerCache
     gold = np.load(GOLD)
     cfg = types.SimpleNamespace(num_hidden_layers=1, num_attention_heads=H, num_key_value_heads=H,
