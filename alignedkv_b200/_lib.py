@@ -31,6 +31,7 @@ SIGNATURES = {
     "akv_v_cache_compute_scratch_bytes": (ctypes.c_longlong, [_I] * 4),
     "akv_decode_step_ex": (_I, [_P] * 16 + [ctypes.c_longlong] + [_I] * 8 + [_P]),
     "akv_decode_scratch_bytes_ex": (ctypes.c_longlong, [_I] * 6),
+    "akv_decode_step_masked": (_I, [_P] * 16 + [ctypes.c_longlong, _P, ctypes.c_longlong] + [_I] * 8 + [_P]),
     "akv_shard_step": (_I, [_P] * 16 + [ctypes.c_longlong] + [_I] * 13 + [_P]),
     "akv_lse_merge": (_I, [_P] * 2 + [_I] * 3 + [_P]),
     "akv_rollback": (_I, [_P] * 6 + [_I] * 6 + [_P]),

@@ -178,12 +178,19 @@ append_flush_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, 
 // or two and the step is bound by the latency of its kernel chain; with many rows the plain form plus a separate
 // probe launch keeps more CTAs per SM and is faster.
 constexpr int SM_REGS = 32;
+// Score t of a row as the fp32 softmax sees it: the fp16 score, plus (optional) the additive fp16 mask of its batch
+// row, added in fp16 as the reference's in-place `scores += mask` on fp16 tensors does (model/KVCache_AlignedKV.py:119-120).
+__device__ __forceinline__ float masked_score(const uint16_t* __restrict__ row, const __half* __restrict__ mrow, int t) {
+    __half s = __ushort_as_half(row[t]);
+    if (mrow) s = __hadd(s, mrow[t]);
+    return __half2float(s);
+}
 template <bool CACHED, bool PROBE>
 __global__ void __launch_bounds__(256)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
                uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats,
                const uint8_t* __restrict__ first8, uint16_t* __restrict__ test_o, int max_seq_len, int H, int G, int D,
-               int R, int qn, int rest, float sqrt_d) {
+               int R, int qn, int rest, float sqrt_d, const __half* __restrict__ mask, long long mask_stride) {
     __shared__ float redf[8];
     __shared__ uint32_t cand_v[256];
     __shared__ int32_t cand_i[256];
@@ -191,6 +198,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint16_t* row = s + (size_t)bhq * R;
+    const __half* mrow = mask ? mask + (size_t)b * mask_stride : nullptr;
     const int len = qn + rest;
     // residual tokens: fp32 dot product rounded to fp16, then divided by sqrt(D) and rounded again, which is
     // what `matmul(q, restk^T) / sqrt(D)` on fp16 tensors produces (k_cache_file.py:156-157)
@@ -211,11 +219,11 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
 #pragma unroll
         for (int i = 0; i < SM_REGS; ++i) {
             const int t = tid + 256 * i;
-            x[i] = t < len ? __half2float(__ushort_as_half(row[t])) : -INFINITY;
+            x[i] = t < len ? masked_score(row, mrow, t) : -INFINITY;
             m = fmaxf(m, x[i]);
         }
     } else {
-        for (int t = tid; t < len; t += 256) m = fmaxf(m, __half2float(__ushort_as_half(row[t])));
+        for (int t = tid; t < len; t += 256) m = fmaxf(m, masked_score(row, mrow, t));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
@@ -236,7 +244,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
             }
         }
     } else {
-        for (int t = tid; t < len; t += 256) sum += expf(__half2float(__ushort_as_half(row[t])) - m);
+        for (int t = tid; t < len; t += 256) sum += expf(masked_score(row, mrow, t) - m);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
@@ -270,7 +278,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     } else {
         for (int t = tid; t < R; t += 256) {
             uint16_t pb = 0;
-            if (t < len) pb = __half_as_ushort(__float2half_rn(expf(__half2float(__ushort_as_half(row[t])) - m) / sum));
+            if (t < len) pb = __half_as_ushort(__float2half_rn(expf(masked_score(row, mrow, t) - m) / sum));
             row[t] = pb;
             if (t < qn && pb > best) {
                 best = pb;
@@ -328,11 +336,12 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
 __global__ void __launch_bounds__(256)
 softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
                            float* __restrict__ cstat, int H, int G, int D, int R, int qn, int rest, float sqrt_d,
-                           int chunks) {
+                           int chunks, const __half* __restrict__ mask, long long mask_stride) {
     __shared__ float redf[8];
     const int bhq = blockIdx.y, ch = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint16_t* row = s + (size_t)bhq * R;
+    const __half* mrow = mask ? mask + (size_t)b * mask_stride : nullptr;
     const int len = qn + rest;
     const int t0 = ch * SM_CHUNK, t1 = min(len, t0 + SM_CHUNK);
     // residual-token scores (k_cache_file.py:156-157) by the chunk(s) that hold them
@@ -348,7 +357,7 @@ softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ 
     }
     __syncthreads();
     float m = -INFINITY;
-    for (int t = t0 + tid; t < t1; t += 256) m = fmaxf(m, __half2float(__ushort_as_half(row[t])));
+    for (int t = t0 + tid; t < t1; t += 256) m = fmaxf(m, masked_score(row, mrow, t));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
     if (lane == 0) redf[warp] = m;
@@ -358,7 +367,7 @@ softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ 
     for (int w = 1; w < 8; ++w) m = fmaxf(m, redf[w]);
     __syncthreads();
     float sum = 0.f;
-    for (int t = t0 + tid; t < t1; t += 256) sum += expf(__half2float(__ushort_as_half(row[t])) - m);
+    for (int t = t0 + tid; t < t1; t += 256) sum += expf(masked_score(row, mrow, t) - m);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
     if (lane == 0) redf[warp] = sum;
@@ -375,7 +384,7 @@ softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ 
 __global__ void __launch_bounds__(256)
 softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ cstat, uint32_t* __restrict__ cand_val,
                            int32_t* __restrict__ cand_idx, int R, int qn, int len, int chunks, int stat_chunks,
-                           int stat_ranks, int t_base) {
+                           int stat_ranks, int t_base, const __half* __restrict__ mask, long long mask_stride, int Hq) {
     // chunks: row stride (in chunks) of the candidate arrays, at least the chunks of this row held here (the grid);
     // stat_chunks: chunks whose statistics make up the row's (they include the other shards' when the sequence is
     // sharded), laid out as stat_ranks blocks of [rows][stat_chunks / stat_ranks] as an all-gather leaves them;
@@ -390,6 +399,7 @@ softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ c
     __shared__ int32_t cand_i[256];
     const int bhq = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
     uint16_t* row = s + (size_t)bhq * R;
+    const __half* mrow = mask ? mask + (size_t)(bhq / Hq) * mask_stride : nullptr;
     // row statistics from the chunk statistics, in chunk order (every CTA of the row computes the same values)
     float m = -INFINITY;
     for (int c = 0; c < stat_chunks; ++c) m = fmaxf(m, stat(c)[0]);
@@ -403,7 +413,7 @@ softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ c
     int32_t best_g = 0;
     for (int t = t0 + tid; t < t1; t += 256) {     // (t0 and 256 are multiples of 32: a thread keeps its class)
         uint16_t pb = 0;
-        if (t < len) pb = __half_as_ushort(__float2half_rn(expf(__half2float(__ushort_as_half(row[t])) - m) / sum));
+        if (t < len) pb = __half_as_ushort(__float2half_rn(expf(masked_score(row, mrow, t) - m) / sum));
         row[t] = pb;
         if (t < qn && pb > best) {
             best = pb;
@@ -638,7 +648,20 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
                        const void* v_new, void* out, void* packed_out, void* scratch, long long scratch_bytes, int bsz,
                        int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
                        int flags, void* stream) {
+    return akv_decode_step_masked(k_first_8, k_mid_4, k_last_4, v_first_8, v_mid_4, v_last_4, k_exp_max, v_exp_max, restk,
+                                  restv, q, k_new, v_new, out, packed_out, nullptr, 0, scratch, scratch_bytes, bsz,
+                                  n_kv_heads, group, head_dim, max_seq_len, rest_len, rest_start, flags, stream);
+}
+
+int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                           void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                           const void* v_new, void* out, void* packed_out, const void* mask, long long mask_stride,
+                           void* scratch, long long scratch_bytes, int bsz, int n_kv_heads, int group, int head_dim,
+                           int max_seq_len, int rest_len, int rest_start, int flags, void* stream) {
     set_error("");
+    AKV_REQUIRE(!mask || ((reinterpret_cast<uintptr_t>(mask) & 1u) == 0 && mask_stride >= 0), AKV_ERR_ALIGN,
+                "decode_step: the mask must be 2-byte aligned with a non-negative row stride");
+    const __half* mk = static_cast<const __half*>(mask);
     const int B = bsz, H = n_kv_heads, G = group, D = head_dim;
     const bool reference = (flags & AKV_STEP_REFERENCE) != 0, order_free = (flags & AKV_STEP_ORDER_FREE) != 0;
     const bool append = (flags & AKV_STEP_NO_APPEND) == 0;
@@ -717,10 +740,10 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
         count_launch();
         softmax_chunk_stats_kernel<<<grid, 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
                                                         static_cast<const __half*>(restk), sc.cstat, H, G, D, R, qn, rest,
-                                                        sqrtf((float)D), sm_chunks);
+                                                        sqrtf((float)D), sm_chunks, mk, mask_stride);
         count_launch();
         softmax_chunk_write_kernel<<<grid, 256, 0, st>>>(sc.s, sc.cstat, sc.cand_val, sc.cand_idx, R, qn, qn + rest,
-                                                        sm_chunks, sm_chunks, 1, 0);
+                                                        sm_chunks, sm_chunks, 1, 0, mk, mask_stride, H * G);
         count_launch();
         softmax_class_reduce_kernel<<<B * H * G, 32, 0, st>>>(sc.cstat, sc.cand_val, sc.cand_idx, sc.pval, sc.pidx,
                                                              sc.stats, sm_chunks, 1);
@@ -730,13 +753,13 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
             launch_chained(softmax_kernel<true, true>, dim3(B * H * G), dim3(256), 0, st, sc.s,
                            static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
                            static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn, rest,
-                           sqrtf((float)D));
+                           sqrtf((float)D), mk, mask_stride);
             probed = true;
         } else {
             launch_chained(softmax_kernel<false, false>, dim3(B * H * G), dim3(256), 0, st, sc.s,
                            static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
                            (const uint8_t*)nullptr, (uint16_t*)nullptr, max_seq_len, H, G, D, R, qn, rest,
-                           sqrtf((float)D));
+                           sqrtf((float)D), mk, mask_stride);
         }
     }
     if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
@@ -879,7 +902,8 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
         if (slot) cudaEventRecord(slot[1], st);
         count_launch();
         softmax_chunk_stats_kernel<<<dim3(chunks, rows), 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
-            static_cast<const __half*>(restk), static_cast<float*>(exch_out), H, G, D, R, qn, rest, sqrtf((float)D), oc);
+            static_cast<const __half*>(restk), static_cast<float*>(exch_out), H, G, D, R, qn, rest, sqrtf((float)D), oc,
+            (const __half*)nullptr, 0ll);
         return cuda_status(cudaGetLastError(), "shard_step statistics launch");
     }
     if (phase == 2) {
@@ -887,7 +911,7 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
         count_launch();
         softmax_chunk_write_kernel<<<dim3(chunks, rows), 256, 0, st>>>(sc.s, static_cast<const float*>(exch_in), val,
             reinterpret_cast<int32_t*>(val + (size_t)rows * oc * TOPK), R, qn, qn + rest, oc, chunks_total, n_ranks,
-            token_base);
+            token_base, (const __half*)nullptr, 0ll, H * G);
         return cuda_status(cudaGetLastError(), "shard_step probabilities launch");
     }
     if (phase == 3) {

@@ -132,14 +132,27 @@ class DecodeLayer:
 
     # ------------------------------------------------------------------ one decode token
     def decode(self, q: torch.Tensor, k: torch.Tensor | None = None, v: torch.Tensor | None = None, *,
-               append: bool = True, packed: bool = False, out: torch.Tensor | None = None):
+               append: bool = True, packed: bool = False, out: torch.Tensor | None = None,
+               mask: torch.Tensor | None = None):
         """Append (k, v) of one token per sequence and return the attention output [B,1,Hq,D] (fp16; written into
         `out` when given).
 
         append=False leaves the cache as it is (the token belongs to another shard of the sequence).  packed=True
         returns instead the fp32 record [B*Hq, D+2] = (max score, sum of exponentials, output) over this cache's
-        tokens, which `akv_lse_merge` combines across the shards of a sequence."""
+        tokens, which `akv_lse_merge` combines across the shards of a sequence.
+
+        mask: the additive attention mask of the reference's caller (model/KVCache_AlignedKV.py:119-120), an fp16 CUDA
+        tensor of shape [B,1,1,n] or [1,1,1,n] with n >= the cache length after this step (one row per batch row,
+        broadcast over the heads); it is added to the fp16 scores in fp16 before the fp32 softmax."""
         B, H, Hq, D = self.B, self.H, self.Hq, self.D
+        mask_ptr, mask_stride = None, 0
+        if mask is not None:
+            need = self.cache_len + (1 if append else 0)
+            if mask.dtype != torch.half or not mask.is_cuda or mask.dim() != 4 or mask.shape[1] != 1 or \
+                    mask.shape[2] != 1 or mask.shape[0] not in (1, B) or mask.shape[3] < need or mask.stride(3) != 1:
+                raise RuntimeError(f"mask: expected a CUDA fp16 tensor of shape [{B} or 1, 1, 1, >= {need}] with a "
+                                   "unit stride along the positions")
+            mask_ptr, mask_stride = mask.data_ptr(), (mask.stride(0) if mask.shape[0] == B else 0)
         checks = [("q", q, Hq)] + ([("k", k, H), ("v", v, H)] if append else [])
         for name, t, heads in checks:
             if t is None or t.shape != (B, 1, heads, D) or t.dtype != torch.half or not t.is_cuda or \
@@ -154,12 +167,13 @@ class DecodeLayer:
             out = torch.empty((B, 1, Hq, D), dtype=torch.half, device=self.device)
         rec = torch.empty((B * Hq, D + 2), dtype=torch.float32, device=self.device) if packed else None
         with torch.cuda.device(self.device):
-            rc = self.lib.akv_decode_step_ex(
+            rc = self.lib.akv_decode_step_masked(
                 self.k_first_8.data_ptr(), self.k_mid_4.data_ptr(), self.k_last_4.data_ptr(),
                 self.v_first_8.data_ptr(), self.v_mid_4.data_ptr(), self.v_last_4.data_ptr(),
                 self.k_exp_max.data_ptr(), self.v_exp_max.data_ptr(), self.restk.data_ptr(), self.restv.data_ptr(),
                 q.data_ptr(), k.data_ptr() if append else None, v.data_ptr() if append else None,
                 out.data_ptr() if out is not None else None, rec.data_ptr() if rec is not None else None,
+                mask_ptr, mask_stride,
                 self.scratch.data_ptr(), self.scratch.numel(), B, H, self.G, D, self.L, self.rest_len, self.rest_start,
                 self._flags(append), torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check("decode_step", rc)

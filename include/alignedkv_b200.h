@@ -111,7 +111,8 @@ int akv_v_cache_compute(const void* v_first_8, const void* v_mid_4, const void* 
 /*
  * One decode step of one layer in a single call: what the reference does between receiving (q, k_new, v_new) of a
  * decode token and returning the attention output - K_Cache_Class.save + decoding_compute
- * (extension/k_cache_file.py:97-118,132-159), the fp32 softmax (model/KVCache_AlignedKV.py:119-121, no mask) and
+ * (extension/k_cache_file.py:97-118,132-159), the fp32 softmax (model/KVCache_AlignedKV.py:119-121; without a mask -
+ * akv_decode_step_masked takes one) and
  * V_Cache_Class.save + decoding_compute (extension/v_cache_file.py:97-116,119-190) - with the wrapper's small
  * tensor operations folded into kernels.  All pointers are device pointers:
  *   planes as above; k_exp_max / v_exp_max [B,1,H,D] u8 (updated in place); restk / restv [B,64,H,D] fp16 residual
@@ -175,6 +176,22 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
                        int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
                        int flags, void* stream);
 long long akv_decode_scratch_bytes_ex(int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int flags);
+
+/*
+ * akv_decode_step_ex with the attention mask the reference adds to the scores before the softmax
+ * (model/KVCache_AlignedKV.py:119-120: `scores[..., :start_pos+seqlen] += mask`).  mask (NULL = none): additive fp16
+ * values, one row per batch row, row b at mask + b * mask_stride halves (mask_stride 0 = one row for the whole batch),
+ * broadcast over the heads; entry t applies to cached position t, entries [0, cache length after this step) are read.
+ * The addition happens in fp16 (one rounding) like the reference's in-place add on fp16 tensors, and the softmax then runs
+ * in fp32 over the masked scores - a left-padded batch passes its usual mask row with the most negative fp16 value at the
+ * padding positions, whose probabilities then come out as zero.
+ */
+int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                           void* k_exp_max, void* v_exp_max, void* restk, void* restv,
+                           const void* q, const void* k_new, const void* v_new, void* out, void* packed_out,
+                           const void* mask, long long mask_stride, void* scratch, long long scratch_bytes,
+                           int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len, int rest_len, int rest_start,
+                           int flags, void* stream);
 
 /*
  * Prompt ingestion in one pass: K_Cache_Class.save + V_Cache_Class.save for start_pos == 0

@@ -177,11 +177,18 @@ class OracleLayerCache:
         self.last.update(v_codes=codes, amin=amin)
         return o
 
-    def decode(self, q16, k16, v16, reference: bool = False) -> np.ndarray:
-        """One decode step (model/KVCache_AlignedKV.py:116-124, no mask) -> fp16 [B,1,H,D]."""
+    def decode(self, q16, k16, v16, reference: bool = False, mask16=None) -> np.ndarray:
+        """One decode step (model/KVCache_AlignedKV.py:116-124) -> fp16 [B,1,H,D].  mask16 (optional): additive fp16
+        mask broadcastable to [B,H,1,cache length after the step], added to the fp16 scores in fp16 before the
+        softmax (model/KVCache_AlignedKV.py:119-120)."""
         start = self.cache_len
         self.save(k16, v16, start, 1)
         s = self.scores(q16, reference)
+        if mask16 is not None:
+            n = start + 1
+            s = s.copy()
+            s[..., :n] = (s[..., :n] + np.broadcast_to(np.asarray(mask16, np.float16)[..., :n], s[..., :n].shape)
+                          ).astype(np.float16)      # one fp16 addition, as the in-place += on fp16 tensors
         p = softmax_fp32_to_half(s)
         self.last.update(s=s, p=p)
         return self.output(p, reference).reshape(self.B, 1, self.H, self.D)

@@ -78,3 +78,67 @@ def load_reference_caller():
         return None
     import alignedkv_b200
     return alignedkv_b200.load_reference_cache(root)
+
+
+class CudaModuleSpy:
+    """Forwards every operator call to a real `cuda_module` and keeps the last arguments and result of each, so that a
+    test can read the tensors the reference's wrappers exchange with its kernels (scores, probabilities, thresholds)."""
+
+    def __init__(self, real):
+        self._real = real
+        self.calls = {}
+
+    def __getattr__(self, name):
+        fn = getattr(self._real, name)
+
+        def wrapped(*args):
+            out = fn(*args)
+            self.calls[name] = {"args": args, "out": out}
+            return out
+
+        return wrapped
+
+
+def load_reference_stack():
+    """The COMPLETE reference on this machine's GPU: its caller (model/KVCache_AlignedKV.py), its wrapper classes
+    (extension/k_cache_file.py, extension/v_cache_file.py) - all imported unchanged from the vendored checkout - over
+    its own CUDA kernels compiled unmodified for sm_100a (oracle/_ref/kv_cache_cuda.so).  Returns
+    (QuantizedCache_AlignedKV, spy) or None when the checkout or the compiled extension is missing.  The reference's
+    loader module (extension/KV_cache_cpp_extention.py, which compiles at import time with a hard-coded host compiler)
+    is the one thing replaced: a stub module whose `cuda_module` is the spy around the compiled extension."""
+    import sys
+    import types
+    root, ext = reference_root(), load_reference_extension()
+    if root is None or ext is None:
+        return None
+    import transformers.cache_utils as cache_utils
+    spy = CudaModuleSpy(ext)
+    names = ["extension", "extension.KV_cache_cpp_extention", "extension.k_cache_file", "extension.v_cache_file"]
+    saved = {n: sys.modules.get(n) for n in names}
+    pkg = types.ModuleType("extension")
+    pkg.__path__ = [os.path.join(root, "extension")]
+    stub = types.ModuleType("extension.KV_cache_cpp_extention")
+    stub.cuda_module = spy
+    for n in names:
+        sys.modules.pop(n, None)
+    sys.modules["extension"] = pkg
+    sys.modules["extension.KV_cache_cpp_extention"] = stub
+
+    class _PlainCache:
+        def __init__(self, *a, **k):
+            pass
+
+    real = cache_utils.Cache
+    cache_utils.Cache = _PlainCache
+    try:
+        spec = importlib.util.spec_from_file_location("akv_full_reference_KVCache_AlignedKV",
+                                                      os.path.join(root, "model", "KVCache_AlignedKV.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    finally:
+        cache_utils.Cache = real
+        for n in names:
+            sys.modules.pop(n, None)
+            if saved[n] is not None:
+                sys.modules[n] = saved[n]
+    return mod.QuantizedCache_AlignedKV, spy
