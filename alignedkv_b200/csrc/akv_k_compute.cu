@@ -425,8 +425,25 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     int grid = (int)((warps_needed + wpc - 1) / wpc);
     size_t smem = (size_t)wpc * per_warp;
     auto go = [&](auto kern) -> int {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_status(e, "k_cache_compute smem attribute");
+        // the opt-in shared-memory size is a per-device attribute of the kernel: set it once per (kernel, device) - to
+        // the device's maximum, so that every launch shape fits - not on every launch
+        static const void* done_kernel[32];
+        static int done_device[32];
+        static int done_count = 0;                 // (guarded by nothing: a racing thread at worst sets it twice)
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const void* kp = reinterpret_cast<const void*>(kern);
+        bool done = false;
+        for (int i = 0; i < done_count && i < 32; ++i) done = done || (done_kernel[i] == kp && done_device[i] == dev);
+        if (!done) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, budget);
+            if (e != cudaSuccess) return cuda_status(e, "k_cache_compute smem attribute");
+            if (done_count < 32) {
+                done_kernel[done_count] = kp;
+                done_device[done_count] = dev;
+                ++done_count;
+            }
+        }
         launch_chained(kern, dim3(grid), dim3(wpc * 32), smem, st, p);
         return AKV_OK;
     };

@@ -28,22 +28,6 @@ class DecodeLayer:
     n_heads is the number of KV heads; n_q_heads (default: the same) may be a multiple of it (grouped-query
     attention; query head i reads KV head i // group).  v_mode "exact" runs P.V in the reference's token order
     (bit-identical to its kernel), "order_free" splits the token axis and accumulates in fp32."""
-    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) by (bench workload, kernel): taken from the
-    # ncu capture of the quarter-batch workload and scaled by 4, because every (batch, head) streams its own planes
-    # once and traffic grows in proportion to the batch
-    NCU_TRAFFIC = {
-        ("llama2-7b-layer-decode", "k_compute"): 4 * (53.549824e6 + 96.768e3),
-        ("llama2-7b-layer-decode", "v_compute"): 4 * 34.341888e6,
-        ("llama2-7b-layer-decode", "v_compute_order_free"): 4 * 34.301952e6,
-        ("llama2-7b-layer-decode-b2", "k_compute"): 53.549824e6 + 96.768e3,
-        ("llama2-7b-layer-decode-b2", "v_compute"): 34.341888e6,
-        ("llama2-7b-layer-decode-b2", "v_compute_order_free"): 34.301952e6,
-        ("llama3-8b-gqa-decode", "k_compute"): 4 * (232.081408e6 + 8.375296e6),
-        ("llama3-8b-gqa-decode", "v_compute"): 4 * (144.298496e6 + 3.497984e6),
-        ("llama3-8b-gqa-decode-b16", "k_compute"): 232.081408e6 + 8.375296e6,
-        ("llama3-8b-gqa-decode-b16", "v_compute"): 144.298496e6 + 3.497984e6,
-    }
-
     def __init__(self, bsz: int, max_seq_len: int, n_heads: int, head_dim: int, device, n_q_heads: int | None = None,
                  v_mode: str = "exact"):
         self.lib = _lib.load()

@@ -69,6 +69,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-other-workloads", action="store_true",
+                    help="default workload only: do not also measure the grouped-query and long-context workloads")
     ap.add_argument("--workload", default="llama2-7b-layer-decode", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graphs", action="store_true",
                     help="decoder workload: launch the dense parts op by op instead of replaying CUDA graphs")
@@ -81,13 +83,51 @@ def parse():
     return args
 
 
+# ---------------------------------------------------------------------------------------------- shared by both arms
+SHARDING_TEXT = {
+    "replicate": "(batch, kv-head) units, no collective; every rank runs the full shape",
+    "batch": "batch rows split across ranks, no collective",
+    "sequence": "cached sequence split across ranks; one all-gather of (max, sum, output) records + log-sum-exp merge",
+    "sequence_exact": "cached sequence split across ranks at multiples of 4096 tokens; four-phase step (akv_shard_step) "
+                      "with exchanges of chunk statistics, probe candidates, winner rows and partial outputs: read "
+                      "decisions of one device holding the whole sequence",
+}
+
+
+def config_dict(name: str, world: int, v_mode: str | None = None) -> dict:
+    """The workload as both arms report it (same keys, same values)."""
+    W = WORKLOADS[name]
+    Bt, Hq, H, D, L = (W[k_] for k_ in ("batch", "heads", "kv_heads", "head_dim", "cache_len"))
+    sharding = W["sharding"] if (world > 1 or W["sharding"] == "sequence_exact") else "replicate"
+    per_gpu = -(-Bt // world) if sharding == "batch" else Bt
+    tokens = Bt * world if W["sharding"] == "replicate" else Bt
+    plane_tokens = L if sharding in ("replicate", "batch") else -(-L // world)
+    plane_mib = per_gpu * H * (-(-plane_tokens // 64) * 64) * D * 4 / 2 ** 20       # K + V: high byte + two nibble planes each
+    return {"workload": name, "batch": Bt, "query_heads": Hq, "kv_heads": H, "head_dim": D, "cache_len": L,
+            "per_gpu_batch": per_gpu, "global_batch": tokens, "pv_kernel": v_mode or W["v_mode"],
+            "sharding": SHARDING_TEXT[sharding],
+            "step": "rewind to cache_len-1 tokens -> append the last token (flushes a 64-token block through the plane "
+                    "writers) -> decode",
+            "l2": "inputs larger than L2 (planes about %.0f MiB per GPU)" % plane_mib}
+
+
 # ---------------------------------------------------------------------------------------------- CPU baseline
-def cpu_dense_baseline(seed: int, budget_s: float = 12.0):
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_dense_baseline(seed: int, budget_s: float = 12.0, name: str | None = None):
     """The reference's torch dense-attention path on the host cores, on a bounded sample of the workload:
-    one batch row (all heads, full cache length), repeated while the time budget lasts."""
+    one batch row (all heads, full cache length), repeated while the time budget lasts.  All host cores are used
+    (a launcher such as torchrun sets OMP_NUM_THREADS=1 for its children; that is undone here)."""
     import torch
     from oracle.pipeline import dense_attention_torch_cpu
-    H, D, L = WORKLOAD["heads"], WORKLOAD["head_dim"], WORKLOAD["cache_len"]
+    W = WORKLOADS[name or WORKLOAD["name"]]
+    H, D, L = W["heads"], W["head_dim"], W["cache_len"]
+    torch.set_num_threads(host_cores())
     g = torch.Generator().manual_seed(seed)
     k = torch.randn(1, L, H, D, generator=g)
     k[..., list(OUTLIER_CHANNELS)] *= 20
@@ -104,8 +144,9 @@ def cpu_dense_baseline(seed: int, budget_s: float = 12.0):
         times.append(time.perf_counter() - t0)
     med = statistics.median(times)
     return {"value": 1.0 / med, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"1 of {WORKLOAD['batch']} batch rows ({H} heads x {L} cached tokens), median of {len(times)} "
-                      f"runs of the reference's fp16 torch dense attention on CPU"}, med
+            "sample": f"1 of {W['batch']} batch rows ({H} heads x {L} cached tokens), median of {len(times)} "
+                      f"runs of the reference's fp16 torch dense attention on CPU (its prefill / dense path, "
+                      f"model/KVCache_AlignedKV.py:77-79,97,87-88); per-step time extrapolated from that row"}, med
 
 
 def run_reference_arm(args):
@@ -115,11 +156,10 @@ def run_reference_arm(args):
     base, med = cpu_dense_baseline(args.seed, budget_s=20.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": med * 1e3 * WORKLOAD["batch"],
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD["name"], **{k: v for k, v in WORKLOAD.items() if k != "name"},
-                   "note": "reference's torch dense fp16 attention on the host cores; per-step time extrapolated "
-                           "from one batch row"},
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": med * 1e3 * WORKLOAD["batch"],
+        "higher_is_better": True, "scaling": "weak" if WORKLOAD["sharding"] == "replicate" else "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": config_dict(WORKLOAD["name"], args.gpus, args.v_mode),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -195,29 +235,42 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------- our arm
-def run_ours(args):
+def load_traffic_table():
+    """DRAM bytes per (batch, KV head) unit and launch of the two streaming kernels, from the ncu captures summarised
+    under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum of a captured launch / its units)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            return json.load(f)["per_unit_bytes"]
+    except (OSError, KeyError, ValueError):
+        return {}
+
+
+def reference_kernels():
+    """The reference's own CUDA kernels compiled unmodified for sm_100a (oracle/_ref), or None.  Used outside the timed
+    region only: as the checker of the step's output and as the `kernel to beat` timed beside ours."""
+    so = os.path.join(ROOT, "oracle", "_ref", "kv_cache_cuda.so")
+    if not os.path.exists(so):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("kv_cache_cuda", so)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measure(name, args, ctx, min_seconds=0.5):
+    """One workload on this job's ranks: returns the dict of everything measured (rank 0; None on the others)."""
     import torch
     import torch.distributed as dist
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: alignedkv_b200 has no CPU path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    from alignedkv_b200 import _lib
     from alignedkv_b200.decode import DecodeLayer
-    _lib.load()
-
-    Bt, Hq, H, D, L = (WORKLOAD[k_] for k_ in ("batch", "heads", "kv_heads", "head_dim", "cache_len"))
-    sharding = WORKLOAD["sharding"] if world > 1 else "replicate"
-    v_mode = args.v_mode or WORKLOAD["v_mode"]
     from alignedkv_b200.sharded import (DecisionExactShardedDecoder, SequenceShardedDecoder, chunk_bounds, shard_batch,
                                         shard_bounds)
+    rank, world, dev = ctx["rank"], ctx["world"], ctx["dev"]
+    W = WORKLOADS[name]
+    Bt, Hq, H, D, L = (W[k_] for k_ in ("batch", "heads", "kv_heads", "head_dim", "cache_len"))
+    G = Hq // H
+    sharding = W["sharding"] if world > 1 else "replicate"
+    v_mode = args.v_mode or W["v_mode"]
     if sharding == "batch":
         lo, hi = shard_batch(Bt, world, rank)
         B = hi - lo
@@ -240,7 +293,7 @@ def run_ours(args):
         seq.prefill(k[:, :hi - lo].contiguous(), v[:, :hi - lo].contiguous())
         layer = seq.backend.layer
         k_tok, v_tok = k[:, hi - lo:].contiguous(), v[:, hi - lo:].contiguous()
-    elif sharding == "sequence_exact" or WORKLOAD["sharding"] == "sequence_exact":
+    elif sharding == "sequence_exact" or W["sharding"] == "sequence_exact":
         # rank r holds tokens [lo, hi) of the L-1 cached tokens, lo a multiple of 4096; every rank sees the decode token
         # (it feeds the exponent maxima), the last rank stores it
         seq = DecisionExactShardedDecoder(B, L - 1, 1, H, D, dev, n_q_heads=Hq)
@@ -258,7 +311,6 @@ def run_ours(args):
         k, v = draw(L)
         layer.prefill(k[:, :L - 1].contiguous(), v[:, :L - 1].contiguous())
         k_tok, v_tok = k[:, L - 1:].contiguous(), v[:, L - 1:].contiguous()
-    del k, v
     q = torch.randn(B, 1, Hq, D, device=dev, generator=torch.Generator(device=dev).manual_seed(args.seed + 7)).half()
     owner = seq if isinstance(seq, DecisionExactShardedDecoder) else layer
     snap = owner.snapshot()                                # state before the decode token (63 tokens in the residual)
@@ -292,42 +344,60 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup, sampler=None):
+    def timed_blocks(fn, steps, warmup, seconds):
+        """Blocks of exactly `steps` steps, each bracketed by a barrier + synchronize on both sides and timed with
+        CUDA events; repeated until `seconds` of device time have been measured (at least 3 blocks).  Returns, per
+        block, the MAX over the ranks of the block's time, and every rank's own times (on rank 0)."""
         for _ in range(warmup):
             fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        own, worst = [], []
         t0 = time.time()
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
+        while len(worst) < 3 or (sum(worst) < seconds * 1e3 and len(worst) < 400):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            barrier()
+            own.append(ms)
+            if world > 1:
+                t = torch.tensor([ms], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)       # (the same number of blocks runs on every rank)
+                ms = float(t.item())
+            worst.append(ms)
         t1 = time.time()
-        ms = e0.elapsed_time(e1)
-        barrier()
+        per_rank = None
         if world > 1:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, t0, t1
+            mine = torch.tensor([min(own), statistics.median(own), max(own)], device=dev, dtype=torch.float64)
+            allr = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(allr, mine)
+            per_rank = [[round(float(x) / steps * 1e3, 2) for x in r.tolist()] for r in allr]   # us per step
+        return worst, per_rank, t0, t1
 
     warm = max(args.warmup, 3)
-    sampler = ClockSampler(local) if rank == 0 else None
+    sampler = ClockSampler(ctx["local"]) if rank == 0 else None
     layer.launches = 0
     if sampler:
         sampler.start()
-    ms, t0, t1 = timed(step_resident, args.steps, warm)    # the headline: no instrumentation inside the steps
-    launches = layer.launches // (args.steps + warm)       # kernels of this library per step (its own counter)
+    blocks, per_rank, t0, t1 = timed_blocks(step_resident, args.steps, warm, min_seconds)   # no instrumentation inside
+    launches = layer.launches // (args.steps * len(blocks) + warm)   # kernels of this library per step (its own counter)
+    ms = statistics.median(blocks)
     # the same steps again with CUDA events recorded around the two streaming kernels (the events cost ~10 us per
     # step, which is why they stay out of the headline pass)
     layer.reset_counters()
-    ms_ev, _, t1 = timed(step_resident, args.steps, 1)
-    clocks = sampler.stop(t0, t1) if sampler else None
+    for _ in range(min(2 * args.steps, 200)):
+        step_resident()
+    clocks = sampler.stop(t0, time.time()) if sampler else None
     kern = layer.kernel_times()                            # median per-kernel CUDA-event durations of that pass
-    ms_e2e, _, _ = timed(step_e2e, args.steps, warm)
+    e2e_blocks, _, _, _ = timed_blocks(step_e2e, args.steps, warm, min_seconds / 2)
+    ms_e2e = statistics.median(e2e_blocks)
 
     # algorithmic bytes under this step's read decisions, summed over the ranks
+    out_last = step_resident()
+    torch.cuda.synchronize()
     acct = layer.bytes_accounting(q)
     keys = ("k_compute", "v_compute", "read", "dense")
     tot = torch.tensor([acct[k_] for k_ in keys], device=dev, dtype=torch.float64)
@@ -335,59 +405,210 @@ def run_ours(args):
         dist.all_reduce(tot)
     total = dict(zip(keys, (float(x) for x in tot.tolist())))
 
+    # ---- outside the timed region: is the output right, and what do the reference's kernels need on the same state
+    flag = torch.tensor([int(layer.lib.akv_device_error_flag())], device=dev)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    check = validate(layer, q, k, v, out_last, G, v_mode, sharded_sequence=seq is not None and world > 1,
+                     want_ref_timing=(rank == 0))
+    check["device_error_flag"] = int(flag.item())
+    if check["device_error_flag"] != 0:
+        raise SystemExit("bench: a bounded wait inside a kernel gave up during the run (akv_device_error_flag != 0)")
+    for key_, bound in (("exact_vs_ref_kernel", 1e-3), ("step_output_vs_fp32_dense", 0.1)):
+        if check["accuracy"].get(key_) is not None and check["accuracy"][key_] > bound:
+            raise SystemExit(f"bench: {key_} = {check['accuracy'][key_]:.3e} exceeds {bound}")
+    if rank != 0:
+        return None
+    ms_step = ms / args.steps
+    tokens = Bt * world if W["sharding"] == "replicate" else Bt
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    traffic = load_traffic_table()
+    units = B * H
+    n_tok = layer.rest_start
+
+    def roofline_of(kname):
+        if kname not in kern:
+            return None
+        a = acct[kname] / (kern[kname]["us"] * 1e-6) / 1e9
+        tkey = "%s|group%d|%s" % (kname if not (kname == "v_compute" and v_mode == "order_free") else
+                                  "v_compute_order_free", G, n_tok)
+        per_unit = traffic.get(tkey)
+        return {"bound": "hbm", "kernel": kname, "achieved": a, "peak": peak, "unit": "GB/s", "frac": a / peak,
+                "peak_source": "of measured" if peaks else "of fallback",
+                "traffic": per_unit * units if per_unit is not None else None,
+                "us_per_launch": kern[kname]["us"], "algorithmic_bytes": acct[kname]}
+
+    dom = max(kern, key=lambda n: kern[n]["us"]) if kern else None
+    roofline = roofline_of(dom) if dom else None
+    if roofline:
+        roofline["timing"] = ("median of CUDA-event brackets around the kernel in a second pass of the same steps (the "
+                              "brackets cost ~10 us per step and are kept out of the headline pass)")
+        roofline["other_kernel"] = roofline_of("k_compute" if dom == "v_compute" else "v_compute")
+    cfg = config_dict(name, world, v_mode)
+    if isinstance(seq, DecisionExactShardedDecoder):
+        cfg["sharding"] = SHARDING_TEXT["sequence_exact"]
+    return {
+        "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak" if W["sharding"] == "replicate" else "strong", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": cfg,
+        "timing": {"blocks": len(blocks), "steps_per_block": args.steps, "block_ms_median": ms, "block_ms_min": min(blocks),
+                   "block_ms_max": max(blocks), "seconds_timed": sum(blocks) * 1e-3,
+                   "per_rank_us_per_step_min_median_max": per_rank,
+                   "rule": "every block = exactly `steps` steps between barrier + synchronize pairs, CUDA events, max "
+                           "over ranks; the reported step time is the median block"},
+        "effective_hbm_gbs": total["dense"] / (ms_step * 1e-3) / 1e9,
+        "achieved_hbm_gbs": total["read"] / (ms_step * 1e-3) / 1e9,
+        "bytes_read_over_dense": total["read"] / total["dense"],
+        "kernels_us": {n: round(kv_["us"], 2) for n, kv_ in kern.items()},
+        "roofline": roofline,
+        "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": int((q.numel() + k_tok.numel() + v_tok.numel()) * 2),
+                "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches * args.steps,
+        "clocks": clocks,
+        "accuracy": check["accuracy"],
+        "validation": {"device_error_flag": check["device_error_flag"], "note": check["note"]},
+        "ref_cuda_kernels_us": check["ref_cuda_kernels_us"],
+    }
+
+
+def validate(layer, q, k, v, out_last, G, v_mode, sharded_sequence, want_ref_timing):
+    """Outside the timed region, on the state the last step left behind: max-norm relative errors
+    max|a - b| / max|b| of the step's output against fp32 dense attention over the original tensors and - where the
+    reference's kernels can run (multi-head attention, their compiled extension at hand) - of the exact and the
+    order-free P.V kernels against the reference kernel on the same probabilities and thresholds; and the reference
+    kernels' own durations on that state (aligned, and reading every plane)."""
+    import math
+    import torch
+    from alignedkv_b200 import _lib
+    acc = {"exact_vs_ref_kernel": None, "order_free_vs_ref_kernel": None, "exact_vs_fp32_dense": None,
+           "order_free_vs_fp32_dense": None, "ref_kernel_vs_fp32_dense": None, "step_output_vs_fp32_dense": None}
+    res = {"accuracy": acc, "ref_cuda_kernels_us": None, "note": ""}
+    if sharded_sequence:
+        res["note"] = "sequence-sharded run: no rank holds the whole sequence, accuracy is covered by the tests"
+        return res
+    B, H, Hq, D, L = layer.B, layer.H, layer.Hq, layer.D, layer.cache_len
+    dev = q.device
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max())
+
+    # fp32 dense attention over the original fp16 tensors, one batch row at a time
+    truth = torch.empty(B, 1, Hq, D, device=dev)
+    for b in range(B):
+        kk = k[b, :L].float().repeat_interleave(G, dim=1).transpose(0, 1)        # [Hq, L, D]
+        vv = v[b, :L].float().repeat_interleave(G, dim=1).transpose(0, 1)
+        s = torch.matmul(q[b, 0].float().unsqueeze(1), kk.transpose(1, 2)) / math.sqrt(D)   # [Hq, 1, L]
+        truth[b, 0] = torch.matmul(torch.softmax(s, dim=-1), vv).squeeze(1)
+        del kk, vv
+    acc["step_output_vs_fp32_dense"] = rel(out_last, truth)
+    acc["exact_vs_fp32_dense" if v_mode == "exact" else "order_free_vs_fp32_dense"] = acc["step_output_vs_fp32_dense"]
+    qn = layer.rest_start
+    if layer.rest_len != 0 or qn == 0:
+        res["note"] = "residual tokens present: per-kernel comparison skipped"
+        return res
+    R = (qn // 64 + 1) * 64
+    p = layer.scratch[:B * Hq * R * 2].view(B, Hq, 1, R * 2)                       # probabilities as the operators take them
+    off = layer._scratch_offset("amin")
+    amin = layer.scratch[off:off + B * Hq].clone()
+    st = torch.cuda.current_stream(dev).cuda_stream
+    lib = layer.lib
+    other = torch.empty(B, 1, Hq, D, dtype=torch.half, device=dev)
+    nbytes = lib.akv_v_cache_compute_scratch_bytes(B, H, G, qn)
+    ws = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=dev)
+    flags = 0 if v_mode == "order_free" else 2                                     # the P.V kernel the step did NOT use
+    rc = lib.akv_v_cache_compute_gqa(layer.v_first_8.data_ptr(), layer.v_mid_4.data_ptr(), layer.v_last_4.data_ptr(),
+                                     p.data_ptr(), amin.data_ptr(), other.data_ptr(), ws.data_ptr(), ws.numel(), B, H, G,
+                                     layer.L, D, R, qn, flags, st)
+    _lib.check("v_cache_compute", rc)
+    acc["order_free_vs_fp32_dense" if v_mode == "exact" else "exact_vs_fp32_dense"] = rel(other, truth)
+    exact, order_free = (out_last, other) if v_mode == "exact" else (other, out_last)
+    ext = reference_kernels() if G == 1 else None
+    if ext is None:
+        res["note"] = ("grouped-query attention: the reference's kernels assert multi-head attention" if G > 1 else
+                       "the reference's compiled extension (oracle/_ref) is not at hand")
+        return res
+    nmb = layer.k_first_8.shape[2]
+    kq_off, kqm_off = layer._scratch_offset("kq"), layer._scratch_offset("kqmax")
+    kq = layer.scratch[kq_off:kq_off + B * Hq * D].view(B, 1, Hq, D)
+    kqmax = layer.scratch[kqm_off:kqm_off + B * Hq].view(B, 1, Hq, 1)
+    amin4 = amin.view(B, Hq, 1, 1)
+
+    def ref_k(reference):
+        return ext.k_cache_compute(layer.k_first_8, layer.k_mid_4, layer.k_last_4, kq, kqmax, q.view(torch.uint8), B, H,
+                                   qn // 64, nmb, D, 64, 1, 1.0 / math.sqrt(D), reference)
+
+    def ref_v(reference):
+        return ext.v_cache_compute(layer.v_first_8, layer.v_mid_4, layer.v_last_4, p, amin4, B, H, layer.L, D, R, qn,
+                                   reference)
+
+    o_ref = ref_v(False).view(torch.half).view(B, 1, Hq, D)
+    torch.cuda.synchronize()
+    acc["exact_vs_ref_kernel"] = rel(exact, o_ref)
+    acc["order_free_vs_ref_kernel"] = rel(order_free, o_ref)
+    acc["ref_kernel_vs_fp32_dense"] = rel(o_ref, truth)
+    if want_ref_timing:
+        def med_us(fn):
+            ts = []
+            for i in range(6):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                if i > 0:
+                    ts.append(e0.elapsed_time(e1) * 1e3)
+            return round(statistics.median(ts), 1)
+        res["ref_cuda_kernels_us"] = {
+            "what": "the reference's own kernels (extension/csrc, compiled unmodified for sm_100a) on the state of the "
+                    "timed step: same planes, alignment inputs, probabilities and thresholds; median of 5 launches",
+            "k_compute": {"aligned": med_us(lambda: ref_k(False)), "all_planes": med_us(lambda: ref_k(True))},
+            "v_compute": {"aligned": med_us(lambda: ref_v(False)), "all_planes": med_us(lambda: ref_v(True))}}
+    return res
+
+
+OTHER_WORKLOADS = ("llama3-8b-gqa-decode", "long-context-decode")
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: alignedkv_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from alignedkv_b200 import _lib
+    _lib.load()
+    ctx = dict(rank=rank, world=world, local=local, dev=dev)
+    line = measure(args.workload, args, ctx)
+    others = {}
+    if args.workload == "llama2-7b-layer-decode" and not args.no_other_workloads:
+        # the other configurations the metric is asked for, at the same number of GPUs: the grouped-query batch (batch
+        # rows split across the ranks) and the long context (sequence split across the ranks, one NCCL all-gather +
+        # log-sum-exp merge per step)
+        for name in OTHER_WORKLOADS:
+            torch.cuda.empty_cache()
+            r = measure(name, args, ctx, min_seconds=0.25)
+            if r is not None:
+                others[name] = {k_: r[k_] for k_ in ("value", "unit", "ms_per_step", "scaling", "config", "kernels_us",
+                                                     "roofline", "e2e", "bytes_read_over_dense", "accuracy", "timing",
+                                                     "gpu_launches", "ref_cuda_kernels_us")}
     if rank == 0:
-        ms_step = ms / args.steps
-        tokens = Bt * world if WORKLOAD["sharding"] == "replicate" else Bt
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except OSError:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        dom = max(kern, key=lambda n: kern[n]["us"]) if kern else None
-        roofline = None
-        if dom:
-            a = acct[dom] / (kern[dom]["us"] * 1e-6) / 1e9
-            roofline = {"bound": "hbm", "kernel": dom, "achieved": a, "peak": peak, "unit": "GB/s", "frac": a / peak,
-                        "peak_source": "measured" if peaks else "fallback",
-                        "traffic": layer.NCU_TRAFFIC.get((WORKLOAD["name"], dom + ("_order_free" if dom == "v_compute" and
-                                                                                    v_mode == "order_free" else ""))), "us_per_launch": kern[dom]["us"],
-                        "algorithmic_bytes": acct[dom],
-                        "timing": "median of CUDA-event brackets around the kernel in a second pass of the same "
-                                  "steps (the brackets cost ~10 us per step and are kept out of the headline pass)",
-                        "ms_per_step_with_events": ms_ev / args.steps}
-        line = {
-            "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak" if WORKLOAD["sharding"] == "replicate" else "strong", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD["name"], "batch": Bt, "query_heads": Hq, "kv_heads": H, "head_dim": D,
-                       "cache_len": L, "per_gpu_batch": B, "global_batch": tokens, "pv_kernel": v_mode,
-                       "sharding": {"replicate": "(batch, kv-head) units, no collective; every rank runs the full shape",
-                                    "batch": "batch rows split across ranks, no collective",
-                                    "sequence": "cached sequence split across ranks; one all-gather of (max, sum, "
-                                                "output) records + log-sum-exp merge",
-                                    "sequence_exact": "cached sequence split across ranks at multiples of 4096 tokens; "
-                                                      "four-phase step (akv_shard_step) with exchanges of chunk "
-                                                      "statistics, probe candidates, winner rows and partial outputs: "
-                                                      "read decisions of one device holding the whole sequence"}[
-                                       "sequence_exact" if isinstance(seq, DecisionExactShardedDecoder) else sharding],
-                       "step": "rewind to cache_len-1 tokens -> append the last token (flushes a 64-token block through "
-                               "the plane writers) -> decode",
-                       "l2": "inputs larger than L2 (planes %.0f MiB per GPU)" % (
-                           sum(t.numel() for t in (layer.k_first_8, layer.k_mid_4, layer.k_last_4, layer.v_first_8,
-                                                   layer.v_mid_4, layer.v_last_4)) / 2 ** 20)},
-            "effective_hbm_gbs": total["dense"] / (ms_step * 1e-3) / 1e9,
-            "achieved_hbm_gbs": total["read"] / (ms_step * 1e-3) / 1e9,
-            "bytes_read_over_dense": total["read"] / total["dense"],
-            "kernels_us": {n: round(kv_["us"], 2) for n, kv_ in kern.items()},
-            "roofline": roofline,
-            "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": int((q.numel() + k_tok.numel() + v_tok.numel()) * 2),
-                    "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": launches * args.steps,
-            "clocks": clocks,
-        }
+        if others:
+            line["other_workloads"] = others
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_dense_baseline(args.seed)
         print(json.dumps(line), flush=True)

@@ -237,7 +237,10 @@ int akv_lse_merge(const void* packed, void* out, int n_ranks, int rows, int head
  * allocating library routine.  Meant for hosts whose device memory was handed out once at start-up and is locked
  * afterwards, and for code that runs where an allocation (which synchronises the device) is not allowed.
  *  - Extents whose workspace (akv_decode_scratch_bytes) exceeds AKV_NOALLOC_SCRATCH_BYTES are rejected with
- *    AKV_ERR_SHAPE; so is a call while the "timing" knob is on (creating events allocates).
+ *    AKV_ERR_SHAPE.  The benchmark's "timing" knob (which creates CUDA events) is ignored by this entry point.
+ *  - With CUDA's lazy module loading the FIRST launch of each kernel of the step may allocate inside the driver; the
+ *    block writers first run on the step that completes a 64-token block.  A caller that must not allocate later warms
+ *    up with steps that cross a block boundary (the residual count passing 63) before its memory is locked.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *    current); make that first call before any stream capture begins.
  *  - All calls on a device share the one array and find the previous call's bytes in it.  Nothing in it has to
