@@ -23,7 +23,7 @@ struct Tuning {
     int k_wpc = 0;      // cap on warps per CTA of the q.K^T kernel (0 = as many as shared memory allows)
     int pdl = 1;        // 1: the kernels of a decode step are chained with programmatic dependent launch
     int k_gqa_kch = 8;  // channels per stage of the q.K^T kernel when query heads share KV heads (8 or 16)
-    int v_impl = 1;     // exact P.V kernel: 0 = chain warps read the landed stage with ldmatrix, 1 = producer-transposed form
+    int v_impl = 0;     // exact P.V kernel: 0 = chain warps read the landed stage with ldmatrix, 1 = producer-transposed form
     int v_nf = 0;       // exact P.V: ring depth in 64-token stages (0 = from the shared-memory budget)
     int v_nside = 0;    // exact P.V: rows of the nibble side ring, a power of two >= 64 (0 = default)
     int v_cps = 0;      // exact P.V: CTAs per SM the shared-memory budget is cut for (0 = one wave)

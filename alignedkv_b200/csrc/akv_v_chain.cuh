@@ -1,32 +1,36 @@
-// Exact-order P.V, streaming form: the kernel body behind v_cache_compute for head_dim 128.
+// Exact-order P.V, streaming form for multi-head attention: the kernel body behind v_cache_compute for head_dim 128.
 //
 // Replaces the reference's v_cache_compute_kernel (extension/csrc/V_cache.cu:178-308); bit-identical outputs: every
 // output channel is the fp16 fused-multiply-add chain over tokens 0..n-1 in order (V_cache.cu:203,304), skipped nibble
 // planes are replaced by the reference's constants (V_cache.cu:198-202,250-253).
 //
-// Design (B200).  The token order leaves one dependent chain per (batch, query head, channel pair); a dependent
-// fp16x2 FMA issues every ~4 cycles, so a chain can absorb about 60 GB/s of high bytes per (batch, head) - more than
-// a CTA's share of HBM - PROVIDED the chain warp spends its issue slots on little else.  The V layout is token-major
-// (a token's 128 high bytes are one row), while a chain thread wants "my channel pair, next tokens".  That
-// transposition is done by the load instruction itself: ldmatrix.x4.trans over eight token rows hands every lane the
-// 16-bit high-byte pair of ITS channel pair for eight consecutive tokens in four registers.  So the high bytes go
-// HBM -> shared memory (one 8 KB bulk asynchronous copy per 64-token stage, exactly as they lie in the plane) ->
-// registers of the chain (one ldmatrix + one 16-byte load of probabilities per 8 tokens), and per token the chain
-// issues one byte permute (high bytes + the constant low byte 0x80) and one FMA per query head.
-//   CTA = one (batch, KV head).  Warps: 2 * G / HPW chain warps + 1 producer warp.
-//   chain warp (head group hg, half wh): lane T owns channel pair 32*wh + 8*(T%4) + T/4 (channels 2p, 2p+1) of the
-//     HPW query heads hg*HPW .. +HPW-1: HPW independent accumulators that share the high-byte registers.
-//   producer warp: per stage it (1) waits until the stage's ring slot was released, (2) starts the 8 KB copy,
-//     (3) lane = tokens (lane, lane + 32): takes the probabilities from a buffer bulk-copied a chunk ahead, decides
-//     the read codes (V_cache.cu:211,250-251), (4) reserves rows of a small side ring for the tokens whose nibble
-//     rows some head of the group reads, records {first side row, union mask, per-head masks} for the chain,
-//     (5) starts 64-byte copies of just those nibble rows (one 4 KB copy when the whole stage reads the plane).
-//     All copies of a stage are byte-counted on the stage's mbarrier.
-//   Groups of 8 tokens in which a head reads a nibble plane (rare in aligned mode: the probability must be within two
-//   binades of the probe threshold) take a per-token path that rebuilds the low byte from the side ring; everything
-//   else is the lean path above.
+// Design (B200).  The token order leaves one dependent chain per (batch, head, channel pair), and the V layout is
+// token-major (a token's 128 high bytes are one row) while a chain thread wants "my channel pairs, next tokens".  That
+// transposition is done by the load instruction: ldmatrix.x4.trans over four token rows (one 8x8 matrix of 16-bit
+// words per token: its eight 16-byte chunks, 128 contiguous bytes, so no bank conflict) hands lane T, for each of
+// the four tokens, one register holding the high-byte pairs of channel pairs 16*(T%4) + T/4 and 16*(T%4) + 8 + T/4.
+// The LOW bytes come the same way from a table of the same shape that holds 0x80 for every channel of every token
+// (the reference's substitute when neither nibble plane is read: the rule, in aligned mode) except for the few tokens
+// whose probability lies within two binades of the threshold; their rows are built from the nibble planes.  So the
+// chain warp runs ONE branch-free instruction stream for every token: per 8 tokens four ldmatrix and one 16-byte load
+// of probabilities, per token two byte permutes (high + low bytes -> two fp16 pairs) and two FMAs - two independent
+// chains per thread, which hide the FMA latency.  That matters more than it seems: a warp whose steady loop carries
+// branches and rarely-run code, or does not fit the scheduler's instruction cache, was measured at a third of the
+// speed of the same arithmetic in a straight line.
+//   A unit = one (batch, head); a CTA holds UPC units, each with its own three warps, rings and barriers.
+//   chain warp: all 64 channel pairs of the head, one 64-token stage per loop iteration.
+//   copy warp: stage i -> ring slot i % nf as soon as the chain has released the slot's previous stage: one 8 KB bulk
+//     asynchronous copy of the high bytes exactly as they lie in the plane.
+//   decision warp: lane = tokens (lane, lane + 32) of a stage.  EARLY part, a ring ahead of its use: takes the
+//     probabilities from a buffer bulk-copied a chunk ahead, decides the read codes (V_cache.cu:211,250-251), reserves
+//     rows of a small side ring for the tokens that read a nibble plane and starts 64-byte copies of just those
+//     rows (one 4 KB copy when the whole stage reads a plane), counted on a barrier of their own.  LATE part, when the
+//     stage's ring slot is free: restores the table rows the slot's previous stage had patched, makes sure the nibble
+//     rows have landed (long ago), builds the flagged tokens' rows of the low-byte table, and arrives on the stage's
+//     barrier.  Requesting the nibble rows a ring ahead matters: issued together with the stage's high bytes, the few
+//     small copies completed late under load and held up every stage that had one.
 // Every wait is bounded (about a second); a wait that runs out raises the device error flag, the chain stores NaN
-// instead of a result, and the producer waits (bounded) for its copies in flight before the CTA leaves.
+// instead of a result, and the producers give their copies in flight time to land before the CTA leaves.
 #pragma once
 #include "akv_common.cuh"
 
@@ -50,7 +54,6 @@ struct VParams {
     int nf, nside, sch;     // streaming form: ring depth (stages), side-ring rows (power of two), stages per chunk
     int units;              // streaming form: number of (batch, KV head) units
     unsigned long long* prof;   // DEBUG
-    int dbg;                    // DEBUG
 };
 static unsigned long long* g_v_prof_host = nullptr;   // DEBUG
 
@@ -93,31 +96,18 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t a, uint32_t parity) {
     atomicOr(&g_v_wait_gave_up, 1u);
     return false;
 }
-// Bounded wait that polls with test_wait (never blocks in hardware) and sleeps between polls.
-__device__ __noinline__ bool mbar_wait_sleep(uint32_t a, uint32_t parity, uint32_t ns) {
-    unsigned long long t0 = 0;
-    for (int spin = 0; spin < (1 << 26); ++spin) {
-        uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-        if (ok) return true;
-        __nanosleep(ns);
-        if ((spin & 63) == 63) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            if (t0 == 0) t0 = t;
-            else if (t - t0 > 1000000000ull) break;
-        }
-    }
-    atomicOr(&g_v_wait_gave_up, 1u);
-    return false;
+// Non-blocking: has the phase with this parity completed?
+__device__ __forceinline__ uint32_t mbar_test(uint32_t a, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+    return ok;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, int* slow = nullptr) {
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(ok) : "r"(a), "r"(parity) : "memory");
     if (__builtin_expect(ok != 0, 1)) return true;
-    if (slow) ++*slow;
     return mbar_wait_slow(a, parity);
 }
 // Bulk asynchronous copy global -> shared through the TMA unit; 16-byte aligned addresses, size a multiple of 16.
@@ -130,28 +120,29 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
 namespace vch {
 constexpr int TOK = 64;            // tokens per stage
 constexpr int D = 128, HD = 64;    // head size, bytes of a nibble row
-constexpr int F_BYTES = TOK * D;   // high bytes of a stage
-__host__ __device__ constexpr int rec_bytes(int G) { return (16 + 8 * G + 15) & ~15; }
+constexpr int F_BYTES = TOK * D;   // high bytes of a stage (and its rows of the low-byte table)
+constexpr int REC = 16;            // record of a stage: {first side row, flagged tokens 0..31, 32..63, rows}
 
-// Shared-memory plan (byte offsets), computed the same way on both sides.
+// Shared-memory plan of one unit (byte offsets), computed the same way on both sides.
 struct Plan {
-    int f, mid, low, sb, rec, thr, bar, bytes;
+    int f, lw, mid, low, sb, rec, thr, bar, bytes;
 };
-__host__ __device__ inline Plan plan(int G, int nf, int nside, int sch) {
+__host__ __device__ inline Plan plan(int nf, int nside, int sch) {
     Plan p;
-    p.f = 0;
-    p.mid = nf * F_BYTES;
+    p.f = 0;                                   // nf stages of high bytes
+    p.lw = nf * F_BYTES;                       // nf stages of low bytes (the table)
+    p.mid = 2 * nf * F_BYTES;                  // side rings: rows of the mid / low nibble planes
     p.low = p.mid + nside * HD;
-    p.sb = p.low + nside * HD;                 // three probability buffers of G x sch x 64 values
-    p.rec = p.sb + 3 * G * sch * TOK * 2;      // per ring slot: {first side row, union mask lo, hi, rows} + per head mask lo, hi
-    p.thr = p.rec + nf * rec_bytes(G);         // threshold (already shifted) per head
-    p.bar = (p.thr + 4 * G + 7) & ~7;          // full[nf], free[nf], probability buffers[3]
-    p.bytes = p.bar + (2 * nf + 3) * 8;
+    p.sb = p.low + nside * HD;                 // three probability buffers of sch x 64 values
+    p.rec = p.sb + 3 * sch * TOK * 2;          // 2 nf records
+    p.thr = p.rec + 2 * nf * REC;              // threshold (already shifted)
+    p.bar = (p.thr + 4 + 7) & ~7;              // full[nf], free[nf], probability buffers[3], nibble rows[2 nf]
+    p.bytes = p.bar + (4 * nf + 3) * 8;
     return p;
 }
 }  // namespace vch
 
-// Both halves of the result = half `hi ? 1 : 0` of w (the probability of one token for both channels of the pair).
+// Both halves of the result = half `hi ? 1 : 0` of w (the probability of one token for both channels of a pair).
 __device__ __forceinline__ __half2 v_dup(uint32_t w, int hi) {
     const __half2 h = *reinterpret_cast<const __half2*>(&w);
     return hi ? __high2half2(h) : __low2half2(h);
@@ -161,66 +152,140 @@ __device__ __forceinline__ uint32_t v_fma(uint32_t k, __half2 s, uint32_t acc) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// Registers of one group of 8 tokens: high-byte pairs [token 2i | token 2i+1] and per head the 8 probabilities.
-template <int HPW>
-struct VGroup {
-    uint32_t h[4];
-    uint4 s[HPW];
-};
-// UPC (batch, KV head) units share a CTA, each with its own warps, rings and barriers.  With two units of four warps
-// (G = HPW) the CTA's warps are [chain, chain, copy, decision] x 2 and land one chain warp on each of the SM's four
-// schedulers; two independent CTAs of four warps would put both their chain warps on the same two schedulers.
-template <int G, int HPW, int UPC, int GPI>
-__global__ void __launch_bounds__(UPC * 32 * (2 * G / HPW + 2)) v_chain_kernel(const VParams p) {
+// About a millisecond of sleep: after a wait gave up (never expected), the copies in flight get time to land before
+// the CTA's shared memory is released.
+__device__ __noinline__ void v_sleep_ms() {
+#pragma unroll 1
+    for (int k = 0; k < 1000; ++k) __nanosleep(1000);
+}
+
+// Starts the copies of the nibble rows of one stage into the side ring and announces their bytes on `bar` (one
+// arrival).  Out of line: it runs for the minority of stages in which some token reads a nibble plane, and the
+// decision warp's steady loop has to stay small.
+//   M, L: mid / low plane rows of the stage's token 0;  ma, la: side rings;  start: first side row;  wrap: rows - 1
+//   um0 / um1: tokens 0..31 / 32..63 that read the mid plane;  c0 / c1: this lane's codes of tokens lane / lane+32
+__device__ __noinline__ void v_issue_nibble_rows(const uint8_t* M, const uint8_t* L, uint32_t ma, uint32_t la, uint32_t bar,
+                                                 uint32_t start, uint32_t wrap, uint32_t um0, uint32_t um1, int c0, int c1,
+                                                 int lane) {
     using namespace vch;
-    constexpr int NCW = 2 * G / HPW;               // chain warps of a unit; then its copy warp and its decision warp
-    constexpr int WPU = NCW + 2;                   // warps per unit
-    constexpr int REC = rec_bytes(G);
-    static_assert(G % HPW == 0, "heads per warp must divide the group");
+    const uint32_t ul0 = __ballot_sync(0xFFFFFFFFu, c0 == 0), ul1 = __ballot_sync(0xFFFFFFFFu, c1 == 0);
+    const uint32_t rows = __popc(um0) + __popc(um1);
+    if (lane == 0) mbar_arrive_expect(bar, (uint32_t)HD * (rows + __popc(ul0) + __popc(ul1)));
+    __syncwarp();
+    const uint32_t lt = (1u << lane) - 1u;
+    if ((um0 & um1) == 0xFFFFFFFFu && start + TOK <= wrap + 1) {
+        // the whole stage reads the mid plane: one 4 KB copy (and one for the low plane when it is all read)
+        if (lane == 0) bulk_copy(ma + start * HD, M, TOK * HD, bar);
+        if ((ul0 & ul1) == 0xFFFFFFFFu) {
+            if (lane == 0) bulk_copy(la + start * HD, L, TOK * HD, bar);
+        } else {
+            if (c0 == 0) bulk_copy(la + ((start + lane) & wrap) * HD, L + (size_t)lane * HD, HD, bar);
+            if (c1 == 0) bulk_copy(la + ((start + 32 + lane) & wrap) * HD, L + (size_t)(lane + 32) * HD, HD, bar);
+        }
+    } else {
+        const uint32_t r0 = (start + __popc(um0 & lt)) & wrap;
+        const uint32_t r1 = (start + __popc(um0) + __popc(um1 & lt)) & wrap;
+        if (c0 < 2) bulk_copy(ma + r0 * HD, M + (size_t)lane * HD, HD, bar);
+        if (c0 == 0) bulk_copy(la + r0 * HD, L + (size_t)lane * HD, HD, bar);
+        if (c1 < 2) bulk_copy(ma + r1 * HD, M + (size_t)(lane + 32) * HD, HD, bar);
+        if (c1 == 0) bulk_copy(la + r1 * HD, L + (size_t)(lane + 32) * HD, HD, bar);
+    }
+}
+
+// Builds the rows of the low-byte table for the flagged tokens of one stage from the side ring (V_cache.cu:250-253):
+// channel pair p of a token has mid byte [even channel nibble | odd channel nibble] and low byte likewise; the low
+// byte of the even channel is (mid & 0xF0) | (low >> 4), of the odd one ((mid & 0x0F) << 4) | (low & 0x0F); a token
+// that reads only the mid plane takes 0x88 for the low-plane byte.  Lane l builds channel pairs 2l, 2l+1 (4 bytes).
+//   lw: the stage's rows of the table;  ma, la: side rings;  rec: {first side row, flagged 0..31, 32..63, rows}
+//   s_a: the stage's probabilities;  thr: shifted threshold
+__device__ __noinline__ void v_build_low_rows(uint32_t lw, uint32_t ma, uint32_t la, uint4 rec, uint32_t wrap, uint32_t s_a,
+                                              uint32_t thr, int reference, int lane) {
+    using namespace vch;
+    uint32_t rank = 0;
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+        for (uint32_t bits = half ? rec.z : rec.y; bits; bits &= bits - 1, ++rank) {
+            const int t = half * 32 + __ffs(bits) - 1;
+            const uint32_t sb = lds16(s_a + t * 2);
+            const int diff = (int)(int16_t)(uint16_t)(thr - sb);
+            const bool low_too = reference || diff < 0x0400;             // (the token reads the mid plane: it is flagged)
+            const uint32_t row = ((rec.x + rank) & wrap) * HD + 2 * lane;
+            const uint32_t mb = lds16(ma + row);                          // pairs 2l, 2l+1
+            const uint32_t lb = low_too ? lds16(la + row) : 0x8888u;
+            const uint32_t even = (mb & 0xF0F0u) | ((lb >> 4) & 0x0F0Fu);     // [pair 2l, pair 2l+1] even channels
+            const uint32_t odd = ((mb & 0x0F0Fu) << 4) | (lb & 0x0F0Fu);
+            // bytes: [even(2l), odd(2l), even(2l+1), odd(2l+1)]
+            const uint32_t w = (even & 0xFFu) | ((odd & 0xFFu) << 8) | ((even & 0xFF00u) << 8) | ((odd & 0xFF00u) << 16);
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(lw + (uint32_t)t * D + lane * 4), "r"(w) : "memory");
+        }
+    }
+}
+
+// Puts the constant 0x80 back into the table rows of the tokens flagged in (m0, m1).
+__device__ __noinline__ void v_restore_low_rows(uint32_t lw, uint32_t m0, uint32_t m1, int lane) {
+    using namespace vch;
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half)
+#pragma unroll 1
+        for (uint32_t bits = half ? m1 : m0; bits; bits &= bits - 1)
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(lw + (uint32_t)(half * 32 + __ffs(bits) - 1) * D + lane * 4),
+                         "r"(0x80808080u) : "memory");
+}
+
+template <int UPC>
+__global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
+    using namespace vch;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int tid = threadIdx.x, lane = tid & 31;
-    // warp order inside the CTA: with two units the chain warps come first so that they spread over the schedulers
-    const int wcta = tid >> 5;
-    const int unit = UPC == 1 ? 0 : (wcta < UPC * NCW ? wcta / NCW : (wcta - UPC * NCW) / 2);
-    const int warp = UPC == 1 ? wcta : (wcta < UPC * NCW ? wcta % NCW : NCW + (wcta - UPC * NCW) % 2);
-    const long long bh = (long long)blockIdx.x * UPC + unit;   // (batch, KV head)
+    const int tid = threadIdx.x, lane = tid & 31, wcta = tid >> 5;
+    // Warp roles: per unit a chain warp, two decision warps (even / odd stages: one warp's serial walk through a stage
+    // takes longer than the chain needs to consume it) and a copy warp.  The warps of a CTA are spread over the SM's
+    // four schedulers by index: [chain u0, chain u1, decision0 u0, decision0 u1, copy u0, copy u1, decision1 u0,
+    // decision1 u1] gives each chain warp a scheduler it shares only with its copy warp (a handful of instructions per
+    // stage), and the four decision warps the other two.
+    const int unit = UPC == 1 ? 0 : (wcta & 1);
+    const int wrole = UPC == 1 ? wcta : (wcta >> 1);
+    const int role = wrole == 2 ? 3 : (wrole == 3 ? 2 : wrole);   // 0: chain, 1, 2: decision (even, odd stages), 3: copy
+    const long long bh = (long long)blockIdx.x * UPC + unit;   // (batch, head)
     const int n = p.n, nf = p.nf, nside = p.nside, sch = p.sch;
     const int nst = (n + TOK - 1) / TOK;
-    const Plan pl = plan(G, nf, nside, sch);
+    const Plan pl = plan(nf, nside, sch);
     const uint32_t base = smem_u32(smem) + (uint32_t)unit * (uint32_t)((pl.bytes + 127) & ~127);
-    const bool unit_on = bh < p.units;
     const uint32_t bar_full = base + pl.bar, bar_free = bar_full + nf * 8, bar_sb = bar_free + nf * 8;
-    const uint32_t sb_head = (uint32_t)sch * TOK * 2, sb_buf = sb_head * G;   // bytes of one head's chunk / one buffer
+    const uint32_t bar_nib = bar_sb + 3 * 8;
 
     pdl_enter();
-    if (warp == 0 && lane == 0) {
-        for (int s = 0; s < nf; ++s) {
-            mbar_init(bar_full + s * 8, 2);        // the copy warp's and the decision warp's arrivals (+ the stage's bytes)
-            mbar_init(bar_free + s * 8, NCW);      // one arrival per chain warp
+    if (role == 0) {
+        if (lane == 0) {
+            for (int s = 0; s < nf; ++s) {
+                mbar_init(bar_full + s * 8, 2);    // the copy warp's and the decision warp's arrivals (+ the high bytes)
+                mbar_init(bar_free + s * 8, 1);    // the chain warp's arrival
+            }
+            for (int s = 0; s < 3; ++s) mbar_init(bar_sb + s * 8, 1);
+            for (int s = 0; s < 2 * nf; ++s) mbar_init(bar_nib + s * 8, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         }
-        for (int s = 0; s < 3; ++s) mbar_init(bar_sb + s * 8, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        // the low-byte table starts as the constant: 0x80 for every channel of every token
+        for (int i = lane; i < nf * F_BYTES / 16; i += 32)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(base + pl.lw + i * 16), "r"(0x80808080u) : "memory");
     }
     __syncthreads();
-    if (!unit_on) return;                          // (odd number of units: the last CTA's second half has none)
+    if (bh >= p.units) return;                     // (odd number of units: the last CTA's second half has none)
 
-    if (warp == NCW) {
+    if (role == 3) {
         // ------------------------------------------------------------------ copy warp: the high bytes
-        // Stage i -> ring slot i % nf as soon as the chain has released the slot's previous stage: one 8 KB copy,
-        // announced on the stage's barrier together with this warp's arrival.
         const uint8_t* F = p.first8 + (size_t)bh * p.max_seq_len * D;
         int slot = 0;
         uint32_t parity = 0;                       // of the release being waited for: (i / nf - 1) & 1
+        bool alive = true;
         // The decision warp's first loads (probe result, exponent maxima) go out before this warp floods the memory
         // system with the first ring of copies - behind that flood they would take several times as long, and the
-        // first stage cannot be consumed before the thresholds are known.
-        asm volatile("bar.sync %0, 64;\n" ::"r"(1 + unit) : "memory");
-        bool alive = true;
-        int nslow = 0;
-        const long long c_t0 = clock64();
+        // first stage cannot be consumed before the threshold is known.
+        asm volatile("bar.sync %0, 96;\n" ::"r"(1 + unit) : "memory");
+#pragma unroll 1
         for (int i = 0; i < nst; ++i) {
             if (i >= nf) {
-                alive = (p.dbg & 2) ? mbar_wait_sleep(bar_free + slot * 8, parity, 100) : mbar_wait(bar_free + slot * 8, parity, &nslow);
+                alive = mbar_wait(bar_free + slot * 8, parity);
                 if (!alive) break;
             }
             if (lane == 0) {
@@ -231,367 +296,258 @@ __global__ void __launch_bounds__(UPC * 32 * (2 * G / HPW + 2)) v_chain_kernel(c
             }
             if (++slot == nf) { slot = 0; if (i >= nf) parity ^= 1u; }
         }
-        // a wait gave up (never expected): give the copies in flight time to land before the CTA's shared memory is
-        // released (a stage completes only with the other warp's arrival, which may not come any more)
-        if (!alive) for (int k = 0; k < 1000; ++k) __nanosleep(1000);
-        if (p.prof && lane == 0) { p.prof[bh * 16 + 8] = clock64() - c_t0; p.prof[bh * 16 + 9] = nslow; }
+        if (!alive) v_sleep_ms();
         return;
     }
-    if (warp == NCW + 1) {
-        int nslow_free = 0, nslow_sb = 0;
-        const long long d_t0 = clock64();
-        long long d_thr = 0;
-        // ------------------------------------------------------------------ decision warp: codes, records, nibble rows
+    if (role == 1 || role == 2) {
+        // ------------------------------------------------------------------ decision warps
+        // Warp w (0, 1) owns the stages of parity w.  The ring depth nf is even, so the previous stage of a ring slot
+        // belongs to the same warp, and each warp has its own half of the side ring: the two never share state.
+        const int w = role - 1;
         const uint8_t* M = p.mid4 + (size_t)bh * p.max_seq_len * HD;
         const uint8_t* L = p.last4 + (size_t)bh * p.max_seq_len * HD;
-        const uint16_t* s_rows = p.s + (size_t)bh * G * p.s_last_dim;
+        const uint16_t* s_row = p.s + (size_t)bh * p.s_last_dim;
         bool alive = true;
-        // probability chunk c (stages c*sch .. of every head) -> buffer c % 3; issued by one thread
+        // probability chunk c (stages c*sch ..) -> buffer `buf` = c % 3; issued by one thread of warp 0
         auto request_s = [&](int c, int buf) {
             const int t0 = c * sch * TOK;
             int cnt = n - t0;
             cnt = cnt > sch * TOK ? sch * TOK : cnt;
             const uint32_t bytes = (uint32_t)((cnt + 7) & ~7) * 2;     // rows are padded to a multiple of 8 values
-            const uint32_t bar = bar_sb + buf * 8;
-            mbar_arrive_expect(bar, bytes * G);
-#pragma unroll
-            for (int g = 0; g < G; ++g)
-                bulk_copy(base + pl.sb + (uint32_t)buf * sb_buf + g * sb_head, s_rows + (size_t)g * p.s_last_dim + t0,
-                          bytes, bar);
+            mbar_arrive_expect(bar_sb + buf * 8, bytes);
+            bulk_copy(base + pl.sb + (uint32_t)buf * (sch * TOK * 2), s_row + t0, bytes, bar_sb + buf * 8);
         };
-        if (lane == 0 && nst > 0) request_s(0, 0);
-        // thresholds: from the probe result (decode step) or as given
-        uint32_t A[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            uint32_t a;
-            if (p.test_o) {
-                a = v_threshold_warp(p.test_o, p.v_exp, bh * G + g, p.H, G, D, lane);
-                if (lane == 0) p.amin_out[bh * G + g] = (uint8_t)a;
-            } else {
-                a = p.amin[bh * G + g];
-            }
-            A[g] = (a << 10) & 0xFFFFu;
-            if (lane == 0) asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(base + pl.thr + g * 4), "r"(A[g]) : "memory");
+        if (w == 0 && lane == 0 && nst > 0) request_s(0, 0);
+        // threshold: from the probe result (decode step) or as given
+        uint32_t a;
+        if (p.test_o) {
+            a = v_threshold_warp(p.test_o, p.v_exp, bh, p.H, 1, D, lane);
+            if (w == 0 && lane == 0) p.amin_out[bh] = (uint8_t)a;
+        } else {
+            a = p.amin[bh];
         }
-        asm volatile("bar.sync %0, 64;\n" ::"r"(1 + unit) : "memory");
-        d_thr = clock64() - d_t0;
+        const uint32_t A = (a << 10) & 0xFFFFu;
+        asm volatile("bar.sync %0, 96;\n" ::"r"(1 + unit) : "memory");
+        const int hside = nside / 2;                       // rows of this warp's half of the side ring
+        const uint32_t ma = base + pl.mid + (uint32_t)w * hside * HD, la = base + pl.low + (uint32_t)w * hside * HD;
+        const uint32_t wrap = (uint32_t)(hside - 1);
         uint32_t side_head = 0, side_tail = 0;    // side rows handed out / taken back so far
-        int freed = 0, freed_slot = 0;            // stages whose release has been consumed; freed % nf
-        uint32_t freed_parity = 0;                // (freed / nf) & 1
-        const uint32_t lt = (1u << lane) - 1u;
-        auto reclaim = [&]() {                    // consume the release of stage `freed`: its side rows are free again
-            alive = (p.dbg & 2) ? mbar_wait_sleep(bar_free + freed_slot * 8, freed_parity, 100) : mbar_wait(bar_free + freed_slot * 8, freed_parity, &nslow_free);
-            side_tail += lds32(base + pl.rec + freed_slot * REC + 12);
-            ++freed;
-            if (++freed_slot == nf) { freed_slot = 0; freed_parity ^= 1u; }
-        };
-        int slot = 0, sic = 0, c = 0, cbuf = 0;   // of stage i: i % nf, i % sch, i / sch, (i / sch) % 3
-        uint32_t cpar = 0;                        // ((i / sch) / 3) & 1
-        for (int i = 0; i < nst && alive; ++i) {
-            while (alive && freed <= i - nf) reclaim();
-            if (!alive) break;
-            if (sic == 0) {             // entering chunk c: ask for the next one, make sure this one has landed
-                if ((c + 1) * sch < nst && lane == 0) request_s(c + 1, cbuf == 2 ? 0 : cbuf + 1);
-                alive = mbar_wait(bar_sb + cbuf * 8, cpar, &nslow_sb);
-                if (!alive) break;
+        const int nrec = 2 * nf;
+        int freed = w, freed_slot = w, freed_rec = w;   // next own stage whose release is to be consumed; % nf, % 2nf
+        uint32_t freed_parity = 0;                      // (freed / nf) & 1
+        uint32_t nib_par = 0;                           // bit r: parity of the NEXT phase of nibble barrier r
+        // consume the release of own stage `freed`: its side rows are free again, its patched table rows become 0x80 again
+        auto reclaim = [&]() {
+            alive = mbar_wait(bar_free + freed_slot * 8, freed_parity);
+            const uint4 rec = lds128(base + pl.rec + freed_rec * REC);
+            if (__builtin_expect(rec.w != 0, 0)) {
+                side_tail += rec.w;
+                if (alive) v_restore_low_rows(base + pl.lw + (uint32_t)freed_slot * F_BYTES, rec.y, rec.z, lane);
             }
-            const int t0 = i * TOK;
+            freed += 2;
+            if ((freed_slot += 2) >= nf) { freed_slot -= nf; freed_parity ^= 1u; }
+            if ((freed_rec += 2) >= nrec) freed_rec -= nrec;
+        };
+        // EARLY part for own stage j (position state advances with j).  armed = next own stage to be armed: side rows
+        // can only be waited for while an armed own stage is still unreleased; otherwise the stage is prepared later
+        // (returns false).
+        int e_rec = w, e_sic = w, e_c = 0, e_buf = 0;   // of stage j: j % 2nf, j % sch, j / sch, (j / sch) % 3
+        uint32_t e_par = 0;                             // ((j / sch) / 3) & 1
+        bool e_chunk = false;                           // the chunk of stage j has been entered
+        auto early = [&](int j, int armed) -> bool {
+            if (e_sic < 2 && !e_chunk) {    // entering chunk c: ask for the next one (warp 0), make sure this one has landed
+                if (w == 0 && (e_c + 1) * sch < nst && lane == 0) request_s(e_c + 1, e_buf == 2 ? 0 : e_buf + 1);
+                alive = mbar_wait(bar_sb + e_buf * 8, e_par);
+                if (!alive) return false;
+                e_chunk = true;
+            }
+            const int t0 = j * TOK;
             const int cnt = (n - t0) < TOK ? (n - t0) : TOK;
             // read codes of tokens `lane` and `lane + 32` from the bit patterns (V_cache.cu:211,250-251): 16-bit
-            // wrap-around, signed compare
-            const uint32_t sa = base + pl.sb + (uint32_t)cbuf * sb_buf + (uint32_t)sic * (TOK * 2) + lane * 2;
-            uint32_t mm[G][2];
-            int uc0 = 2, uc1 = 2;
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                // (beyond the last token the buffer holds stale but readable bytes; they are ignored)
-                const uint32_t s0 = lds16(sa + g * sb_head), s1 = lds16(sa + g * sb_head + 64);
-                const int d0 = (int)(int16_t)(uint16_t)(A[g] - s0), d1 = (int)(int16_t)(uint16_t)(A[g] - s1);
-                int c0 = p.reference ? 0 : (d0 >= 0x0800 ? 2 : (d0 >= 0x0400 ? 1 : 0));
-                int c1 = p.reference ? 0 : (d1 >= 0x0800 ? 2 : (d1 >= 0x0400 ? 1 : 0));
-                if (p.dbg & 4) c0 = c1 = 2;
-                if (lane >= cnt) c0 = 2;
-                if (lane + 32 >= cnt) c1 = 2;
-                mm[g][0] = __ballot_sync(0xFFFFFFFFu, c0 < 2);
-                mm[g][1] = __ballot_sync(0xFFFFFFFFu, c1 < 2);
-                uc0 = c0 < uc0 ? c0 : uc0;
-                uc1 = c1 < uc1 ? c1 : uc1;
-            }
-            // union over the heads of the group (with one head it is that head's masks)
-            const uint32_t um0 = G == 1 ? mm[0][0] : __ballot_sync(0xFFFFFFFFu, uc0 < 2);
-            const uint32_t um1 = G == 1 ? mm[0][1] : __ballot_sync(0xFFFFFFFFu, uc1 < 2);
-            const uint32_t bar = bar_full + slot * 8;
-            const uint32_t ra = base + pl.rec + slot * REC;
-            uint32_t rows = 0, start = 0, nib_bytes = 0, ul0 = 0, ul1 = 0;
-            if (um0 | um1) {            // (warp-uniform)
-                ul0 = __ballot_sync(0xFFFFFFFFu, uc0 == 0);
-                ul1 = __ballot_sync(0xFFFFFFFFu, uc1 == 0);
+            // wrap-around, signed compare  (beyond the last token the buffer holds stale but readable bytes)
+            const uint32_t sa = base + pl.sb + (uint32_t)e_buf * (sch * TOK * 2) + (uint32_t)e_sic * (TOK * 2) + lane * 2;
+            const uint32_t s0 = lds16(sa), s1 = lds16(sa + 64);
+            const int d0 = (int)(int16_t)(uint16_t)(A - s0), d1 = (int)(int16_t)(uint16_t)(A - s1);
+            int c0 = p.reference ? 0 : (d0 >= 0x0800 ? 2 : (d0 >= 0x0400 ? 1 : 0));
+            int c1 = p.reference ? 0 : (d1 >= 0x0800 ? 2 : (d1 >= 0x0400 ? 1 : 0));
+            if (lane >= cnt) c0 = 2;
+            if (lane + 32 >= cnt) c1 = 2;
+            const uint32_t um0 = __ballot_sync(0xFFFFFFFFu, c0 < 2), um1 = __ballot_sync(0xFFFFFFFFu, c1 < 2);
+            uint32_t rows = 0, start = 0;
+            if (__builtin_expect((um0 | um1) != 0, 0)) {    // (warp-uniform)
                 rows = __popc(um0) + __popc(um1);
-                nib_bytes = (uint32_t)HD * (rows + __popc(ul0) + __popc(ul1));
                 // rows of the side ring, taken in token order; wait for older stages to hand theirs back if it is full
-                while (alive && side_head + rows - side_tail > (uint32_t)nside) reclaim();
-                if (!alive) break;
-                start = side_head & (uint32_t)(nside - 1);
+                while (alive && side_head + rows - side_tail > (uint32_t)hside) {
+                    if (freed >= armed) return false;       // nothing armed is outstanding: prepare this stage later
+                    reclaim();
+                }
+                if (!alive) return false;
+                start = side_head & wrap;
                 side_head += rows;
+                nib_par ^= 1u << e_rec;
+                v_issue_nibble_rows(M + (size_t)t0 * HD, L + (size_t)t0 * HD, ma, la, bar_nib + e_rec * 8, start, wrap, um0,
+                                    um1, c0, c1, lane);
             }
-            if (lane == 0) {
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(ra), "r"(start), "r"(um0), "r"(um1), "r"(rows) : "memory");
-#pragma unroll
-                for (int g = 0; g < G; ++g) sts64(ra + 16 + g * 8, mm[g][0], mm[g][1]);
-                // publishes the record, announces the nibble bytes; the phase completes when all bytes have landed
-                if (nib_bytes) mbar_arrive_expect(bar, nib_bytes);
-                else mbar_arrive(bar);
+            if (lane == 0)
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(base + pl.rec + e_rec * REC), "r"(start), "r"(um0),
+                             "r"(um1), "r"(rows) : "memory");
+            __syncwarp();               // (the record is read back by every lane in the late part)
+            if ((e_rec += 2) >= nrec) e_rec -= nrec;
+            e_chunk = false;
+            if ((e_sic += 2) >= sch) {
+                e_sic -= sch;
+                ++e_c;
+                if (++e_buf == 3) { e_buf = 0; e_par ^= 1u; }
             }
-            if (rows) {
-                const uint32_t ma = base + pl.mid, la = base + pl.low, wrap = (uint32_t)(nside - 1);
-                const size_t src = (size_t)t0 * HD;
-                const bool dense = (um0 & um1) == 0xFFFFFFFFu && start + TOK <= (uint32_t)nside;
-                if (dense) {
-                    // the whole stage reads the mid plane: one 4 KB copy (and one for the low plane when it is all read)
-                    if (lane == 0) bulk_copy(ma + start * HD, M + src, TOK * HD, bar);
-                    if ((ul0 & ul1) == 0xFFFFFFFFu) {
-                        if (lane == 0) bulk_copy(la + start * HD, L + src, TOK * HD, bar);
-                    } else {
-                        if (uc0 == 0) bulk_copy(la + ((start + lane) & wrap) * HD, L + src + (size_t)lane * HD, HD, bar);
-                        if (uc1 == 0) bulk_copy(la + ((start + 32 + lane) & wrap) * HD, L + src + (size_t)(lane + 32) * HD, HD, bar);
+            return true;
+        };
+        int slot = w, rec = w, j = w;             // of stage i: i % nf, i % 2nf; j: next own stage to prepare
+        int l_sic = w, l_buf = 0;                 // of stage i: i % sch, (i / sch) % 3
+#pragma unroll 1
+        for (int i = w; i < nst && alive; i += 2) {
+            while (alive && freed <= i - nf) reclaim();
+            // phase 0: stage i must be prepared (it normally is, a ring ago), then it is armed; phase 1: run ahead, up
+            // to a ring's length (one call site of the early part for both)
+#pragma unroll 1
+            for (int phase = 0; phase < 2 && alive; ++phase) {
+                const int lim = phase == 0 ? i : i + nf;
+#pragma unroll 1
+                while (alive && j <= lim && j < nst) {
+                    if (!early(j, i + 2 * phase)) break;
+                    j += 2;
+                }
+                if (phase == 0 && alive) {
+                    // LATE part of stage i: its nibble rows (requested long ago) must have landed and its rows of the
+                    // low-byte table be built; then it is armed
+                    const uint4 r = lds128(base + pl.rec + rec * REC);
+                    if (__builtin_expect(r.w != 0, 0)) {
+                        alive = mbar_wait(bar_nib + rec * 8, ((nib_par >> rec) & 1u) ^ 1u);
+                        if (alive)
+                            v_build_low_rows(base + pl.lw + (uint32_t)slot * F_BYTES, ma, la, r, wrap,
+                                             base + pl.sb + (uint32_t)l_buf * (sch * TOK * 2) + (uint32_t)l_sic * (TOK * 2), A,
+                                             p.reference, lane);
                     }
-                } else {
-                    const uint32_t r0 = (start + __popc(um0 & lt)) & wrap;
-                    const uint32_t r1 = (start + __popc(um0) + __popc(um1 & lt)) & wrap;
-                    if (uc0 < 2) bulk_copy(ma + r0 * HD, M + src + (size_t)lane * HD, HD, bar);
-                    if (uc0 == 0) bulk_copy(la + r0 * HD, L + src + (size_t)lane * HD, HD, bar);
-                    if (uc1 < 2) bulk_copy(ma + r1 * HD, M + src + (size_t)(lane + 32) * HD, HD, bar);
-                    if (uc1 == 0) bulk_copy(la + r1 * HD, L + src + (size_t)(lane + 32) * HD, HD, bar);
+                    __syncwarp();
+                    if (lane == 0 && alive) mbar_arrive(bar_full + slot * 8);   // publishes the table rows; the copy warp adds the bytes
+                    if ((slot += 2) >= nf) slot -= nf;
+                    if ((rec += 2) >= nrec) rec -= nrec;
+                    if ((l_sic += 2) >= sch) { l_sic -= sch; l_buf = l_buf == 2 ? 0 : l_buf + 1; }
                 }
             }
-            if (++slot == nf) slot = 0;
-            if (++sic == sch) {
-                sic = 0;
-                ++c;
-                if (++cbuf == 3) { cbuf = 0; cpar ^= 1u; }
-            }
         }
-        // a wait gave up (never expected): give the copies in flight time to land before the CTA's shared memory is
-        // released
-        if (!alive) for (int k = 0; k < 1000; ++k) __nanosleep(1000);
-        if (p.prof && lane == 0) { p.prof[bh * 16 + 10] = clock64() - d_t0; p.prof[bh * 16 + 11] = nslow_free; p.prof[bh * 16 + 12] = nslow_sb; p.prof[bh * 16 + 13] = d_thr; }
+        if (!alive) v_sleep_ms();
         return;
     }
 
-    // ---------------------------------------------------------------------- chain warps
-    const int hg = warp >> 1, wh = warp & 1, g0 = hg * HPW;
-    const int pair = 32 * wh + 8 * (lane & 3) + (lane >> 2);          // this lane's channel pair
-    // ldmatrix row address of this lane inside a group of 8 tokens: matrix lane/8 = tokens 2i, 2i+1; row r of a matrix
-    // = token 2i + (r & 1), 16-byte chunk 4*wh + r/2 of the token's row
-    const uint32_t lm_off = (uint32_t)((2 * (lane >> 3) + (lane & 1)) * D + (4 * wh + ((lane & 7) >> 1)) * 16);
-    uint32_t acc[HPW];
-#pragma unroll
-    for (int h = 0; h < HPW; ++h) acc[h] = 0;
+    // ---------------------------------------------------------------------- chain warp
+    const int pairA = 16 * (lane & 3) + (lane >> 2), pairB = pairA + 8;   // this lane's channel pairs
+    // ldmatrix row address of this lane inside four token rows: matrix lane/8 = token, row lane%8 = 16-byte chunk
+    const uint32_t lm_off = (uint32_t)((lane >> 3) * D + (lane & 7) * 16);
+    uint32_t accA = 0, accB = 0;
     bool alive = true;
     const int nsf = n / TOK;                                           // full stages
-    uint32_t A[HPW];                                                   // thresholds, for the per-token path
-
-    // Position of a stage in the rings, advanced stage by stage (no divisions in the loop).
-    struct Pos {
-        int slot;            // ring slot = stage % nf
-        uint32_t parity;     // (stage / nf) & 1
-        int sic, buf;        // stage inside its probability chunk, chunk % 3
+    // Registers of one group of 8 tokens: per token [pair A even, odd | pair B even, odd] high bytes and low bytes, and
+    // the 8 probabilities.
+    struct Grp {
+        uint32_t h[8], l[8];
+        uint4 s;
     };
-    auto next_pos = [&](Pos q) {
-        if (++q.slot == nf) { q.slot = 0; q.parity ^= 1u; }
-        if (++q.sic == sch) { q.sic = 0; q.buf = q.buf == 2 ? 0 : q.buf + 1; }
-        return q;
-    };
-    auto f_addr = [&](const Pos& q) { return base + pl.f + (uint32_t)q.slot * F_BYTES; };
-    auto s_addr = [&](const Pos& q) {     // probabilities of token 0 of the stage, first head of this warp
-        return base + pl.sb + (uint32_t)q.buf * sb_buf + (uint32_t)g0 * sb_head + (uint32_t)q.sic * (TOK * 2);
-    };
-    auto fetch = [&](VGroup<HPW>& r, uint32_t fa, uint32_t sa, int grp) {
+    auto ldm = [](uint32_t (&r)[8], int o, uint32_t a) {
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(r.h[0]), "=r"(r.h[1]), "=r"(r.h[2]), "=r"(r.h[3]) : "r"(fa + (uint32_t)grp * (8 * D) + lm_off));
-#pragma unroll
-        for (int h = 0; h < HPW; ++h) r.s[h] = lds128(sa + h * sb_head + grp * 16);
+                     : "=r"(r[o]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]) : "r"(a));
     };
-    // Low bytes [even channel, odd channel] of this lane's pair for token t of the stage, head h of this warp, from the
-    // side ring under the head's own code (V_cache.cu:250-253); 0x8080 when the head reads neither plane.
-    auto low_word = [&](const uint4& rec, uint32_t sa, int t, int h) -> uint32_t {
-        const uint32_t sb = lds16(sa + h * sb_head + t * 2);
-        const int diff = (int)(int16_t)(uint16_t)(A[h] - sb);
-        const int code = p.reference ? 0 : (diff >= 0x0800 ? 2 : (diff >= 0x0400 ? 1 : 0));
-        if (code == 2) return 0x8080u;                                   // (warp-uniform)
-        const uint32_t rank = t < 32 ? __popc(rec.y & ((1u << t) - 1u))
-                                     : __popc(rec.y) + __popc(rec.z & ((1u << (t - 32)) - 1u));
-        const uint32_t row = ((rec.x + rank) & (uint32_t)(nside - 1)) * HD + pair;
-        const uint32_t mb = lds8(base + pl.mid + row);
-        const uint32_t lb = code == 0 ? lds8(base + pl.low + row) : 0x88u;
-        return ((mb & 0xF0u) | (lb >> 4)) | ((((mb & 0x0Fu) << 4) | (lb & 0x0Fu)) << 8);
+    auto fetch = [&](Grp& r, uint32_t fa, uint32_t sa, int grp) {
+#ifdef VCH_T_FIXED
+        fa = base + pl.f; sa = base + pl.sb;
+#endif
+        const uint32_t a = fa + (uint32_t)grp * (8 * D) + lm_off;
+        ldm(r.h, 0, a);
+        ldm(r.h, 4, a + 4 * D);
+#ifndef VCH_T_NOLW
+        ldm(r.l, 0, a + (uint32_t)(pl.lw - pl.f));
+        ldm(r.l, 4, a + (uint32_t)(pl.lw - pl.f) + 4 * D);
+#endif
+        r.s = lds128(sa + grp * 16);
     };
-    // A lean group (no head of this warp reads a nibble plane for any of its 8 tokens): one byte permute per token
-    // (high bytes + the constant low byte 0x80) shared by the heads, one FMA per token and head.
-    auto lean = [&](const VGroup<HPW>& r) {
-        uint32_t k[8];
+    auto consume = [&](const Grp& r) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) k[u] = __byte_perm(r.h[u >> 1], 0x80808080u, (u & 1) ? 0x3424 : 0x1404);
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-#pragma unroll
-            for (int h = 0; h < HPW; ++h) acc[h] = v_fma(k[u], v_dup(u4w(r.s[h], u >> 1), u & 1), acc[h]);
-    };
-    // Any group: as above, but the k~ words of the flagged tokens (bits of `any`) are patched with the low bytes from
-    // the side ring, head by head.  The patch is a short loop over the flagged tokens and exists once: what this path
-    // costs is the instruction-cache lines it touches, so it is kept small.
-    auto mixed = [&](const VGroup<HPW>& r, const uint4& rec, uint32_t sa, int grp, uint32_t any) {
-        uint32_t k[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) k[u] = __byte_perm(r.h[u >> 1], 0x80808080u, (u & 1) ? 0x3424 : 0x1404);
-#pragma unroll
-        for (int h = 0; h < HPW; ++h) {
-            uint32_t kh[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) kh[u] = k[u];
-#pragma unroll 1
-            for (uint32_t bits = any; bits; bits &= bits - 1) {
-                const int u = __ffs(bits) - 1;
-                const uint32_t lw = low_word(rec, sa, grp * 8 + u, h);
-                const uint32_t hp = (u >> 1) == 0 ? r.h[0] : (u >> 1) == 1 ? r.h[1] : (u >> 1) == 2 ? r.h[2] : r.h[3];
-                const uint32_t kk = __byte_perm(hp, lw, (u & 1) ? 0x3524 : 0x1504);
-#pragma unroll
-                for (int v = 0; v < 8; ++v) kh[v] = (v == u) ? kk : kh[v];
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) acc[h] = v_fma(kh[u], v_dup(u4w(r.s[h], u >> 1), u & 1), acc[h]);
+        for (int u = 0; u < 8; ++u) {
+            const __half2 sd = v_dup(u4w(r.s, u >> 1), u & 1);
+#ifdef VCH_T_NOLW
+            accA = v_fma(__byte_perm(r.h[u], 0x80808080u, 0x1404), sd, accA);
+            accB = v_fma(__byte_perm(r.h[u], 0x80808080u, 0x3424), sd, accB);
+#else
+            accA = v_fma(__byte_perm(r.h[u], r.l[u], 0x1504), sd, accA);
+            accB = v_fma(__byte_perm(r.h[u], r.l[u], 0x3726), sd, accB);
+#endif
         }
     };
-    // Tokens [0, u1) of a partial group, token by token from shared memory (the last few tokens of a sequence whose
-    // length is not a multiple of 8).
-    auto per_token = [&](const uint4& rec, uint32_t fa, uint32_t sa, int grp, int u1) {
-#pragma unroll 1
-        for (int u = 0; u < u1; ++u) {
-            const int t = grp * 8 + u;
-            const uint32_t hw = lds16(fa + (uint32_t)t * D + pair * 2);
-#pragma unroll
-            for (int h = 0; h < HPW; ++h) {
-                const uint32_t sb = lds16(sa + h * sb_head + t * 2);
-                acc[h] = hfma2_bits(__byte_perm(hw, low_word(rec, sa, t, h), 0x1504), sb | (sb << 16), acc[h]);
-            }
-        }
-    };
-    // this warp's heads' "reads a nibble plane" bits of the stage in ring slot `slot`: lo = tokens 0..31, hi = 32..63
-    auto masks = [&](int slot, uint32_t& lo, uint32_t& hi) {
-        lo = hi = 0;
-#pragma unroll
-        for (int h = 0; h < HPW; ++h) {
-            const uint2 m = lds64(base + pl.rec + (uint32_t)slot * REC + 16 + (g0 + h) * 8);
-            lo |= m.x;
-            hi |= m.y;
-        }
-    };
-    auto any_of = [](uint32_t lo, uint32_t hi, int grp) { return ((grp < 4 ? lo : hi) >> ((grp & 3) * 8)) & 0xFFu; };
-
-    VGroup<HPW> ra, rb;
-    uint32_t mlo = 0, mhi = 0;
-    long long prof_wait = 0, prof_t0 = clock64(), prof_first = 0;
-    int nslow_full = 0;
-    long long prof_gen = 0;
-    Pos cur = {0, 0u, 0, 0};
-    uint32_t fa = f_addr(cur), sa = s_addr(cur);
+    int slot = 0, sic = 0, buf = 0;                                    // of the current stage: % nf, % sch, chunk % 3
+    uint32_t parity = 0;
+    auto f_addr = [&]() { return base + pl.f + (uint32_t)slot * F_BYTES; };
+    auto s_addr = [&]() { return base + pl.sb + (uint32_t)buf * (sch * TOK * 2) + (uint32_t)sic * (TOK * 2); };
+    Grp ra, rb;
+    uint32_t fa = f_addr(), sa = s_addr();
+    const long long prof_t0 = clock64();
+    long long prof_first = 0, prof_wait = 0;
     if (nst > 0) {
         alive = mbar_wait(bar_full, 0);
         prof_first = clock64() - prof_t0;
-        if (alive) {
-#pragma unroll
-            for (int h = 0; h < HPW; ++h) A[h] = lds32(base + pl.thr + (g0 + h) * 4);
-            if (nsf > 0) {
-                masks(0, mlo, mhi);
-                fetch(ra, fa, sa, 0);
-            }
-        }
+        if (alive && nsf > 0) fetch(ra, fa, sa, 0);
     }
-    // One full stage per iteration; on entry ra holds group 0 of the stage and (mlo, mhi) its masks.
+    // One full stage per iteration, straight-line: groups alternate between ra and rb, the group after next is
+    // fetched while one is consumed; on entry ra holds group 0 of the stage.
 #pragma unroll 1
     for (int left = nsf; left > 0 && alive; --left) {
-        const Pos nxt = next_pos(cur);
-        const uint32_t nfa = f_addr(nxt), nsa = s_addr(nxt);
-        uint32_t nlo = 0, nhi = 0;
-        if (p.dbg & 1) {
-            if (left > 1) {
-                const long long w0 = clock64();
-                alive = mbar_wait(bar_full + nxt.slot * 8, nxt.parity, &nslow_full);
-                prof_wait += clock64() - w0;
-                if (alive) masks(nxt.slot, nlo, nhi);
-            }
-        } else if (__builtin_expect((mlo | mhi) == 0, 1)) {
-            // lean stage: 64 tokens straight-line, no branch but the wait; groups alternate between ra and rb and the
-            // group after next is fetched while one is consumed
+        const int cslot = slot;
+        if (++slot == nf) { slot = 0; parity ^= 1u; }
+        if (++sic == sch) { sic = 0; buf = buf == 2 ? 0 : buf + 1; }
+        const uint32_t nfa = f_addr(), nsa = s_addr();
+        uint32_t landed = 0;
 #pragma unroll
-            for (int ga = 0; ga < 8; ga += 2) {
-                fetch(rb, fa, sa, ga + 1);
-                lean(ra);
-                if (ga < 6) {
-                    fetch(ra, fa, sa, ga + 2);
-                } else if (left > 1) {
-                    // first group of the next stage; it has normally landed long ago (the ring is several stages deep)
+        for (int ga = 0; ga < 8; ga += 2) {
+            fetch(rb, fa, sa, ga + 1);
+            consume(ra);
+            if (ga < 6) {
+                fetch(ra, fa, sa, ga + 2);
+                // the next stage has normally landed long ago (the ring is several stages deep): probe its barrier two
+                // groups before the answer is needed, so that the probe's latency is hidden
+                if (ga == 2 && left > 1) landed = mbar_test(bar_full + slot * 8, parity);
+            } else if (left > 1) {
+                if (__builtin_expect(!landed, 0)) {
                     const long long w0 = clock64();
-                    alive = mbar_wait(bar_full + nxt.slot * 8, nxt.parity, &nslow_full);
+                    alive = mbar_wait(bar_full + slot * 8, parity);
                     prof_wait += clock64() - w0;
-                    if (alive) {
-                        masks(nxt.slot, nlo, nhi);
-                        fetch(ra, nfa, nsa, 0);
-                    }
                 }
-                lean(rb);
+                if (alive) fetch(ra, nfa, nsa, 0);      // first group of the next stage
             }
-        } else {
-            // a stage in which some token reads a nibble plane: one group per iteration through one copy of compact code
-            const long long g0c = clock64();
-            const uint4 rec = lds128(base + pl.rec + (uint32_t)cur.slot * REC);   // {first side row, union lo, hi, rows}
-#pragma unroll 1
-            for (int grp = 0; grp < 8; ++grp) {
-                if (grp > 0) fetch(ra, fa, sa, grp);
-                mixed(ra, rec, sa, grp, any_of(mlo, mhi, grp));
-            }
-            if (left > 1) {
-                alive = mbar_wait(bar_full + nxt.slot * 8, nxt.parity, &nslow_full);
-                if (alive) {
-                    masks(nxt.slot, nlo, nhi);
-                    fetch(ra, nfa, nsa, 0);
-                }
-            }
-            prof_gen += clock64() - g0c;
+            consume(rb);
         }
+        // the stage is consumed: hand back its ring slot
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_free + cur.slot * 8);           // ring slot, side rows and record are free
-        cur = nxt; fa = nfa; sa = nsa; mlo = nlo; mhi = nhi;
+        if (lane == 0) mbar_arrive(bar_free + cslot * 8);
+        fa = nfa; sa = nsa;
     }
     const int tail = n - nsf * TOK;
     if (tail > 0 && alive) {
-        // last, partial stage (rows of the slot beyond the last token hold stale bytes that are never used)
-        if (nsf > 0) alive = mbar_wait(bar_full + cur.slot * 8, cur.parity);
+        // last, partial stage, token by token (rows of the slot beyond the last token hold stale bytes, never used)
+        if (nsf > 0) alive = mbar_wait(bar_full + slot * 8, parity);
         if (alive) {
-            masks(cur.slot, mlo, mhi);
-            const uint4 rec = lds128(base + pl.rec + (uint32_t)cur.slot * REC);
-            for (int grp = 0; grp * 8 < tail; ++grp) {
-                const int u1 = tail - grp * 8 < 8 ? tail - grp * 8 : 8;
-                if (u1 == 8) {
-                    fetch(ra, fa, sa, grp);
-                    mixed(ra, rec, sa, grp, any_of(mlo, mhi, grp));
-                } else {
-                    per_token(rec, fa, sa, grp, u1);
-                }
+            const uint32_t la = fa + (uint32_t)(pl.lw - pl.f);
+#pragma unroll 1
+            for (int t = 0; t < tail; ++t) {
+                const uint32_t hw = lds16(fa + (uint32_t)t * D + pairA * 2) | (lds16(fa + (uint32_t)t * D + pairB * 2) << 16);
+                const uint32_t lw = lds16(la + (uint32_t)t * D + pairA * 2) | (lds16(la + (uint32_t)t * D + pairB * 2) << 16);
+                const uint32_t sb = lds16(sa + t * 2);
+                accA = hfma2_bits(__byte_perm(hw, lw, 0x1504), sb | (sb << 16), accA);
+                accB = hfma2_bits(__byte_perm(hw, lw, 0x3726), sb | (sb << 16), accB);
             }
         }
     }
-    if (p.prof && lane == 0) {
-        const long long t1 = clock64();
-        p.prof[bh * 16 + warp] = t1 - prof_t0;
-        p.prof[bh * 16 + 4 + warp] = prof_wait;
-        if (warp == 0) { p.prof[bh * 16 + 14] = nslow_full; p.prof[bh * 16 + 7] = prof_gen; }
-        if (warp == 0) { p.prof[bh * 16 + 2] = prof_first; }
-    }
-#pragma unroll
-    for (int h = 0; h < HPW; ++h)
-        reinterpret_cast<uint32_t*>(p.o)[((size_t)bh * G + g0 + h) * 64 + pair] = alive ? acc[h] : 0x7E007E00u;
+    if (p.prof && lane == 0) { p.prof[bh * 4] = clock64() - prof_t0; p.prof[bh * 4 + 1] = prof_first; p.prof[bh * 4 + 2] = prof_wait; }
+    uint32_t* o = reinterpret_cast<uint32_t*>(p.o) + (size_t)bh * 64;
+    o[pairA] = alive ? accA : 0x7E007E00u;
+    o[pairB] = alive ? accB : 0x7E007E00u;
 }
 
 }  // namespace akv

@@ -473,25 +473,20 @@ static int launch_v_fast(const VParams& p, int BH, cudaStream_t st) {
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
 }
 
-// ---- launch of the streaming form (v_chain_kernel)
-// Ring sizes follow from how many CTAs have to share an SM so that the whole grid is resident at once (the kernel is a
-// pure stream: a second wave would start with cold rings): shared memory per CTA = SM capacity / CTAs per SM, of which
-// the probability buffers and the side ring take a fixed part and the high-byte ring the rest.
+// ---- launch of the branch-free streaming form for multi-head attention (v_chain_kernel)
+// Ring sizes follow from how many units ((batch, head) pairs) have to share an SM so that the whole grid is resident
+// at once (the kernel is a pure stream: a second wave would start with cold rings): shared memory per unit = SM
+// capacity / units per SM, of which the probability buffers and the side ring take a fixed part and the two rings
+// (high bytes, low-byte table: 16 KB per stage) the rest.
 struct VChainCfg {
-    int hpw, upc, nf, nside, sch, smem;
+    int upc, nf, nside, sch, smem;
 };
-static VChainCfg v_chain_config(int BH, int G, int reference) {
+static VChainCfg v_chain_config(int BH, int reference) {
     const Tuning& t = tuning();
     const int sms = sm_count();
     VChainCfg c;
-    // heads per chain warp: all of the group when there are CTAs enough to fill every scheduler, else spread the
-    // group's heads over more warps so that a warp's issue slots do not bound the chain
-    c.hpw = G;
-    if (G >= 4 && BH < 2 * sms) c.hpw = 2;
-    if (G == 8 && c.hpw == 8) c.hpw = 4;
-    if (t.v_hpw > 0 && G % t.v_hpw == 0 && 2 * G / t.v_hpw <= 8) c.hpw = t.v_hpw;
-    // units per CTA: two when a unit has four warps, so that the CTA's eight warps put one chain warp on each scheduler
-    c.upc = (2 * G / c.hpw == 2 && BH >= 2) ? 2 : 1;
+    // two units per CTA: its six warps then put the chain and decision warps on four different schedulers
+    c.upc = BH >= 2 ? 2 : 1;
     if (t.v_upc > 0) c.upc = t.v_upc;
     const int ctas = (BH + c.upc - 1) / c.upc;
     int cps = (ctas + sms - 1) / sms;                      // CTAs per SM for a single wave
@@ -500,56 +495,41 @@ static VChainCfg v_chain_config(int BH, int G, int reference) {
     if (t.v_cps > 0) cps = t.v_cps;
     // shared memory of one unit (1 KB per CTA is reserved by the system)
     const int budget = ((max_dyn_smem() + 1024) / cps - 1024) / c.upc - 256;
-    const int ups = cps * c.upc;                           // units per SM
-    c.nside = reference ? 256 : 128;
+    c.nside = reference ? 256 : 128;                       // (each decision warp owns half: at least a stage's 64 rows)
     c.sch = 16;
-    if (ups >= 3) { c.nside = 64; c.sch = G >= 4 ? 8 : 16; }
-    if (t.v_nside > 0) c.nside = t.v_nside;
-    const int fixed = vch::plan(G, 0, c.nside, c.sch).bytes + 64;
-    int nf = (budget - fixed) / (vch::F_BYTES + vch::rec_bytes(G) + 16);
-    if (nf > c.sch) nf = c.sch;                            // the probability buffers cover three chunks of sch stages
-    if (nf > 16) nf = 16;
+    if (t.v_nside >= 128) c.nside = t.v_nside;
+    const int fixed = vch::plan(0, c.nside, c.sch).bytes + 64;
+    int nf = (budget - fixed) / (2 * vch::F_BYTES + 2 * vch::REC + 32);
+    if (nf > c.sch / 2) nf = c.sch / 2;                    // the decision warp runs a ring ahead: 2 nf stages <= a chunk
     if (t.v_nf > 0 && t.v_nf < nf) nf = t.v_nf;
+    nf &= ~1;                                              // even: a ring slot's stages all belong to one decision warp
     if (nf < 2) nf = 2;
     c.nf = nf;
-    c.smem = c.upc * ((vch::plan(G, c.nf, c.nside, c.sch).bytes + 127) & ~127);
+    c.smem = c.upc * ((vch::plan(c.nf, c.nside, c.sch).bytes + 127) & ~127);
     return c;
 }
 
-template <int G, int HPW, int UPC, int GPI>
-static int launch_v_chain_g(VParams& p, const VChainCfg& c, int BH, cudaStream_t st) {
-    static bool configured[64] = {false};   // the attribute is per device
+template <int UPC>
+static int launch_v_chain_u(VParams& p, const VChainCfg& c, int BH, cudaStream_t st) {
+    static bool configured[64] = {false};   // the attribute is per device (one array per instantiation)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(v_chain_kernel<G, HPW, UPC, GPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(v_chain_kernel<UPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              max_dyn_smem());
         if (e != cudaSuccess) return cuda_status(e, "v_cache_compute smem attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     AKV_REQUIRE(c.smem <= max_dyn_smem(), AKV_ERR_CUDA, "v_cache_compute: %d bytes of shared memory are too many", c.smem);
     p.nf = c.nf; p.nside = c.nside; p.sch = c.sch; p.units = BH;
-    launch_chained(v_chain_kernel<G, HPW, UPC, GPI>, dim3((BH + UPC - 1) / UPC), dim3(UPC * 32 * (2 * G / HPW + 2)),
-                   (size_t)c.smem, st, p);
+    launch_chained(v_chain_kernel<UPC>, dim3((BH + UPC - 1) / UPC), dim3(UPC * 128), (size_t)c.smem, st, p);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
-}
-template <int G, int HPW, int UPC>
-static int launch_v_chain_u(VParams& p, const VChainCfg& c, int BH, cudaStream_t st) {
-    const int gpi = tuning().v_gpi;
-    if (gpi == 2) return launch_v_chain_g<G, HPW, UPC, 2>(p, c, BH, st);
-    if (gpi == 8 && G == 1) return launch_v_chain_g<G, HPW, UPC, (G == 1 ? 8 : 4)>(p, c, BH, st);
-    return launch_v_chain_g<G, HPW, UPC, 4>(p, c, BH, st);
-}
-template <int G, int HPW>
-static int launch_v_chain(VParams& p, const VChainCfg& c, int BH, cudaStream_t st) {
-    if (2 * G / HPW == 2 && c.upc == 2) return launch_v_chain_u<G, HPW, (2 * G / HPW == 2 ? 2 : 1)>(p, c, BH, st);
-    return launch_v_chain_u<G, HPW, 1>(p, c, BH, st);
 }
 
 // true when launch_v_compute_probe runs the streaming kernel, which can compute the threshold bytes itself
 bool v_compute_takes_probe(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
                            const uint8_t* o, int group, int D, int s_last_dim, int n) {
-    return D == 128 && (group == 1 || group == 2 || group == 4 || (group == 8 && tuning().v_impl == 0)) &&
+    return D == 128 && (group == 1 || group == 2 || group == 4) &&
            aligned16(first8) && aligned16(mid4) &&
            aligned16(last4) && (n == 0 || (aligned16(s) && s_last_dim % 8 == 0 && ((n + 7) & ~7) <= s_last_dim)) &&
            ((reinterpret_cast<uintptr_t>(o) & 3u) == 0);
@@ -572,25 +552,12 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
     p.group = group;
     p.nf = p.nside = p.sch = p.units = 0;
     p.prof = g_v_prof_host;
-    p.dbg = tuning().v_dbg;
     const int BH = bsz * H;
     const bool fast = v_compute_takes_probe(first8, mid4, last4, s, o, group, D, s_last_dim, n);
     AKV_REQUIRE(fast || !test_o, AKV_ERR_SHAPE, "v_cache_compute: the probe form needs the streaming kernel");
-    if (fast && tuning().v_impl == 0) {
-        const VChainCfg c = v_chain_config(BH, group, reference);
-        switch (group * 10 + c.hpw) {
-            case 11: return launch_v_chain<1, 1>(p, c, BH, st);
-            case 21: return launch_v_chain<2, 1>(p, c, BH, st);
-            case 22: return launch_v_chain<2, 2>(p, c, BH, st);
-            case 41: return launch_v_chain<4, 1>(p, c, BH, st);
-            case 42: return launch_v_chain<4, 2>(p, c, BH, st);
-            case 44: return launch_v_chain<4, 4>(p, c, BH, st);
-            case 82: return launch_v_chain<8, 2>(p, c, BH, st);
-            case 84: return launch_v_chain<8, 4>(p, c, BH, st);
-            default:
-                set_error("v_cache_compute: no kernel for group %d with %d heads per warp", group, c.hpw);
-                return AKV_ERR_SHAPE;
-        }
+    if (fast && group == 1 && !reference && tuning().v_impl == 0) {
+        const VChainCfg c = v_chain_config(BH, reference);
+        return c.upc == 2 ? launch_v_chain_u<2>(p, c, BH, st) : launch_v_chain_u<1>(p, c, BH, st);
     }
     if (fast && group == 1) return launch_v_fast<1, 6, 2, 1>(p, BH, st);
     if (fast && group == 2) return launch_v_fast<2, 6, 2, 2>(p, BH, st);

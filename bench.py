@@ -391,13 +391,14 @@ def measure(name, args, ctx, min_seconds=0.5):
     for _ in range(min(2 * args.steps, 200)):
         step_resident()
     clocks = sampler.stop(t0, time.time()) if sampler else None
-    kern = layer.kernel_times()                            # median per-kernel CUDA-event durations of that pass
+    kern_in_step = layer.kernel_times()                    # median per-kernel CUDA-event brackets of that pass
     e2e_blocks, _, _, _ = timed_blocks(step_e2e, args.steps, warm, min_seconds / 2)
     ms_e2e = statistics.median(e2e_blocks)
 
     # algorithmic bytes under this step's read decisions, summed over the ranks
     out_last = step_resident()
     torch.cuda.synchronize()
+    kern = kernel_loop_times(layer, q, v_mode) or kern_in_step
     acct = layer.bytes_accounting(q)
     keys = ("k_compute", "v_compute", "read", "dense")
     tot = torch.tensor([acct[k_] for k_ in keys], device=dev, dtype=torch.float64)
@@ -446,8 +447,11 @@ def measure(name, args, ctx, min_seconds=0.5):
     dom = max(kern, key=lambda n: kern[n]["us"]) if kern else None
     roofline = roofline_of(dom) if dom else None
     if roofline:
-        roofline["timing"] = ("median of CUDA-event brackets around the kernel in a second pass of the same steps (the "
-                              "brackets cost ~10 us per step and are kept out of the headline pass)")
+        roofline["timing"] = ("average duration of %d back-to-back launches of the kernel on the state of the timed step "
+                              "(same planes, alignment inputs, probabilities, thresholds), between two CUDA events on "
+                              "the launching stream, after 3 warm-up launches; the planes one launch streams are larger "
+                              "than L2.  A bracket of events around a single launch inside the step adds the launch "
+                              "latency after the first event (kernels_us_in_step_event_brackets)" % KERNEL_LOOP_LAUNCHES)
         roofline["other_kernel"] = roofline_of("k_compute" if dom == "v_compute" else "v_compute")
     cfg = config_dict(name, world, v_mode)
     if isinstance(seq, DecisionExactShardedDecoder):
@@ -467,6 +471,7 @@ def measure(name, args, ctx, min_seconds=0.5):
         "achieved_hbm_gbs": total["read"] / (ms_step * 1e-3) / 1e9,
         "bytes_read_over_dense": total["read"] / total["dense"],
         "kernels_us": {n: round(kv_["us"], 2) for n, kv_ in kern.items()},
+        "kernels_us_in_step_event_brackets": {n: round(kv_["us"], 2) for n, kv_ in kern_in_step.items()},
         "roofline": roofline,
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int((q.numel() + k_tok.numel() + v_tok.numel()) * 2),
@@ -477,6 +482,60 @@ def measure(name, args, ctx, min_seconds=0.5):
         "validation": {"device_error_flag": check["device_error_flag"], "note": check["note"]},
         "ref_cuda_kernels_us": check["ref_cuda_kernels_us"],
     }
+
+
+KERNEL_LOOP_LAUNCHES = 20
+
+
+def kernel_loop_times(layer, q, v_mode):
+    """Average launch duration of the two streaming kernels: KERNEL_LOOP_LAUNCHES back-to-back launches of each, through
+    the operator entry points of the C ABI, on the state the last step left behind (the step's own planes, alignment
+    inputs, probabilities and threshold bytes), between two CUDA events.  None when the state has residual tokens."""
+    import math
+    import torch
+    from alignedkv_b200 import _lib
+    B, H, Hq, G, D = layer.B, layer.H, layer.Hq, layer.G, layer.D
+    qn = layer.rest_start
+    if layer.rest_len != 0 or qn == 0:
+        return None
+    dev = q.device
+    lib = layer.lib
+    R = (qn // 64 + 1) * 64
+    nmb = layer.k_first_8.shape[2]
+    st = torch.cuda.current_stream(dev).cuda_stream
+    off = {n: layer._scratch_offset(n) for n in ("kq", "kqmax", "amin")}
+    p_ptr = layer.scratch.data_ptr()                       # probabilities: rows of R halves
+    s_tmp = torch.empty(B * Hq * R, dtype=torch.half, device=dev)
+    o_tmp = torch.empty(B * Hq * D, dtype=torch.half, device=dev)
+    flags = (2 if v_mode == "order_free" else 0) | (1 if layer.reference else 0)
+    nbytes = int(lib.akv_v_cache_compute_scratch_bytes(B, H, G, qn))
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+    base = layer.scratch.data_ptr()
+
+    def launch_k():
+        _lib.check("k_cache_compute", lib.akv_k_cache_compute_gqa(
+            layer.k_first_8.data_ptr(), layer.k_mid_4.data_ptr(), layer.k_last_4.data_ptr(), base + off["kq"],
+            base + off["kqmax"], q.data_ptr(), s_tmp.data_ptr(), B, H, G, qn // 64, nmb, D, 64, 1, 1.0 / math.sqrt(D),
+            1 if layer.reference else 0, st))
+
+    def launch_v():
+        _lib.check("v_cache_compute", lib.akv_v_cache_compute_gqa(
+            layer.v_first_8.data_ptr(), layer.v_mid_4.data_ptr(), layer.v_last_4.data_ptr(), p_ptr, base + off["amin"],
+            o_tmp.data_ptr(), ws.data_ptr(), ws.numel(), B, H, G, layer.L, D, R, qn, flags, st))
+
+    res = {}
+    for name, fn in (("k_compute", launch_k), ("v_compute", launch_v)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(KERNEL_LOOP_LAUNCHES):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        res[name] = {"us": e0.elapsed_time(e1) * 1e3 / KERNEL_LOOP_LAUNCHES, "launches": KERNEL_LOOP_LAUNCHES}
+    return res
 
 
 def validate(layer, q, k, v, out_last, G, v_mode, sharded_sequence, want_ref_timing):
