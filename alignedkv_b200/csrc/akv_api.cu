@@ -93,13 +93,10 @@ int akv_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "k_wpc") && value >= 0 && value <= 16) t.k_wpc = value;
     else if (!strcmp(key, "v_impl") && (value == 0 || value == 1)) t.v_impl = value;
     else if (!strcmp(key, "v_nf") && value >= 0 && value <= 16) t.v_nf = value;
-    else if (!strcmp(key, "v_nside") && (value == 0 || value == 64 || value == 128 || value == 256 || value == 512))
+    else if (!strcmp(key, "v_nside") && (value == 0 || value == 128 || value == 256 || value == 512))
         t.v_nside = value;
     else if (!strcmp(key, "v_cps") && value >= 0 && value <= 8) t.v_cps = value;
-    else if (!strcmp(key, "v_dbg")) t.v_dbg = value;
-    else if (!strcmp(key, "v_gpi") && (value == 2 || value == 4 || value == 8)) t.v_gpi = value;
     else if (!strcmp(key, "v_upc") && value >= 0 && value <= 2) t.v_upc = value;
-    else if (!strcmp(key, "v_hpw") && value >= 0 && value <= 8) t.v_hpw = value;
     else {
         set_error("set_tuning: unknown key or value out of range (%s = %d)", key, value);
         return AKV_ERR_SHAPE;

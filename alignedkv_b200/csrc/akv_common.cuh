@@ -23,14 +23,11 @@ struct Tuning {
     int k_wpc = 0;      // cap on warps per CTA of the q.K^T kernel (0 = as many as shared memory allows)
     int pdl = 1;        // 1: the kernels of a decode step are chained with programmatic dependent launch
     int k_gqa_kch = 8;  // channels per stage of the q.K^T kernel when query heads share KV heads (8 or 16)
-    int v_impl = 0;     // exact P.V kernel: 0 = chain warps read the landed stage with ldmatrix, 1 = producer-transposed form
-    int v_nf = 0;       // exact P.V: ring depth in 64-token stages (0 = from the shared-memory budget)
-    int v_nside = 0;    // exact P.V: rows of the nibble side ring, a power of two >= 64 (0 = default)
-    int v_cps = 0;      // exact P.V: CTAs per SM the shared-memory budget is cut for (0 = one wave)
-    int v_dbg = 0;
-    int v_gpi = 4;      // exact P.V: 8-token groups per iteration of the chain loop (2, 4, or 8 with one head)
-    int v_upc = 0;      // exact P.V: (batch, KV head) units per CTA, 1 or 2 (0 = default)
-    int v_hpw = 0;      // exact P.V: query heads per chain warp (0 = default)
+    int v_impl = 0;     // exact P.V, multi-head, aligned mode: 0 = branch-free chain form, 1 = producer-transposed form
+    int v_nf = 0;       // exact P.V (form 0): cap on the ring depth in 64-token stages (0 = from the shared-memory budget)
+    int v_nside = 0;    // exact P.V (form 0): rows of the nibble side ring, a power of two >= 128 (0 = default)
+    int v_cps = 0;      // exact P.V (form 0): CTAs per SM the shared-memory budget is cut for (0 = one wave)
+    int v_upc = 0;      // exact P.V (form 0): (batch, head) units per CTA, 1 or 2 (0 = default)
 };
 Tuning& tuning();
 

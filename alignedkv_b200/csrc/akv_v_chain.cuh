@@ -53,9 +53,7 @@ struct VParams {
     int group;              // query heads per KV head (1 = multi-head attention)
     int nf, nside, sch;     // streaming form: ring depth (stages), side-ring rows (power of two), stages per chunk
     int units;              // streaming form: number of (batch, KV head) units
-    unsigned long long* prof;   // DEBUG
 };
-static unsigned long long* g_v_prof_host = nullptr;   // DEBUG
 
 // ---- device error flag and shared-memory barriers (mbarrier) with bounded waits
 static __device__ unsigned int g_v_wait_gave_up = 0;   // set when a bounded wait ran out (never expected)
@@ -457,29 +455,19 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
                      : "=r"(r[o]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]) : "r"(a));
     };
     auto fetch = [&](Grp& r, uint32_t fa, uint32_t sa, int grp) {
-#ifdef VCH_T_FIXED
-        fa = base + pl.f; sa = base + pl.sb;
-#endif
         const uint32_t a = fa + (uint32_t)grp * (8 * D) + lm_off;
         ldm(r.h, 0, a);
         ldm(r.h, 4, a + 4 * D);
-#ifndef VCH_T_NOLW
         ldm(r.l, 0, a + (uint32_t)(pl.lw - pl.f));
         ldm(r.l, 4, a + (uint32_t)(pl.lw - pl.f) + 4 * D);
-#endif
         r.s = lds128(sa + grp * 16);
     };
     auto consume = [&](const Grp& r) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const __half2 sd = v_dup(u4w(r.s, u >> 1), u & 1);
-#ifdef VCH_T_NOLW
-            accA = v_fma(__byte_perm(r.h[u], 0x80808080u, 0x1404), sd, accA);
-            accB = v_fma(__byte_perm(r.h[u], 0x80808080u, 0x3424), sd, accB);
-#else
             accA = v_fma(__byte_perm(r.h[u], r.l[u], 0x1504), sd, accA);
             accB = v_fma(__byte_perm(r.h[u], r.l[u], 0x3726), sd, accB);
-#endif
         }
     };
     int slot = 0, sic = 0, buf = 0;                                    // of the current stage: % nf, % sch, chunk % 3
@@ -488,11 +476,8 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
     auto s_addr = [&]() { return base + pl.sb + (uint32_t)buf * (sch * TOK * 2) + (uint32_t)sic * (TOK * 2); };
     Grp ra, rb;
     uint32_t fa = f_addr(), sa = s_addr();
-    const long long prof_t0 = clock64();
-    long long prof_first = 0, prof_wait = 0;
     if (nst > 0) {
         alive = mbar_wait(bar_full, 0);
-        prof_first = clock64() - prof_t0;
         if (alive && nsf > 0) fetch(ra, fa, sa, 0);
     }
     // One full stage per iteration, straight-line: groups alternate between ra and rb, the group after next is
@@ -514,11 +499,7 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
                 // groups before the answer is needed, so that the probe's latency is hidden
                 if (ga == 2 && left > 1) landed = mbar_test(bar_full + slot * 8, parity);
             } else if (left > 1) {
-                if (__builtin_expect(!landed, 0)) {
-                    const long long w0 = clock64();
-                    alive = mbar_wait(bar_full + slot * 8, parity);
-                    prof_wait += clock64() - w0;
-                }
+                if (__builtin_expect(!landed, 0)) alive = mbar_wait(bar_full + slot * 8, parity);
                 if (alive) fetch(ra, nfa, nsa, 0);      // first group of the next stage
             }
             consume(rb);
@@ -544,7 +525,6 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
             }
         }
     }
-    if (p.prof && lane == 0) { p.prof[bh * 4] = clock64() - prof_t0; p.prof[bh * 4 + 1] = prof_first; p.prof[bh * 4 + 2] = prof_wait; }
     uint32_t* o = reinterpret_cast<uint32_t*>(p.o) + (size_t)bh * 64;
     o[pairA] = alive ? accA : 0x7E007E00u;
     o[pairB] = alive ? accB : 0x7E007E00u;

@@ -551,7 +551,6 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
     p.max_seq_len = max_seq_len; p.D = D; p.s_last_dim = s_last_dim; p.n = n; p.reference = reference;
     p.group = group;
     p.nf = p.nside = p.sch = p.units = 0;
-    p.prof = g_v_prof_host;
     const int BH = bsz * H;
     const bool fast = v_compute_takes_probe(first8, mid4, last4, s, o, group, D, s_last_dim, n);
     AKV_REQUIRE(fast || !test_o, AKV_ERR_SHAPE, "v_cache_compute: the probe form needs the streaming kernel");
@@ -626,8 +625,6 @@ int launch_v_probe(const uint8_t* first8, const uint8_t* s_val, const uint8_t* s
 }
 
 }  // namespace akv
-
-extern "C" void akv_debug_v_prof(void* ptr) { akv::g_v_prof_host = (unsigned long long*)ptr; }
 
 extern "C" int akv_device_error_flag(void) {
     // Non-zero once a bounded wait inside a kernel of this library gave up (never expected; the kernel then

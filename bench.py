@@ -69,6 +69,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--min-seconds", type=float, default=0.5,
+                    help="timed blocks of --steps steps repeat until this much device time (0: three blocks; profiling runs)")
     ap.add_argument("--no-other-workloads", action="store_true",
                     help="default workload only: do not also measure the grouped-query and long-context workloads")
     ap.add_argument("--workload", default="llama2-7b-layer-decode", choices=sorted(WORKLOADS))
@@ -258,7 +260,7 @@ def reference_kernels():
     return mod
 
 
-def measure(name, args, ctx, min_seconds=0.5):
+def measure(name, args, ctx, min_seconds):
     """One workload on this job's ranks: returns the dict of everything measured (rank 0; None on the others)."""
     import torch
     import torch.distributed as dist
@@ -652,7 +654,7 @@ def run_ours(args):
     from alignedkv_b200 import _lib
     _lib.load()
     ctx = dict(rank=rank, world=world, local=local, dev=dev)
-    line = measure(args.workload, args, ctx)
+    line = measure(args.workload, args, ctx, args.min_seconds)
     others = {}
     if args.workload == "llama2-7b-layer-decode" and not args.no_other_workloads:
         # the other configurations the metric is asked for, at the same number of GPUs: the grouped-query batch (batch
@@ -660,7 +662,7 @@ def run_ours(args):
         # log-sum-exp merge per step)
         for name in OTHER_WORKLOADS:
             torch.cuda.empty_cache()
-            r = measure(name, args, ctx, min_seconds=0.25)
+            r = measure(name, args, ctx, args.min_seconds / 2)
             if r is not None:
                 others[name] = {k_: r[k_] for k_ in ("value", "unit", "ms_per_step", "scaling", "config", "kernels_us",
                                                      "roofline", "e2e", "bytes_read_over_dense", "accuracy", "timing",
