@@ -185,6 +185,38 @@ __device__ __forceinline__ float masked_score(const uint16_t* __restrict__ row, 
     if (mrow) s = __hadd(s, mrow[t]);
     return __half2float(s);
 }
+// Scores of the residual tokens of one (batch, query head) row, by a CTA of 256 threads: thread = (token tid / 4,
+// quarter tid % 4 of the channels in 16-byte pieces), all loads of a row in flight at once, fp32 dot product rounded to
+// fp16, then divided by sqrt(D) and rounded again, which is what `matmul(q, restk^T) / sqrt(D)` on fp16 tensors
+// produces (k_cache_file.py:156-157).  Only tokens with t_lo <= qn + r < t_hi are written (a row split across CTAs).
+__device__ __forceinline__ void residual_scores(uint16_t* __restrict__ row, const __half* __restrict__ qr,
+                                                const __half* __restrict__ restk, int b, int h, int H, int D, int qn,
+                                                int rest, float sqrt_d, int t_lo, int t_hi) {
+    const int tid = threadIdx.x;
+    for (int r0 = 0; r0 < rest; r0 += 64) {       // (the residual buffer holds at most 64 tokens: one round)
+        const int r = r0 + (tid >> 2), c = tid & 3;
+        const bool mine = r < rest && qn + r >= t_lo && qn + r < t_hi;
+        float acc = 0.f;
+        if (mine) {
+            const __half* kr = restk + (((size_t)b * BLK + r) * H + h) * D;
+            for (int d = c * 8; d < D; d += 32) {
+                const uint4 kv = *reinterpret_cast<const uint4*>(kr + d), qv = *reinterpret_cast<const uint4*>(qr + d);
+                const __half2* k2 = reinterpret_cast<const __half2*>(&kv);
+                const __half2* q2 = reinterpret_cast<const __half2*>(&qv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 kf = __half22float2(k2[i]), qf = __half22float2(q2[i]);
+                    acc = fmaf(qf.x, kf.x, acc);
+                    acc = fmaf(qf.y, kf.y, acc);
+                }
+            }
+        }
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
+        if (mine && c == 0) row[qn + r] = __half_as_ushort(__float2half_rn(__half2float(__float2half_rn(acc)) / sqrt_d));
+    }
+}
+
 template <bool CACHED, bool PROBE>
 __global__ void __launch_bounds__(256)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
@@ -200,17 +232,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     uint16_t* row = s + (size_t)bhq * R;
     const __half* mrow = mask ? mask + (size_t)b * mask_stride : nullptr;
     const int len = qn + rest;
-    // residual tokens: fp32 dot product rounded to fp16, then divided by sqrt(D) and rounded again, which is
-    // what `matmul(q, restk^T) / sqrt(D)` on fp16 tensors produces (k_cache_file.py:156-157)
-    for (int r = warp; r < rest; r += 8) {
-        const __half* kr = restk + (((size_t)b * BLK + r) * H + h) * D;
-        const __half* qr = q + (size_t)bhq * D;
-        float acc = 0.f;
-        for (int d = lane; d < D; d += 32) acc += __half2float(qr[d]) * __half2float(kr[d]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-        if (lane == 0) row[qn + r] = __half_as_ushort(__float2half_rn(__half2float(__float2half_rn(acc)) / sqrt_d));
-    }
+    residual_scores(row, q + (size_t)bhq * D, restk, b, h, H, D, qn, rest, sqrt_d, 0, len);
     __syncthreads();
     float x[CACHED ? SM_REGS : 1];
     // pass 1: maximum
@@ -344,17 +366,8 @@ softmax_chunk_stats_kernel(uint16_t* __restrict__ s, const __half* __restrict__ 
     const __half* mrow = mask ? mask + (size_t)b * mask_stride : nullptr;
     const int len = qn + rest;
     const int t0 = ch * SM_CHUNK, t1 = min(len, t0 + SM_CHUNK);
-    // residual-token scores (k_cache_file.py:156-157) by the chunk(s) that hold them
-    for (int r = warp; r < rest; r += 8) {
-        if (qn + r < t0 || qn + r >= t1) continue;
-        const __half* kr = restk + (((size_t)b * BLK + r) * H + h) * D;
-        const __half* qr = q + (size_t)bhq * D;
-        float acc = 0.f;
-        for (int d = lane; d < D; d += 32) acc += __half2float(qr[d]) * __half2float(kr[d]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-        if (lane == 0) row[qn + r] = __half_as_ushort(__float2half_rn(__half2float(__float2half_rn(acc)) / sqrt_d));
-    }
+    // residual-token scores by the chunk(s) that hold them
+    residual_scores(row, q + (size_t)bhq * D, restk, b, h, H, D, qn, rest, sqrt_d, t0, t1);
     __syncthreads();
     float m = -INFINITY;
     for (int t = t0 + tid; t < t1; t += 256) m = fmaxf(m, masked_score(row, mrow, t));
@@ -495,11 +508,39 @@ tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_mai
             float* __restrict__ packed, int H, int G, int D, int R, int qn, int rest) {
     pdl_enter();
     const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
+    // residual sum: item = (channel pair, quarter g of the tokens: r = g, g+4, ...), all of an item's loads in flight
+    // at once; the four partial sums of a channel are added in order g = 0..3
+    __shared__ float part[4][1024];
+    const int hd = D >> 1;
+    if (rest > 0) {
+        const uint16_t* pr = p + (size_t)bhq * R + qn;
+        const size_t vs = (size_t)H * D;
+        for (int i = threadIdx.x; i < 4 * hd; i += blockDim.x) {
+            const int g = i / hd, c = i - g * hd;
+            const __half* vr = restv + ((size_t)b * BLK * H + h) * D + 2 * c;
+            float pv[16];
+            __half2 vv[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int r = g + 4 * j;
+                const bool on = r < rest;
+                pv[j] = on ? __half2float(__ushort_as_half(pr[r])) : 0.f;
+                vv[j] = on ? *reinterpret_cast<const __half2*>(vr + (size_t)r * vs) : __half2(__half(0.f), __half(0.f));
+            }
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float2 f = __half22float2(vv[j]);
+                a0 = fmaf(pv[j], f.x, a0);
+                a1 = fmaf(pv[j], f.y, a1);
+            }
+            part[g][2 * c] = a0;
+            part[g][2 * c + 1] = a1;
+        }
+        __syncthreads();
+    }
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.f;
-        for (int r = 0; r < rest; ++r)
-            acc += __half2float(__ushort_as_half(p[(size_t)bhq * R + qn + r])) *
-                   __half2float(restv[(((size_t)b * BLK + r) * H + h) * D + d]);
+        const float acc = rest > 0 ? ((part[0][d] + part[1][d]) + part[2][d]) + part[3][d] : 0.f;
         float v;
         if (o_main32) v = o_main32[(size_t)bhq * D + d] + acc;
         else v = (o_main ? __half2float(__ushort_as_half(o_main[(size_t)bhq * D + d])) : 0.f) +
@@ -803,7 +844,7 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
         if (rc != AKV_OK) return rc;
     }
     if (need_tail) {
-        launch_chained(tail_kernel, dim3(B * H * G), dim3(D < 256 ? ((D + 31) / 32) * 32 : 256), 0, st,
+        launch_chained(tail_kernel, dim3(B * H * G), dim3(256), 0, st,
                        (const uint16_t*)((qn > 0 && !order_free) ? sc.o_main : nullptr),
                        (const float*)(order_free ? sc.o_main32 : nullptr), (const uint16_t*)sc.s,
                        static_cast<const __half*>(restv), static_cast<__half*>(out), (const float*)sc.stats,
@@ -944,7 +985,7 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
     }
     if (slot4) cudaEventRecord(slot4[3], st);
     g_shard_timing = nullptr;
-    launch_chained(tail_kernel, dim3(rows), dim3(128), 0, st, (const uint16_t*)nullptr, (const float*)sc.o_main32,
+    launch_chained(tail_kernel, dim3(rows), dim3(256), 0, st, (const uint16_t*)nullptr, (const float*)sc.o_main32,
                    (const uint16_t*)sc.s, static_cast<const __half*>(restv), static_cast<__half*>(nullptr),
                    (const float*)sc.stats, static_cast<float*>(exch_out), H, G, D, R, qn, rest);
     return cuda_status(cudaGetLastError(), "shard_step tail launch");

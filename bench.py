@@ -64,7 +64,7 @@ UNIT = "tokens/s"
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seed", type=int, default=0)
@@ -86,6 +86,7 @@ def parse():
 
 
 # ---------------------------------------------------------------------------------------------- shared by both arms
+RUN_TOKENS = 64     # consecutive decode tokens before the cache is rewound: one 64-token block of the residual buffer
 SHARDING_TEXT = {
     "replicate": "(batch, kv-head) units, no collective; every rank runs the full shape",
     "batch": "batch rows split across ranks, no collective",
@@ -108,8 +109,11 @@ def config_dict(name: str, world: int, v_mode: str | None = None) -> dict:
     return {"workload": name, "batch": Bt, "query_heads": Hq, "kv_heads": H, "head_dim": D, "cache_len": L,
             "per_gpu_batch": per_gpu, "global_batch": tokens, "pv_kernel": v_mode or W["v_mode"],
             "sharding": SHARDING_TEXT[sharding],
-            "step": "rewind to cache_len-1 tokens -> append the last token (flushes a 64-token block through the plane "
-                    "writers) -> decode",
+            "step": "one decode token of a run of %d consecutive tokens that starts with cache_len tokens cached (all of "
+                    "them quantized): 63 tokens are appended to the residual buffer, the 64th flushes the 64-token block "
+                    "through the plane writers; then the cache is rewound to the start of the run (akv_rollback, inside "
+                    "the timed region).  Every step streams at least cache_len quantized tokens plus the residual "
+                    "ones" % RUN_TOKENS,
             "l2": "inputs larger than L2 (planes about %.0f MiB per GPU)" % plane_mib}
 
 
@@ -289,7 +293,7 @@ def measure(name, args, ctx, min_seconds):
 
     if sharding == "sequence":
         # rank r holds tokens [lo, hi) of the L-1 cached tokens; the last rank also takes the decode token
-        seq = SequenceShardedDecoder(B, L - 1, 1, H, D, dev, n_q_heads=Hq, v_mode=v_mode)
+        seq = SequenceShardedDecoder(B, L - 1, RUN_TOKENS + 1, H, D, dev, n_q_heads=Hq, v_mode=v_mode)
         lo, hi = shard_bounds(L - 1, world)[rank]
         k, v = draw(hi - lo + 1)
         seq.prefill(k[:, :hi - lo].contiguous(), v[:, :hi - lo].contiguous())
@@ -298,7 +302,7 @@ def measure(name, args, ctx, min_seconds):
     elif sharding == "sequence_exact" or W["sharding"] == "sequence_exact":
         # rank r holds tokens [lo, hi) of the L-1 cached tokens, lo a multiple of 4096; every rank sees the decode token
         # (it feeds the exponent maxima), the last rank stores it
-        seq = DecisionExactShardedDecoder(B, L - 1, 1, H, D, dev, n_q_heads=Hq)
+        seq = DecisionExactShardedDecoder(B, L - 1, RUN_TOKENS + 1, H, D, dev, n_q_heads=Hq)
         lo, hi = chunk_bounds(L - 1, world)[rank]
         k, v = draw(hi - lo + 1)
         seq.prefill(k[:, :hi - lo].contiguous(), v[:, :hi - lo].contiguous())
@@ -309,19 +313,23 @@ def measure(name, args, ctx, min_seconds):
             dist.broadcast(v_tok, src=world - 1)
     else:
         seq = None
-        layer = DecodeLayer(B, L, H, D, dev, n_q_heads=Hq, v_mode=v_mode)
+        layer = DecodeLayer(B, L + RUN_TOKENS, H, D, dev, n_q_heads=Hq, v_mode=v_mode)   # room for one run
         k, v = draw(L)
         layer.prefill(k[:, :L - 1].contiguous(), v[:, :L - 1].contiguous())
         k_tok, v_tok = k[:, L - 1:].contiguous(), v[:, L - 1:].contiguous()
     q = torch.randn(B, 1, Hq, D, device=dev, generator=torch.Generator(device=dev).manual_seed(args.seed + 7)).half()
     owner = seq if isinstance(seq, DecisionExactShardedDecoder) else layer
-    snap = owner.snapshot()                                # state before the decode token (63 tokens in the residual)
+    snap_flush = owner.snapshot()                          # cache_len-1 tokens cached, 63 of them in the residual buffer
 
     def decode(q_, k_, v_):
         return seq.decode(q_, k_, v_) if seq is not None else layer.decode(q_, k_, v_)
 
     def step_resident():
-        owner.restore(snap)
+        return decode(q, k_tok, v_tok)
+
+    def step_flush():
+        """Rewind to cache_len-1 tokens, append token cache_len (which flushes the 64-token block), decode."""
+        owner.restore(snap_flush)
         return decode(q, k_tok, v_tok)
 
     # end-to-end number: the step's inputs (q | k | v of the new token) lie in ONE pinned host buffer and cross in
@@ -333,7 +341,6 @@ def measure(name, args, ctx, min_seconds):
     hout = torch.empty((B, 1, Hq, D), dtype=torch.half).pin_memory()
 
     def step_e2e():
-        owner.restore(snap)
         din.copy_(hin, non_blocking=True)
         out = decode(dq, dk, dv)
         hout.copy_(out, non_blocking=True)
@@ -346,23 +353,37 @@ def measure(name, args, ctx, min_seconds):
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed_blocks(fn, steps, warmup, seconds):
+    run = {"pos": 0, "snap": None}
+
+    def in_run(fn):
+        """One step of a run of consecutive decode tokens: after RUN_TOKENS tokens the cache is rewound to the start of
+        the run (cache_len tokens cached, residual buffer empty) - inside whatever is being timed."""
+        if run["pos"] == RUN_TOKENS:
+            owner.restore(run["snap"])
+            run["pos"] = 0
+        run["pos"] += 1
+        return fn()
+
+    def timed_blocks(fn, steps, warmup, seconds, stepper):
         """Blocks of exactly `steps` steps, each bracketed by a barrier + synchronize on both sides and timed with
         CUDA events; repeated until `seconds` of device time have been measured (at least 3 blocks).  Returns, per
-        block, the MAX over the ranks of the block's time, and every rank's own times (on rank 0)."""
+        block, the MAX over the ranks of the block's time, every rank's own times (on rank 0), and the library's
+        launch count per block."""
         for _ in range(warmup):
-            fn()
-        own, worst = [], []
+            stepper(fn)
+        own, worst, counts = [], [], []
         t0 = time.time()
         while len(worst) < 3 or (sum(worst) < seconds * 1e3 and len(worst) < 400):
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n0 = layer.launches
             e0.record()
             for _ in range(steps):
-                fn()
+                stepper(fn)
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
+            counts.append(layer.launches - n0)
             barrier()
             own.append(ms)
             if world > 1:
@@ -377,43 +398,51 @@ def measure(name, args, ctx, min_seconds):
             allr = [torch.zeros_like(mine) for _ in range(world)]
             dist.all_gather(allr, mine)
             per_rank = [[round(float(x) / steps * 1e3, 2) for x in r.tolist()] for r in allr]   # us per step
-        return worst, per_rank, t0, t1
+        return worst, per_rank, t0, t1, counts
 
     warm = max(args.warmup, 3)
-    sampler = ClockSampler(ctx["local"]) if rank == 0 else None
     layer.launches = 0
-    if sampler:
-        sampler.start()
-    blocks, per_rank, t0, t1 = timed_blocks(step_resident, args.steps, warm, min_seconds)   # no instrumentation inside
-    launches = layer.launches // (args.steps * len(blocks) + warm)   # kernels of this library per step (its own counter)
-    ms = statistics.median(blocks)
-    # the same steps again with CUDA events recorded around the two streaming kernels (the events cost ~10 us per
-    # step, which is why they stay out of the headline pass)
+    # ---- the first step of a run by itself, every step (rewind + append with the flush + decode): the run's worst step
+    flush_blocks, _, _, _, _ = timed_blocks(step_flush, args.steps, warm, min_seconds / 5, lambda fn: fn())
+    ms_flush = statistics.median(flush_blocks)
+    # such steps again with CUDA events recorded around the two streaming kernels (the events cost ~10 us per step)
     layer.reset_counters()
     for _ in range(min(2 * args.steps, 200)):
-        step_resident()
-    clocks = sampler.stop(t0, time.time()) if sampler else None
+        step_flush()
     kern_in_step = layer.kernel_times()                    # median per-kernel CUDA-event brackets of that pass
-    e2e_blocks, _, _, _ = timed_blocks(step_e2e, args.steps, warm, min_seconds / 2)
-    ms_e2e = statistics.median(e2e_blocks)
-
-    # algorithmic bytes under this step's read decisions, summed over the ranks
-    out_last = step_resident()
+    out_last = step_flush()
     torch.cuda.synchronize()
     kern = kernel_loop_times(layer, q, v_mode) or kern_in_step
+    # algorithmic bytes under this step's read decisions, summed over the ranks
     acct = layer.bytes_accounting(q)
     keys = ("k_compute", "v_compute", "read", "dense")
     tot = torch.tensor([acct[k_] for k_ in keys], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tot)
     total = dict(zip(keys, (float(x) for x in tot.tolist())))
+    n_tok = layer.rest_start
+    # outside any timed region: is the output right, and what do the reference's kernels need on the same state
+    check = validate(layer, q, k, v, out_last, G, v_mode, sharded_sequence=seq is not None and world > 1,
+                     want_ref_timing=(rank == 0))
 
-    # ---- outside the timed region: is the output right, and what do the reference's kernels need on the same state
+    # ---- the headline: runs of consecutive decode tokens from cache_len cached tokens (the state the step above left)
+    run["snap"] = owner.snapshot()
+    sampler = ClockSampler(ctx["local"]) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    blocks, per_rank, t0, t1, counts = timed_blocks(step_resident, args.steps, warm, min_seconds, in_run)   # no instrumentation inside
+    clocks = sampler.stop(t0, time.time()) if sampler else None
+    launches = int(statistics.median(counts))              # kernels of this library per timed block (its own counter)
+    # whole runs per block: all blocks are alike, take the median; else the blocks differ (some hold the flush and the
+    # rewind, some do not) and the mean is the cost per token
+    whole_runs = args.steps % RUN_TOKENS == 0
+    ms = statistics.median(blocks) if whole_runs else sum(blocks) / len(blocks)
+    e2e_blocks, _, _, _, _ = timed_blocks(step_e2e, args.steps, warm, min_seconds / 2, in_run)
+    ms_e2e = statistics.median(e2e_blocks) if whole_runs else sum(e2e_blocks) / len(e2e_blocks)
+
     flag = torch.tensor([int(layer.lib.akv_device_error_flag())], device=dev)
     if world > 1:
         dist.all_reduce(flag, op=dist.ReduceOp.MAX)
-    check = validate(layer, q, k, v, out_last, G, v_mode, sharded_sequence=seq is not None and world > 1,
-                     want_ref_timing=(rank == 0))
     check["device_error_flag"] = int(flag.item())
     if check["device_error_flag"] != 0:
         raise SystemExit("bench: a bounded wait inside a kernel gave up during the run (akv_device_error_flag != 0)")
@@ -432,7 +461,6 @@ def measure(name, args, ctx, min_seconds):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     traffic = load_traffic_table()
     units = B * H
-    n_tok = layer.rest_start
 
     def roofline_of(kname):
         if kname not in kern:
@@ -464,11 +492,14 @@ def measure(name, args, ctx, min_seconds):
         "scaling": "weak" if W["sharding"] == "replicate" else "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
         "config": cfg,
-        "timing": {"blocks": len(blocks), "steps_per_block": args.steps, "block_ms_median": ms, "block_ms_min": min(blocks),
+        "timing": {"blocks": len(blocks), "steps_per_block": args.steps, "block_ms_median": statistics.median(blocks),
+                   "block_ms_mean": sum(blocks) / len(blocks), "statistic": "median" if whole_runs else "mean",
+                   "block_ms_min": min(blocks),
                    "block_ms_max": max(blocks), "seconds_timed": sum(blocks) * 1e-3,
                    "per_rank_us_per_step_min_median_max": per_rank,
                    "rule": "every block = exactly `steps` steps between barrier + synchronize pairs, CUDA events, max "
-                           "over ranks; the reported step time is the median block"},
+                           "over ranks; the reported step time is the median block when a block holds whole runs of "
+                           "%d tokens (the default), else the mean over the blocks" % RUN_TOKENS},
         "effective_hbm_gbs": total["dense"] / (ms_step * 1e-3) / 1e9,
         "achieved_hbm_gbs": total["read"] / (ms_step * 1e-3) / 1e9,
         "bytes_read_over_dense": total["read"] / total["dense"],
@@ -478,7 +509,11 @@ def measure(name, args, ctx, min_seconds):
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int((q.numel() + k_tok.numel() + v_tok.numel()) * 2),
                 "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": launches * args.steps,
+        "flush_step": {"ms_per_step": ms_flush / args.steps,
+                       "what": "the flushing step timed by itself, every step: rewind to cache_len-1 tokens, append "
+                               "token cache_len with the flush of the 64-token block, decode.  The per-kernel figures, "
+                               "the accuracy block and the reference kernels' timings are taken on this step's state"},
+        "gpu_launches": launches,
         "clocks": clocks,
         "accuracy": check["accuracy"],
         "validation": {"device_error_flag": check["device_error_flag"], "note": check["note"]},
@@ -666,7 +701,7 @@ def run_ours(args):
             if r is not None:
                 others[name] = {k_: r[k_] for k_ in ("value", "unit", "ms_per_step", "scaling", "config", "kernels_us",
                                                      "roofline", "e2e", "bytes_read_over_dense", "accuracy", "timing",
-                                                     "gpu_launches", "ref_cuda_kernels_us")}
+                                                     "gpu_launches", "ref_cuda_kernels_us", "flush_step")}
     if rank == 0:
         if others:
             line["other_workloads"] = others
