@@ -28,6 +28,7 @@ struct Tuning {
     int v_nside = 0;    // exact P.V (form 0): rows of the nibble side ring, a power of two >= 128 (0 = default)
     int v_cps = 0;      // exact P.V (form 0): CTAs per SM the shared-memory budget is cut for (0 = one wave)
     int v_upc = 0;      // exact P.V (form 0): (batch, head) units per CTA, 1 or 2 (0 = default)
+    int v_gqa_chain_waves = 1;   // exact P.V, grouped queries: form 0 with one unit per query head up to this many waves of CTAs
 };
 Tuning& tuning();
 
@@ -134,13 +135,26 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
 __device__ __forceinline__ uint32_t v_threshold_warp(const uint16_t* __restrict__ test_o,
                                                      const uint8_t* __restrict__ v_exp, long long i, int H, int G,
                                                      int D, int lane) {
-    const long long Hq = (long long)H * G;
-    const long long bb = i / (Hq * Hq), hp = (i / Hq) % Hq, he = i % Hq;
+    // (row indices fit 32 bits: launchers reject more than 2^30 rows)
+    const uint32_t Hq = (uint32_t)(H * G), iu = (uint32_t)i;
+    const uint32_t bb = iu / (Hq * Hq), hp = (iu / Hq) % Hq, he = iu % Hq;
+    const uint16_t* trow = test_o + (size_t)(bb * Hq + hp) * D;
+    const uint8_t* erow = v_exp + (size_t)(bb * H + he / G) * D;
     uint32_t m = 255;
-    for (int d = lane; d < D; d += 32) {
-        const uint32_t e = ((uint32_t)test_o[(size_t)(bb * Hq + hp) * D + d] >> 10) & 0x1Eu;
-        const uint32_t a = (e + 15u - v_exp[(size_t)(bb * H + he / G) * D + d]) & 0xFFu;
-        m = min(m, a);
+    for (int d0 = 0; d0 < D; d0 += 128) {       // four loads of each row in flight per lane
+        uint32_t t[4], x[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int d = d0 + r * 32 + lane;
+            t[r] = d < D ? (uint32_t)trow[d] : 0u;
+            x[r] = d < D ? (uint32_t)erow[d] : 0u;
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const uint32_t e = (t[r] >> 10) & 0x1Eu;
+            const uint32_t a = (e + 15u - x[r]) & 0xFFu;
+            if (d0 + r * 32 + lane < D) m = min(m, a);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));

@@ -17,7 +17,9 @@
 // chains per thread, which hide the FMA latency.  That matters more than it seems: a warp whose steady loop carries
 // branches and rarely-run code, or does not fit the scheduler's instruction cache, was measured at a third of the
 // speed of the same arithmetic in a straight line.
-//   A unit = one (batch, head); a CTA holds UPC units, each with its own three warps, rings and barriers.
+//   A unit = one (batch, query head); a CTA holds UPC units, each with its own warps, rings and barriers.  With grouped
+//   queries the heads of a KV head are neighbouring units that stream the same planes at the same pace: the first
+//   one's copies bring a stage into L2, the others' hit there.
 //   chain warp: all 64 channel pairs of the head, one 64-token stage per loop iteration.
 //   copy warp: stage i -> ring slot i % nf as soon as the chain has released the slot's previous stage: one 8 KB bulk
 //     asynchronous copy of the high bytes exactly as they lie in the plane.
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
 
     if (role == 3) {
         // ------------------------------------------------------------------ copy warp: the high bytes
-        const uint8_t* F = p.first8 + (size_t)bh * p.max_seq_len * D;
+        const uint8_t* F = p.first8 + (size_t)(bh / p.group) * p.max_seq_len * D;   // planes of the unit's KV head
         int slot = 0;
         uint32_t parity = 0;                       // of the release being waited for: (i / nf - 1) & 1
         bool alive = true;
@@ -302,8 +304,8 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
         // Warp w (0, 1) owns the stages of parity w.  The ring depth nf is even, so the previous stage of a ring slot
         // belongs to the same warp, and each warp has its own half of the side ring: the two never share state.
         const int w = role - 1;
-        const uint8_t* M = p.mid4 + (size_t)bh * p.max_seq_len * HD;
-        const uint8_t* L = p.last4 + (size_t)bh * p.max_seq_len * HD;
+        const uint8_t* M = p.mid4 + (size_t)(bh / p.group) * p.max_seq_len * HD;
+        const uint8_t* L = p.last4 + (size_t)(bh / p.group) * p.max_seq_len * HD;
         const uint16_t* s_row = p.s + (size_t)bh * p.s_last_dim;
         bool alive = true;
         // probability chunk c (stages c*sch ..) -> buffer `buf` = c % 3; issued by one thread of warp 0
@@ -319,7 +321,7 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
         // threshold: from the probe result (decode step) or as given
         uint32_t a;
         if (p.test_o) {
-            a = v_threshold_warp(p.test_o, p.v_exp, bh, p.H, 1, D, lane);
+            a = v_threshold_warp(p.test_o, p.v_exp, bh, p.H, p.group, D, lane);
             if (w == 0 && lane == 0) p.amin_out[bh] = (uint8_t)a;
         } else {
             a = p.amin[bh];

@@ -554,9 +554,15 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
     const int BH = bsz * H;
     const bool fast = v_compute_takes_probe(first8, mid4, last4, s, o, group, D, s_last_dim, n);
     AKV_REQUIRE(fast || !test_o, AKV_ERR_SHAPE, "v_cache_compute: the probe form needs the streaming kernel");
-    if (fast && group == 1 && !reference && tuning().v_impl == 0) {
-        const VChainCfg c = v_chain_config(BH, reference);
-        return c.upc == 2 ? launch_v_chain_u<2>(p, c, BH, st) : launch_v_chain_u<1>(p, c, BH, st);
+    // The chain form has one unit per (batch, QUERY head).  With grouped queries the heads of a group re-read their
+    // KV head's planes (from L2), which pays while the units fit one wave of CTAs (98 -> 61 us for 8 x 8 KV heads x 4
+    // query heads x 8192 tokens); beyond that the grouped kernel below, which stages every plane byte once for the
+    // whole group, is as fast or faster.
+    const long long units = (long long)BH * group;
+    const bool chain_form = group == 1 || units <= (long long)tuning().v_gqa_chain_waves * 2 * sm_count();
+    if (fast && chain_form && !reference && tuning().v_impl == 0) {
+        const VChainCfg c = v_chain_config((int)units, reference);
+        return c.upc == 2 ? launch_v_chain_u<2>(p, c, (int)units, st) : launch_v_chain_u<1>(p, c, (int)units, st);
     }
     if (fast && group == 1) return launch_v_fast<1, 6, 2, 1>(p, BH, st);
     if (fast && group == 2) return launch_v_fast<2, 6, 2, 2>(p, BH, st);
