@@ -54,7 +54,8 @@ struct VParams {
     int max_seq_len, D, s_last_dim, n, reference;
     int group;              // query heads per KV head (1 = multi-head attention)
     int nf, nside, sch;     // streaming form: ring depth (stages), side-ring rows (power of two), stages per chunk
-    int units;              // streaming form: number of (batch, KV head) units
+    int npt;                // streaming form: low-byte tables per head (even: half of them per decision warp)
+    int units;              // streaming form: number of ring units (heads / heads per ring)
 };
 
 // ---- device error flag and shared-memory barriers (mbarrier) with bounded waits
@@ -121,23 +122,33 @@ namespace vch {
 constexpr int TOK = 64;            // tokens per stage
 constexpr int D = 128, HD = 64;    // head size, bytes of a nibble row
 constexpr int F_BYTES = TOK * D;   // high bytes of a stage (and its rows of the low-byte table)
-constexpr int REC = 16;            // record of a stage: {first side row, flagged tokens 0..31, 32..63, rows}
+constexpr int REC = 16;            // record of a stage: {first side row, flagged tokens 0..31, 32..63, rows | (table + 1) << 8}
 
-// Shared-memory plan of one unit (byte offsets), computed the same way on both sides.
+// Shared-memory plan of a CTA (byte offsets), computed the same way on both sides.  A CTA holds `upc` rings, each
+// shared by `gh` heads (gh > 1: the query heads of one KV head read the same high bytes).
 struct Plan {
-    int f, lw, mid, low, sb, rec, thr, bar, bytes;
+    int ctab;                        // the constant low-byte table (0x80 everywhere), one per CTA
+    int ring0, ring_bytes, rbar;     // ring r at ring0 + r * ring_bytes: nf stages of high bytes, then full[nf], free[nf] at rbar
+    int head0, head_bytes;           // head u at head0 + u * head_bytes, inside it:
+    int lw, mid, low, sb, rec, thr, bar;
+    int bytes;
 };
-__host__ __device__ inline Plan plan(int nf, int nside, int sch) {
+__host__ __device__ inline Plan plan(int nf, int nside, int sch, int npt, int upc, int gh) {
     Plan p;
-    p.f = 0;                                   // nf stages of high bytes
-    p.lw = nf * F_BYTES;                       // nf stages of low bytes (the table)
-    p.mid = 2 * nf * F_BYTES;                  // side rings: rows of the mid / low nibble planes
+    p.ctab = 0;
+    p.ring0 = F_BYTES;
+    p.rbar = nf * F_BYTES;
+    p.ring_bytes = (nf * F_BYTES + 2 * nf * 8 + 127) & ~127;
+    p.head0 = p.ring0 + upc * p.ring_bytes;
+    p.lw = 0;                                  // npt low-byte tables, each of a stage's shape
+    p.mid = npt * F_BYTES;                     // side rings: rows of the mid / low nibble planes
     p.low = p.mid + nside * HD;
     p.sb = p.low + nside * HD;                 // three probability buffers of sch x 64 values
     p.rec = p.sb + 3 * sch * TOK * 2;          // 2 nf records
     p.thr = p.rec + 2 * nf * REC;              // threshold (already shifted)
-    p.bar = (p.thr + 4 + 7) & ~7;              // full[nf], free[nf], probability buffers[3], nibble rows[2 nf]
-    p.bytes = p.bar + (4 * nf + 3) * 8;
+    p.bar = (p.thr + 4 + 7) & ~7;              // probability buffers[3], nibble rows[2 nf]
+    p.head_bytes = (p.bar + (2 * nf + 3) * 8 + 127) & ~127;
+    p.bytes = p.head0 + upc * gh * p.head_bytes;
     return p;
 }
 }  // namespace vch
@@ -233,55 +244,74 @@ __device__ __noinline__ void v_restore_low_rows(uint32_t lw, uint32_t m0, uint32
                          "r"(0x80808080u) : "memory");
 }
 
-template <int UPC>
-__global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
+template <int UPC, int GH>
+__global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(const VParams p) {
     using namespace vch;
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NU = UPC * GH;                   // heads of the CTA
+    // Low-byte tables.  One head per ring: a table per ring slot (npt == nf), patched for the slot's stage and restored
+    // when the slot is released - a stage without flagged tokens finds the constant there, and the chain needs neither
+    // the record nor a select.  Several heads per ring: there is no room for that, so each decision warp has a few
+    // tables it hands to its stages with flagged tokens, and the other stages read the CTA's constant table.
+    constexpr bool SLOT_TABLES = GH == 1;
     const int tid = threadIdx.x, lane = tid & 31, wcta = tid >> 5;
-    // Warp roles: per unit a chain warp, two decision warps (even / odd stages: one warp's serial walk through a stage
-    // takes longer than the chain needs to consume it) and a copy warp.  The warps of a CTA are spread over the SM's
-    // four schedulers by index: [chain u0, chain u1, decision0 u0, decision0 u1, copy u0, copy u1, decision1 u0,
-    // decision1 u1] gives each chain warp a scheduler it shares only with its copy warp (a handful of instructions per
-    // stage), and the four decision warps the other two.
-    const int unit = UPC == 1 ? 0 : (wcta & 1);
-    const int wrole = UPC == 1 ? wcta : (wcta >> 1);
-    const int role = wrole == 2 ? 3 : (wrole == 3 ? 2 : wrole);   // 0: chain, 1, 2: decision (even, odd stages), 3: copy
-    const long long bh = (long long)blockIdx.x * UPC + unit;   // (batch, head)
+    // Warp roles: per head a chain warp and two decision warps (even / odd stages: one warp's serial walk through a
+    // stage takes longer than the chain needs to consume it), per ring a copy warp.  Order in the CTA: the chain warps,
+    // the even-stage decision warps, the copy warps, the odd-stage decision warps.  The warps are spread over the SM's
+    // four schedulers by index, so with two rings of one head each chain warp shares its scheduler only with its copy
+    // warp (a handful of instructions per stage) and the four decision warps have the other two; with four heads on
+    // one ring every scheduler has one chain warp.
+    int role, hu;                                  // 0: chain, 1, 2: decision (even, odd stages), 3: copy; head of the CTA
+    if (wcta < NU) { role = 0; hu = wcta; }
+    else if (wcta < 2 * NU) { role = 1; hu = wcta - NU; }
+    else if (wcta < 2 * NU + UPC) { role = 3; hu = (wcta - 2 * NU) * GH; }
+    else { role = 2; hu = wcta - 2 * NU - UPC; }
+    const int ring = hu / GH, hg = hu - ring * GH;
+    const long long ru = (long long)blockIdx.x * UPC + ring;   // ring unit
+    const long long bh = ru * GH + hg;                         // (batch, query head)
+    const long long kv = (ru * GH) / p.group;                  // (batch, KV head) whose planes the ring streams
     const int n = p.n, nf = p.nf, nside = p.nside, sch = p.sch;
     const int nst = (n + TOK - 1) / TOK;
-    const Plan pl = plan(nf, nside, sch);
-    const uint32_t base = smem_u32(smem) + (uint32_t)unit * (uint32_t)((pl.bytes + 127) & ~127);
-    const uint32_t bar_full = base + pl.bar, bar_free = bar_full + nf * 8, bar_sb = bar_free + nf * 8;
-    const uint32_t bar_nib = bar_sb + 3 * 8;
+    const Plan pl = plan(nf, nside, sch, p.npt, UPC, GH);
+    const uint32_t cta = smem_u32(smem);
+    const uint32_t rbase = cta + pl.ring0 + (uint32_t)ring * pl.ring_bytes;    // the ring's stages of high bytes
+    const uint32_t base = cta + pl.head0 + (uint32_t)hu * pl.head_bytes;       // everything of this head
+    const uint32_t bar_full = rbase + pl.rbar, bar_free = bar_full + nf * 8;
+    const uint32_t bar_sb = base + pl.bar, bar_nib = bar_sb + 3 * 8;
+    const uint32_t ctab = cta + pl.ctab;
 
     pdl_enter();
+    if (!SLOT_TABLES)
+        for (int i = tid; i < F_BYTES / 16; i += blockDim.x)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(ctab + i * 16), "r"(0x80808080u) : "memory");
     if (role == 0) {
         if (lane == 0) {
-            for (int s = 0; s < nf; ++s) {
-                mbar_init(bar_full + s * 8, 2);    // the copy warp's and the decision warp's arrivals (+ the high bytes)
-                mbar_init(bar_free + s * 8, 1);    // the chain warp's arrival
-            }
+            if (hg == 0)
+                for (int s = 0; s < nf; ++s) {
+                    mbar_init(bar_full + s * 8, 1 + GH);   // the copy warp's arrival (+ the high bytes) and one decision warp's per head
+                    mbar_init(bar_free + s * 8, GH);       // the chain warps' arrivals
+                }
             for (int s = 0; s < 3; ++s) mbar_init(bar_sb + s * 8, 1);
             for (int s = 0; s < 2 * nf; ++s) mbar_init(bar_nib + s * 8, 1);
             asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         }
-        // the low-byte table starts as the constant: 0x80 for every channel of every token
-        for (int i = lane; i < nf * F_BYTES / 16; i += 32)
+        // the head's own low-byte tables start as the constant too: 0x80 for every channel of every token
+        for (int i = lane; i < p.npt * F_BYTES / 16; i += 32)
             asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(base + pl.lw + i * 16), "r"(0x80808080u) : "memory");
     }
     __syncthreads();
-    if (bh >= p.units) return;                     // (odd number of units: the last CTA's second half has none)
+    if (ru >= p.units) return;                     // (odd number of ring units: the last CTA's second ring has none)
 
     if (role == 3) {
         // ------------------------------------------------------------------ copy warp: the high bytes
-        const uint8_t* F = p.first8 + (size_t)(bh / p.group) * p.max_seq_len * D;   // planes of the unit's KV head
+        const uint8_t* F = p.first8 + (size_t)kv * p.max_seq_len * D;
         int slot = 0;
         uint32_t parity = 0;                       // of the release being waited for: (i / nf - 1) & 1
         bool alive = true;
         // The decision warp's first loads (probe result, exponent maxima) go out before this warp floods the memory
         // system with the first ring of copies - behind that flood they would take several times as long, and the
         // first stage cannot be consumed before the threshold is known.
-        asm volatile("bar.sync %0, 96;\n" ::"r"(1 + unit) : "memory");
+        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + ring), "r"((2 * GH + 1) * 32) : "memory");
 #pragma unroll 1
         for (int i = 0; i < nst; ++i) {
             if (i >= nf) {
@@ -292,7 +322,7 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
                 const int cnt = (n - i * TOK) < TOK ? (n - i * TOK) : TOK;
                 const uint32_t bar = bar_full + slot * 8;
                 mbar_arrive_expect(bar, (uint32_t)cnt * D);
-                bulk_copy(base + pl.f + (uint32_t)slot * F_BYTES, F + (size_t)i * TOK * D, (uint32_t)cnt * D, bar);
+                bulk_copy(rbase + (uint32_t)slot * F_BYTES, F + (size_t)i * TOK * D, (uint32_t)cnt * D, bar);
             }
             if (++slot == nf) { slot = 0; if (i >= nf) parity ^= 1u; }
         }
@@ -304,8 +334,8 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
         // Warp w (0, 1) owns the stages of parity w.  The ring depth nf is even, so the previous stage of a ring slot
         // belongs to the same warp, and each warp has its own half of the side ring: the two never share state.
         const int w = role - 1;
-        const uint8_t* M = p.mid4 + (size_t)(bh / p.group) * p.max_seq_len * HD;
-        const uint8_t* L = p.last4 + (size_t)(bh / p.group) * p.max_seq_len * HD;
+        const uint8_t* M = p.mid4 + (size_t)kv * p.max_seq_len * HD;
+        const uint8_t* L = p.last4 + (size_t)kv * p.max_seq_len * HD;
         const uint16_t* s_row = p.s + (size_t)bh * p.s_last_dim;
         bool alive = true;
         // probability chunk c (stages c*sch ..) -> buffer `buf` = c % 3; issued by one thread of warp 0
@@ -327,7 +357,7 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
             a = p.amin[bh];
         }
         const uint32_t A = (a << 10) & 0xFFFFu;
-        asm volatile("bar.sync %0, 96;\n" ::"r"(1 + unit) : "memory");
+        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + ring), "r"((2 * GH + 1) * 32) : "memory");
         const int hside = nside / 2;                       // rows of this warp's half of the side ring
         const uint32_t ma = base + pl.mid + (uint32_t)w * hside * HD, la = base + pl.low + (uint32_t)w * hside * HD;
         const uint32_t wrap = (uint32_t)(hside - 1);
@@ -336,13 +366,20 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
         int freed = w, freed_slot = w, freed_rec = w;   // next own stage whose release is to be consumed; % nf, % 2nf
         uint32_t freed_parity = 0;                      // (freed / nf) & 1
         uint32_t nib_par = 0;                           // bit r: parity of the NEXT phase of nibble barrier r
+        // low-byte tables of this warp, used in turn by its stages with flagged tokens; t_out = tables in use (built
+        // and not yet restored)
+        const int npw = p.npt >> 1;
+        int t_next = 0, t_out = 0;
         // consume the release of own stage `freed`: its side rows are free again, its patched table rows become 0x80 again
         auto reclaim = [&]() {
             alive = mbar_wait(bar_free + freed_slot * 8, freed_parity);
             const uint4 rec = lds128(base + pl.rec + freed_rec * REC);
             if (__builtin_expect(rec.w != 0, 0)) {
-                side_tail += rec.w;
-                if (alive) v_restore_low_rows(base + pl.lw + (uint32_t)freed_slot * F_BYTES, rec.y, rec.z, lane);
+                side_tail += rec.w & 0xFFu;
+                if (alive && (rec.w >> 8) != 0) {           // (a stage that was prepared but never armed has no table)
+                    v_restore_low_rows(base + pl.lw + ((rec.w >> 8) - 1u) * F_BYTES, rec.y, rec.z, lane);
+                    --t_out;
+                }
             }
             freed += 2;
             if ((freed_slot += 2) >= nf) { freed_slot -= nf; freed_parity ^= 1u; }
@@ -421,11 +458,20 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
                     // low-byte table be built; then it is armed
                     const uint4 r = lds128(base + pl.rec + rec * REC);
                     if (__builtin_expect(r.w != 0, 0)) {
-                        alive = mbar_wait(bar_nib + rec * 8, ((nib_par >> rec) & 1u) ^ 1u);
-                        if (alive)
-                            v_build_low_rows(base + pl.lw + (uint32_t)slot * F_BYTES, ma, la, r, wrap,
+                        // a table of this warp: the oldest one in use is handed back when its (armed) stage is released
+                        while (!SLOT_TABLES && alive && t_out >= npw) reclaim();
+                        if (alive) alive = mbar_wait(bar_nib + rec * 8, ((nib_par >> rec) & 1u) ^ 1u);
+                        if (alive) {
+                            const uint32_t tbl = SLOT_TABLES ? (uint32_t)slot : (uint32_t)(w * npw + t_next);
+                            v_build_low_rows(base + pl.lw + tbl * F_BYTES, ma, la, r, wrap,
                                              base + pl.sb + (uint32_t)l_buf * (sch * TOK * 2) + (uint32_t)l_sic * (TOK * 2), A,
                                              p.reference, lane);
+                            if (lane == 0)
+                                asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(base + pl.rec + rec * REC + 12),
+                                             "r"(r.w | ((tbl + 1u) << 8)) : "memory");
+                            t_next = t_next + 1 == npw ? 0 : t_next + 1;
+                            ++t_out;
+                        }
                     }
                     __syncwarp();
                     if (lane == 0 && alive) mbar_arrive(bar_full + slot * 8);   // publishes the table rows; the copy warp adds the bytes
@@ -446,6 +492,7 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
     uint32_t accA = 0, accB = 0;
     bool alive = true;
     const int nsf = n / TOK;                                           // full stages
+    const int nrec = 2 * nf;                                           // records: one per stage, a ring of two ring lengths
     // Registers of one group of 8 tokens: per token [pair A even, odd | pair B even, odd] high bytes and low bytes, and
     // the 8 probabilities.
     struct Grp {
@@ -456,12 +503,14 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                      : "=r"(r[o]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]) : "r"(a));
     };
-    auto fetch = [&](Grp& r, uint32_t fa, uint32_t sa, int grp) {
-        const uint32_t a = fa + (uint32_t)grp * (8 * D) + lm_off;
-        ldm(r.h, 0, a);
-        ldm(r.h, 4, a + 4 * D);
-        ldm(r.l, 0, a + (uint32_t)(pl.lw - pl.f));
-        ldm(r.l, 4, a + (uint32_t)(pl.lw - pl.f) + 4 * D);
+    // la: the low-byte table of the stage - one of the head's own tables when the stage has flagged tokens, else the
+    // CTA's constant table (an address select, no branch)
+    auto fetch = [&](Grp& r, uint32_t fa, uint32_t la, uint32_t sa, int grp) {
+        const uint32_t a = (uint32_t)grp * (8 * D) + lm_off;
+        ldm(r.h, 0, fa + a);
+        ldm(r.h, 4, fa + a + 4 * D);
+        ldm(r.l, 0, la + a);
+        ldm(r.l, 4, la + a + 4 * D);
         r.s = lds128(sa + grp * 16);
     };
     auto consume = [&](const Grp& r) {
@@ -472,15 +521,22 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
             accB = v_fma(__byte_perm(r.h[u], r.l[u], 0x3726), sd, accB);
         }
     };
-    int slot = 0, sic = 0, buf = 0;                                    // of the current stage: % nf, % sch, chunk % 3
+    int slot = 0, sic = 0, buf = 0, crec = 0;                          // of the current stage: % nf, % sch, chunk % 3, % 2 nf
     uint32_t parity = 0;
-    auto f_addr = [&]() { return base + pl.f + (uint32_t)slot * F_BYTES; };
+    auto f_addr = [&]() { return rbase + (uint32_t)slot * F_BYTES; };
     auto s_addr = [&]() { return base + pl.sb + (uint32_t)buf * (sch * TOK * 2) + (uint32_t)sic * (TOK * 2); };
+    // the stage's table, from its record (word 3: flagged rows | (table + 1) << 8; 0 = no flagged token)
+    auto l_addr = [&]() {
+        if (SLOT_TABLES) return base + pl.lw + (uint32_t)slot * F_BYTES;
+        const uint32_t w = lds32(base + pl.rec + (uint32_t)crec * REC + 12);
+        return w ? base + pl.lw + ((w >> 8) - 1u) * F_BYTES : ctab;
+    };
     Grp ra, rb;
-    uint32_t fa = f_addr(), sa = s_addr();
+    uint32_t fa = f_addr(), sa = s_addr(), la = ctab;
     if (nst > 0) {
         alive = mbar_wait(bar_full, 0);
-        if (alive && nsf > 0) fetch(ra, fa, sa, 0);
+        if (alive) la = l_addr();
+        if (alive && nsf > 0) fetch(ra, fa, la, sa, 0);
     }
     // One full stage per iteration, straight-line: groups alternate between ra and rb, the group after next is
     // fetched while one is consumed; on entry ra holds group 0 of the stage.
@@ -489,34 +545,39 @@ __global__ void __launch_bounds__(UPC * 128) v_chain_kernel(const VParams p) {
         const int cslot = slot;
         if (++slot == nf) { slot = 0; parity ^= 1u; }
         if (++sic == sch) { sic = 0; buf = buf == 2 ? 0 : buf + 1; }
+        if (++crec == nrec) crec = 0;
         const uint32_t nfa = f_addr(), nsa = s_addr();
-        uint32_t landed = 0;
+        uint32_t landed = 0, nla = ctab;
 #pragma unroll
         for (int ga = 0; ga < 8; ga += 2) {
-            fetch(rb, fa, sa, ga + 1);
+            fetch(rb, fa, la, sa, ga + 1);
             consume(ra);
             if (ga < 6) {
-                fetch(ra, fa, sa, ga + 2);
+                fetch(ra, fa, la, sa, ga + 2);
                 // the next stage has normally landed long ago (the ring is several stages deep): probe its barrier two
-                // groups before the answer is needed, so that the probe's latency is hidden
+                // groups before the answer is needed, so that the probe's latency is hidden; then read its record
                 if (ga == 2 && left > 1) landed = mbar_test(bar_full + slot * 8, parity);
+                if (ga == 4 && left > 1) nla = l_addr();              // (valid only if it had landed)
             } else if (left > 1) {
-                if (__builtin_expect(!landed, 0)) alive = mbar_wait(bar_full + slot * 8, parity);
-                if (alive) fetch(ra, nfa, nsa, 0);      // first group of the next stage
+                if (__builtin_expect(!landed, 0)) {
+                    alive = mbar_wait(bar_full + slot * 8, parity);
+                    nla = l_addr();
+                }
+                if (alive) fetch(ra, nfa, nla, nsa, 0);      // first group of the next stage
             }
             consume(rb);
         }
         // the stage is consumed: hand back its ring slot
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_free + cslot * 8);
-        fa = nfa; sa = nsa;
+        fa = nfa; sa = nsa; la = nla;
     }
     const int tail = n - nsf * TOK;
     if (tail > 0 && alive) {
         // last, partial stage, token by token (rows of the slot beyond the last token hold stale bytes, never used)
         if (nsf > 0) alive = mbar_wait(bar_full + slot * 8, parity);
         if (alive) {
-            const uint32_t la = fa + (uint32_t)(pl.lw - pl.f);
+            if (nsf > 0) la = l_addr();
 #pragma unroll 1
             for (int t = 0; t < tail; ++t) {
                 const uint32_t hw = lds16(fa + (uint32_t)t * D + pairA * 2) | (lds16(fa + (uint32_t)t * D + pairB * 2) << 16);

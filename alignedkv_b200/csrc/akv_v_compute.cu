@@ -479,50 +479,54 @@ static int launch_v_fast(const VParams& p, int BH, cudaStream_t st) {
 // capacity / units per SM, of which the probability buffers and the side ring take a fixed part and the two rings
 // (high bytes, low-byte table: 16 KB per stage) the rest.
 struct VChainCfg {
-    int upc, nf, nside, sch, smem;
+    int upc, gh, nf, nside, sch, npt, smem;
 };
-static VChainCfg v_chain_config(int BH, int reference) {
+// heads: (batch, query head) rows; gh: heads that share a ring (1, or the group size: the query heads of a KV head)
+static VChainCfg v_chain_config(long long heads, int gh, int reference) {
     const Tuning& t = tuning();
-    const int sms = sm_count();
     VChainCfg c;
-    // two units per CTA: its six warps then put the chain and decision warps on four different schedulers
-    c.upc = BH >= 2 ? 2 : 1;
-    if (t.v_upc > 0) c.upc = t.v_upc;
-    const int ctas = (BH + c.upc - 1) / c.upc;
-    int cps = (ctas + sms - 1) / sms;                      // CTAs per SM for a single wave
-    if (cps < 1) cps = 1;
-    if (cps * c.upc > 4) cps = 4 / c.upc;
-    if (t.v_cps > 0) cps = t.v_cps;
-    // shared memory of one unit (1 KB per CTA is reserved by the system)
-    const int budget = ((max_dyn_smem() + 1024) / cps - 1024) / c.upc - 256;
+    c.gh = gh;
+    // one head per ring: two rings per CTA, whose eight warps put the chain and decision warps on different schedulers
+    c.upc = (gh == 1 && heads >= 2) ? 2 : 1;
+    if (gh == 1 && t.v_upc > 0) c.upc = t.v_upc;
+    const int budget = max_dyn_smem();
     c.nside = reference ? 256 : 128;                       // (each decision warp owns half: at least a stage's 64 rows)
     c.sch = 16;
     if (t.v_nside >= 128) c.nside = t.v_nside;
-    const int fixed = vch::plan(0, c.nside, c.sch).bytes + 64;
-    int nf = (budget - fixed) / (2 * vch::F_BYTES + 2 * vch::REC + 32);
-    if (nf > c.sch / 2) nf = c.sch / 2;                    // the decision warp runs a ring ahead: 2 nf stages <= a chunk
+    // low-byte tables per head: two per decision warp where they fit (a third stage with flagged tokens among a warp's
+    // stages in flight is rare and only makes that warp wait for the oldest one), one with four heads on a ring
+    c.npt = c.upc * gh >= 4 ? 2 : 4;
+    if (t.v_npt == 2 || t.v_npt == 4 || t.v_npt == 6 || t.v_npt == 8) c.npt = t.v_npt;
+    // ring depth: the decision warp runs a ring ahead, 2 nf stages <= a chunk; one head per ring gains nothing beyond
+    // four stages (measured: 4, 6 and 8 alike), heads that share a ring wait for each other and use what fits
+    int nf = gh == 1 ? 4 : c.sch / 2;
     if (t.v_nf > 0 && t.v_nf < nf) nf = t.v_nf;
     nf &= ~1;                                              // even: a ring slot's stages all belong to one decision warp
+    // (one head per ring: a table per ring slot)
+    while (nf > 2 && vch::plan(nf, c.nside, c.sch, gh == 1 ? nf : c.npt, c.upc, gh).bytes > budget) nf -= 2;
     if (nf < 2) nf = 2;
     c.nf = nf;
-    c.smem = c.upc * ((vch::plan(c.nf, c.nside, c.sch).bytes + 127) & ~127);
+    if (gh == 1) c.npt = nf;
+    c.smem = vch::plan(c.nf, c.nside, c.sch, c.npt, c.upc, gh).bytes;
     return c;
 }
 
-template <int UPC>
-static int launch_v_chain_u(VParams& p, const VChainCfg& c, int BH, cudaStream_t st) {
+template <int UPC, int GH>
+static int launch_v_chain_u(VParams& p, const VChainCfg& c, long long heads, cudaStream_t st) {
     static bool configured[64] = {false};   // the attribute is per device (one array per instantiation)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(v_chain_kernel<UPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(v_chain_kernel<UPC, GH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              max_dyn_smem());
         if (e != cudaSuccess) return cuda_status(e, "v_cache_compute smem attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     AKV_REQUIRE(c.smem <= max_dyn_smem(), AKV_ERR_CUDA, "v_cache_compute: %d bytes of shared memory are too many", c.smem);
-    p.nf = c.nf; p.nside = c.nside; p.sch = c.sch; p.units = BH;
-    launch_chained(v_chain_kernel<UPC>, dim3((BH + UPC - 1) / UPC), dim3(UPC * 128), (size_t)c.smem, st, p);
+    p.nf = c.nf; p.nside = c.nside; p.sch = c.sch; p.npt = c.npt;
+    p.units = (int)(heads / GH);
+    const int grid = (p.units + UPC - 1) / UPC;
+    launch_chained(v_chain_kernel<UPC, GH>, dim3(grid), dim3((3 * UPC * GH + UPC) * 32), (size_t)c.smem, st, p);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
 }
 
@@ -554,15 +558,19 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
     const int BH = bsz * H;
     const bool fast = v_compute_takes_probe(first8, mid4, last4, s, o, group, D, s_last_dim, n);
     AKV_REQUIRE(fast || !test_o, AKV_ERR_SHAPE, "v_cache_compute: the probe form needs the streaming kernel");
-    // The chain form has one unit per (batch, QUERY head).  With grouped queries the heads of a group re-read their
-    // KV head's planes (from L2), which pays while the units fit one wave of CTAs (98 -> 61 us for 8 x 8 KV heads x 4
-    // query heads x 8192 tokens); beyond that the grouped kernel below, which stages every plane byte once for the
-    // whole group, is as fast or faster.
-    const long long units = (long long)BH * group;
-    const bool chain_form = group == 1 || units <= (long long)tuning().v_gqa_chain_waves * 2 * sm_count();
-    if (fast && chain_form && !reference && tuning().v_impl == 0) {
-        const VChainCfg c = v_chain_config((int)units, reference);
-        return c.upc == 2 ? launch_v_chain_u<2>(p, c, (int)units, st) : launch_v_chain_u<1>(p, c, (int)units, st);
+    const long long heads = (long long)BH * group;
+    if (fast && !reference && tuning().v_impl == 0 && heads < (1ll << 30)) {
+        // grouped queries: the heads of a KV head share one ring of high bytes in a CTA (gh = group); the form with
+        // one ring per query head, whose heads meet in L2, stays selectable for measurements
+        // (measured at 8192 tokens, 8 KV heads x 4: batch 8: 98 us grouped kernel, 84 shared ring, 65 ring per head;
+        // batch 16: 117 / 102 / 125): a ring per head while the heads fit one wave of CTAs, else the shared ring
+        const int w = tuning().v_gqa_chain_waves;
+        const bool per_head = group == 1 || w == 1 || (w == 0 && heads <= 2ll * sm_count());
+        const int gh = per_head ? 1 : group;
+        const VChainCfg c = v_chain_config(heads, gh, reference);
+        if (gh == 4) return launch_v_chain_u<1, 4>(p, c, heads, st);
+        if (gh == 2) return launch_v_chain_u<1, 2>(p, c, heads, st);
+        return c.upc == 2 ? launch_v_chain_u<2, 1>(p, c, heads, st) : launch_v_chain_u<1, 1>(p, c, heads, st);
     }
     if (fast && group == 1) return launch_v_fast<1, 6, 2, 1>(p, BH, st);
     if (fast && group == 2) return launch_v_fast<2, 6, 2, 2>(p, BH, st);
