@@ -27,6 +27,7 @@
 //     A run has two code paths (lean / not lean), chosen once per run; there is no per-token branch.
 // Every wait is time-bounded; a wait that gives up raises a flag the host can read (akv_device_error_flag).
 #include "akv_v_chain.cuh"
+#include "akv_v_stream.cuh"
 
 namespace akv {
 
@@ -636,6 +637,19 @@ int launch_v_probe(const uint8_t* first8, const uint8_t* s_val, const uint8_t* s
                    reinterpret_cast<const uint16_t*>(s_val), reinterpret_cast<const int32_t*>(s_idx),
                    reinterpret_cast<uint16_t*>(out), max_seq_len, D, K, group);
     return cuda_status(cudaGetLastError(), "v_cache_test_compute launch");
+}
+
+// Split pass of the order-free P.V in its streaming form (akv_v_stream.cuh), for akv_v_split.cu.
+int launch_v_split_stream(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                          const uint8_t* amin, float* partial, int BH, int max_seq_len, int s_last_dim, int n,
+                          int chunk_tokens, int chunks, cudaStream_t st) {
+    VStreamParams p;
+    p.first8 = first8; p.mid4 = mid4; p.last4 = last4;
+    p.s = reinterpret_cast<const uint16_t*>(s);
+    p.amin = amin; p.partial = partial;
+    p.max_seq_len = max_seq_len; p.s_last_dim = s_last_dim; p.n = n;
+    p.chunk_tokens = chunk_tokens; p.chunks = chunks; p.nf = 0;
+    return launch_v_stream(p, BH, st);
 }
 
 }  // namespace akv

@@ -190,6 +190,21 @@ static void split_plan(int BH, int n, int* chunk_tokens, int* chunks) {
     *chunks = n > 0 ? (n + ct - 1) / ct : 1;
 }
 
+// The streaming form (akv_v_stream.cuh; multi-head attention, aligned mode) wants about three long-lived CTAs per SM:
+// fewer, longer chunks than the direct form - so the direct form's plan bounds the scratch of both.
+static void stream_plan(int BH, int n, int* chunk_tokens, int* chunks) {
+    const int target = sm_count() * 3;
+    int want = (target + BH - 1) / BH;
+    if (want < 1) want = 1;
+    int ct = (n + want - 1) / want;
+    ct = ((ct + 127) / 128) * 128;
+    if (ct < 512) ct = 512;
+    *chunk_tokens = ct;
+    *chunks = n > 0 ? (n + ct - 1) / ct : 1;
+}
+int launch_v_split_stream(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, float*, int, int,
+                          int, int, int, int, cudaStream_t);
+
 long long v_split_scratch_bytes(int bsz, int H, int group, int n) {
     int ct, ch;
     split_plan(bsz * H, n, &ct, &ch);
@@ -212,6 +227,16 @@ int launch_v_split(const uint8_t* first8, const uint8_t* mid4, const uint8_t* la
     p.amin = amin;
     p.partial = scratch;
     p.max_seq_len = max_seq_len; p.s_last_dim = s_last_dim; p.n = n; p.reference = reference;
+    int rc;
+    if (group == 1 && !reference && tuning().v_split_impl == 0 && n >= 512) {
+        stream_plan(bsz * H, n, &p.chunk_tokens, &p.chunks);
+        count_launch();   // the combine
+        rc = launch_v_split_stream(first8, mid4, last4, s, amin, scratch, bsz * H, max_seq_len, s_last_dim, n,
+                                   p.chunk_tokens, p.chunks, st);
+        if (rc != AKV_OK) return rc;
+        v_combine_kernel<<<bsz * H * group, 128, 0, st>>>(scratch, reinterpret_cast<__half*>(o16), o32, p.chunks, D);
+        return cuda_status(cudaGetLastError(), "v_cache_compute (order-free) combine launch");
+    }
     split_plan(bsz * H, n, &p.chunk_tokens, &p.chunks);
     dim3 grid(p.chunks, bsz * H);
     count_launch(2);   // the split pass and the combine
@@ -219,7 +244,7 @@ int launch_v_split(const uint8_t* first8, const uint8_t* mid4, const uint8_t* la
     else if (group == 2) v_split_kernel<2><<<grid, 128, 0, st>>>(p);
     else if (group == 4) v_split_kernel<4><<<grid, 128, 0, st>>>(p);
     else v_split_kernel<8><<<grid, 128, 0, st>>>(p);
-    int rc = cuda_status(cudaGetLastError(), "v_cache_compute (order-free) launch");
+    rc = cuda_status(cudaGetLastError(), "v_cache_compute (order-free) launch");
     if (rc != AKV_OK) return rc;
     v_combine_kernel<<<bsz * H * group, 128, 0, st>>>(scratch, reinterpret_cast<__half*>(o16), o32, p.chunks, D);
     return cuda_status(cudaGetLastError(), "v_cache_compute (order-free) combine launch");

@@ -54,6 +54,8 @@ def v_state(seed, B, H, L, max_len, D=128):
 @pytest.mark.parametrize("B,H,G,n,max_len,amin_val", [
     (2, 4, 1, 512, 512, 13),
     (1, 2, 1, 1000, 1024, 14),      # ragged token count (not a multiple of 8, 32 or 64)
+    (1, 3, 1, 4500, 4608, 13),      # several chunks per head, ragged last stage (order-free: streaming form)
+    (1, 2, 1, 2048, 2048, 3),       # a low threshold: many tokens read the nibble planes, several per lane
     (2, 2, 4, 640, 768, 13),        # grouped-query: 4 query heads per KV head, different probabilities each
     (1, 2, 2, 256, 256, 15),
     (1, 1, 8, 320, 320, 13),
