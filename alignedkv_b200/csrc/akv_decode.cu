@@ -27,6 +27,10 @@ int launch_v_compute_probe(const uint8_t*, const uint8_t*, const uint8_t*, const
                            const uint8_t*, uint8_t*, int, int, int, int, int, int, int, int, cudaStream_t);
 int launch_v_split(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, float*,
                    float*, int, int, int, int, int, int, int, int, cudaStream_t);
+int launch_v_split_probe(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, const uint8_t*,
+                         const uint8_t*, uint8_t*, float*, float*, int*, int, int, int, int, int, int, int, int,
+                         cudaStream_t);
+bool v_split_takes_probe(int, int, int);
 long long v_split_scratch_bytes(int, int, int, int);
 int launch_v_probe(const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int, int,
                    cudaStream_t);
@@ -505,7 +509,7 @@ amin_kernel(const uint16_t* __restrict__ test_o, const uint8_t* __restrict__ v_e
 __global__ void __launch_bounds__(256)
 tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_main32, const uint16_t* __restrict__ p,
             const __half* __restrict__ restv, __half* __restrict__ out, const float* __restrict__ stats,
-            float* __restrict__ packed, int H, int G, int D, int R, int qn, int rest) {
+            float* __restrict__ packed, int H, int G, int D, int R, int qn, int rest, int chunks) {
     pdl_enter();
     const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     // residual sum: item = (channel pair, quarter g of the tokens: r = g, g+4, ...), all of an item's loads in flight
@@ -542,7 +546,12 @@ tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_mai
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         const float acc = rest > 0 ? ((part[0][d] + part[1][d]) + part[2][d]) + part[3][d] : 0.f;
         float v;
-        if (o_main32) v = o_main32[(size_t)bhq * D + d] + acc;
+        if (o_main32 && chunks > 0) {
+            // o_main32 holds the order-free kernel's chunk partials [chunks][D] of this row: added in chunk order
+            float m = 0.f;
+            for (int c = 0; c < chunks; ++c) m += o_main32[((size_t)bhq * chunks + c) * D + d];
+            v = m + acc;
+        } else if (o_main32) v = o_main32[(size_t)bhq * D + d] + acc;
         else v = (o_main ? __half2float(__ushort_as_half(o_main[(size_t)bhq * D + d])) : 0.f) +
                  __half2float(__float2half_rn(acc));
         if (out) out[(size_t)bhq * D + d] = __float2half_rn(v);
@@ -806,6 +815,7 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
     }
     if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
     const bool need_tail = rest > 0 || qn == 0 || packed_out != nullptr || order_free;
+    int v_chunks = 0;       // order-free P.V: chunk partials per row left for the tail kernel to add up
     if (qn > 0) {
         if (!probed) {
             rc = launch_v_probe(static_cast<const uint8_t*>(v_first_8), reinterpret_cast<const uint8_t*>(sc.pval),
@@ -815,10 +825,11 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
         }
         // the exact-order kernel derives the threshold bytes from the probe result in its prologue when it runs its
         // streaming form; otherwise a small kernel does
-        const bool v_takes_probe = !order_free && v_compute_takes_probe(static_cast<const uint8_t*>(v_first_8),
-            static_cast<const uint8_t*>(v_mid_4), static_cast<const uint8_t*>(v_last_4),
-            reinterpret_cast<const uint8_t*>(sc.s), need_tail ? (const uint8_t*)sc.o_main : (const uint8_t*)out, G, D, R,
-            qn);
+        const bool v_takes_probe = order_free
+            ? v_split_takes_probe(G, reference, qn)
+            : v_compute_takes_probe(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                                    static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s),
+                                    need_tail ? (const uint8_t*)sc.o_main : (const uint8_t*)out, G, D, R, qn);
         if (!v_takes_probe) {
             launch_chained(amin_kernel, dim3((B * H * G + 3) / 4), dim3(128), 0, st, (const uint16_t*)sc.test_o,
                            static_cast<const uint8_t*>(v_exp_max), sc.amin, B * H * G, H, G, D);
@@ -826,9 +837,12 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
         }
         if (ev) cudaEventRecord(ev[2], st);
         if (order_free)
-            rc = launch_v_split(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
-                                static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s), sc.amin,
-                                nullptr, sc.o_main32, sc.partial, B, H, G, max_seq_len, D, R, qn, reference, st);
+            // the chunk partials stay in the workspace: the tail kernel adds them up (one launch less)
+            rc = launch_v_split_probe(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                                      static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s),
+                                      sc.amin, v_takes_probe ? (const uint8_t*)sc.test_o : nullptr,
+                                      static_cast<const uint8_t*>(v_exp_max), nullptr, nullptr, sc.partial, &v_chunks, B,
+                                      H, G, max_seq_len, D, R, qn, reference, st);
         else
             rc = launch_v_compute_probe(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
                                         static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s),
@@ -846,9 +860,9 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
     if (need_tail) {
         launch_chained(tail_kernel, dim3(B * H * G), dim3(256), 0, st,
                        (const uint16_t*)((qn > 0 && !order_free) ? sc.o_main : nullptr),
-                       (const float*)(order_free ? sc.o_main32 : nullptr), (const uint16_t*)sc.s,
+                       (const float*)(order_free ? (v_chunks > 0 ? sc.partial : sc.o_main32) : nullptr), (const uint16_t*)sc.s,
                        static_cast<const __half*>(restv), static_cast<__half*>(out), (const float*)sc.stats,
-                       static_cast<float*>(packed_out), H, G, D, R, qn, rest);
+                       static_cast<float*>(packed_out), H, G, D, R, qn, rest, v_chunks);
         if ((rc = cuda_status(cudaGetLastError(), "decode_step tail launch")) != AKV_OK) return rc;
     }
     return AKV_OK;
@@ -987,7 +1001,7 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
     g_shard_timing = nullptr;
     launch_chained(tail_kernel, dim3(rows), dim3(256), 0, st, (const uint16_t*)nullptr, (const float*)sc.o_main32,
                    (const uint16_t*)sc.s, static_cast<const __half*>(restv), static_cast<__half*>(nullptr),
-                   (const float*)sc.stats, static_cast<float*>(exch_out), H, G, D, R, qn, rest);
+                   (const float*)sc.stats, static_cast<float*>(exch_out), H, G, D, R, qn, rest, 0);
     return cuda_status(cudaGetLastError(), "shard_step tail launch");
 }
 

@@ -641,12 +641,13 @@ int launch_v_probe(const uint8_t* first8, const uint8_t* s_val, const uint8_t* s
 
 // Split pass of the order-free P.V in its streaming form (akv_v_stream.cuh), for akv_v_split.cu.
 int launch_v_split_stream(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
-                          const uint8_t* amin, float* partial, int BH, int max_seq_len, int s_last_dim, int n,
-                          int chunk_tokens, int chunks, cudaStream_t st) {
+                          uint8_t* amin, const uint8_t* test_o, const uint8_t* v_exp, int H, float* partial, int BH,
+                          int max_seq_len, int s_last_dim, int n, int chunk_tokens, int chunks, cudaStream_t st) {
     VStreamParams p;
     p.first8 = first8; p.mid4 = mid4; p.last4 = last4;
     p.s = reinterpret_cast<const uint16_t*>(s);
     p.amin = amin; p.partial = partial;
+    p.test_o = reinterpret_cast<const uint16_t*>(test_o); p.v_exp = v_exp; p.amin_out = amin; p.H = H;
     p.max_seq_len = max_seq_len; p.s_last_dim = s_last_dim; p.n = n;
     p.chunk_tokens = chunk_tokens; p.chunks = chunks; p.nf = 0;
     return launch_v_stream(p, BH, st);

@@ -202,8 +202,13 @@ static void stream_plan(int BH, int n, int* chunk_tokens, int* chunks) {
     *chunk_tokens = ct;
     *chunks = n > 0 ? (n + ct - 1) / ct : 1;
 }
-int launch_v_split_stream(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, float*, int, int,
-                          int, int, int, int, cudaStream_t);
+int launch_v_split_stream(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, const uint8_t*,
+                          const uint8_t*, int, float*, int, int, int, int, int, int, cudaStream_t);
+
+// true when launch_v_split_probe runs the streaming form, which can compute the threshold bytes itself
+bool v_split_takes_probe(int group, int reference, int n) {
+    return group == 1 && !reference && tuning().v_split_impl == 0 && n >= 512;
+}
 
 long long v_split_scratch_bytes(int bsz, int H, int group, int n) {
     int ct, ch;
@@ -212,15 +217,23 @@ long long v_split_scratch_bytes(int bsz, int H, int group, int n) {
 }
 
 // Order-free P.V over n quantized tokens (head_dim 128).  o16 / o32: [B, Hq, D], either may be null.
-int launch_v_split(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
-                   const uint8_t* amin, uint8_t* o16, float* o32, float* scratch, int bsz, int H, int group,
-                   int max_seq_len, int D, int s_last_dim, int n, int reference, cudaStream_t st) {
+// test_o != nullptr (only when v_split_takes_probe() holds): the threshold bytes are computed in the kernel from the
+// probe result and the exponent maxima v_exp and written to amin; otherwise they are read from amin.
+// o16 == o32 == nullptr: the chunk partials are left in `scratch` for the caller to add up, in chunk order
+// (*chunks_out of them per (batch, query head), D floats each).
+int launch_v_split_probe(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                         uint8_t* amin, const uint8_t* test_o, const uint8_t* v_exp, uint8_t* o16, float* o32,
+                         float* scratch, int* chunks_out, int bsz, int H, int group, int max_seq_len, int D,
+                         int s_last_dim, int n, int reference, cudaStream_t st) {
     AKV_REQUIRE(D == 128, AKV_ERR_SHAPE, "v_cache_compute (order-free): head_dim %d is not supported (128 only)", D);
     AKV_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8, AKV_ERR_SHAPE,
                 "v_cache_compute (order-free): group size %d is not supported (1, 2, 4, 8)", group);
     AKV_REQUIRE(aligned16(first8) && (reinterpret_cast<uintptr_t>(mid4) & 7u) == 0 &&
                 (reinterpret_cast<uintptr_t>(last4) & 7u) == 0 && aligned16(s) && s_last_dim % 8 == 0 &&
                 aligned16(scratch), AKV_ERR_ALIGN, "v_cache_compute (order-free): misaligned pointer or row stride");
+    AKV_REQUIRE(!test_o || v_split_takes_probe(group, reference, n), AKV_ERR_SHAPE,
+                "v_cache_compute (order-free): the probe form needs the streaming kernel");
+    const bool combine = o16 != nullptr || o32 != nullptr;
     VSplitParams p;
     p.first8 = first8; p.mid4 = mid4; p.last4 = last4;
     p.s = reinterpret_cast<const uint16_t*>(s);
@@ -230,24 +243,33 @@ int launch_v_split(const uint8_t* first8, const uint8_t* mid4, const uint8_t* la
     int rc;
     if (group == 1 && !reference && tuning().v_split_impl == 0 && n >= 512) {
         stream_plan(bsz * H, n, &p.chunk_tokens, &p.chunks);
+        if (chunks_out) *chunks_out = p.chunks;
+        rc = launch_v_split_stream(first8, mid4, last4, s, amin, test_o, v_exp, H, scratch, bsz * H, max_seq_len,
+                                   s_last_dim, n, p.chunk_tokens, p.chunks, st);
+        if (rc != AKV_OK || !combine) return rc;
         count_launch();   // the combine
-        rc = launch_v_split_stream(first8, mid4, last4, s, amin, scratch, bsz * H, max_seq_len, s_last_dim, n,
-                                   p.chunk_tokens, p.chunks, st);
-        if (rc != AKV_OK) return rc;
         v_combine_kernel<<<bsz * H * group, 128, 0, st>>>(scratch, reinterpret_cast<__half*>(o16), o32, p.chunks, D);
         return cuda_status(cudaGetLastError(), "v_cache_compute (order-free) combine launch");
     }
     split_plan(bsz * H, n, &p.chunk_tokens, &p.chunks);
+    if (chunks_out) *chunks_out = p.chunks;
     dim3 grid(p.chunks, bsz * H);
-    count_launch(2);   // the split pass and the combine
+    count_launch(combine ? 2 : 1);   // the split pass and the combine
     if (group == 1) v_split_kernel<1><<<grid, 128, 0, st>>>(p);
     else if (group == 2) v_split_kernel<2><<<grid, 128, 0, st>>>(p);
     else if (group == 4) v_split_kernel<4><<<grid, 128, 0, st>>>(p);
     else v_split_kernel<8><<<grid, 128, 0, st>>>(p);
     rc = cuda_status(cudaGetLastError(), "v_cache_compute (order-free) launch");
-    if (rc != AKV_OK) return rc;
+    if (rc != AKV_OK || !combine) return rc;
     v_combine_kernel<<<bsz * H * group, 128, 0, st>>>(scratch, reinterpret_cast<__half*>(o16), o32, p.chunks, D);
     return cuda_status(cudaGetLastError(), "v_cache_compute (order-free) combine launch");
+}
+
+int launch_v_split(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                   const uint8_t* amin, uint8_t* o16, float* o32, float* scratch, int bsz, int H, int group,
+                   int max_seq_len, int D, int s_last_dim, int n, int reference, cudaStream_t st) {
+    return launch_v_split_probe(first8, mid4, last4, s, const_cast<uint8_t*>(amin), nullptr, nullptr, o16, o32, scratch,
+                                nullptr, bsz, H, group, max_seq_len, D, s_last_dim, n, reference, st);
 }
 
 // ------------------------------------------------------------------ log-sum-exp merge of per-rank partial results

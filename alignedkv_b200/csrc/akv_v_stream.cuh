@@ -28,6 +28,12 @@ struct VStreamParams {
     const uint8_t* last4;
     const uint16_t* s;      // probabilities, one row per (batch, head)
     const uint8_t* amin;    // threshold byte per (batch, head)
+    // test_o != nullptr: every CTA computes its head's threshold byte itself from the probe result [B,H,D] and the
+    // exponent maxima [B,H,D] (v_threshold_warp), and chunk 0 stores it to amin_out
+    const uint16_t* test_o;
+    const uint8_t* v_exp;
+    uint8_t* amin_out;
+    int H;
     float* partial;         // [B*H, chunks, D]
     int max_seq_len, s_last_dim, n, chunk_tokens, chunks, nf;
 };
@@ -136,7 +142,14 @@ __global__ void __launch_bounds__(160) v_stream_kernel(const VStreamParams p) {
         const uint8_t* M = p.mid4 + (size_t)bh * p.max_seq_len * HD + cg * 8;
         const uint8_t* L = p.last4 + (size_t)bh * p.max_seq_len * HD + cg * 8;
         const uint16_t* s_row = p.s + (size_t)bh * p.s_last_dim;
-        const uint32_t A = ((uint32_t)p.amin[bh] << 10) & 0xFFFFu;
+        uint32_t a8;
+        if (p.test_o) {
+            a8 = v_threshold_warp(p.test_o, p.v_exp, bh, p.H, 1, D, lane);
+            if (chunk == 0 && warp == 0 && lane == 0) p.amin_out[bh] = (uint8_t)a8;
+        } else {
+            a8 = p.amin[bh];
+        }
+        const uint32_t A = (a8 << 10) & 0xFFFFu;
         const int n8 = (p.n + 7) & ~7;                       // readable extent of the probability row
         bool alive = true;
         // probabilities of this lane's 16 tokens of a stage (two 16-byte loads; the row is padded to 8 values)
