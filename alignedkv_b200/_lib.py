@@ -17,6 +17,7 @@ SIGNATURES = {
     "akv_last_error": (ctypes.c_char_p, []),
     "akv_set_tuning": (_I, [ctypes.c_char_p, _I]),
     "akv_device_error_flag": (_I, []),
+    "akv_device_error_clear": (_I, []),
     "akv_launch_count": (ctypes.c_longlong, []),
     "akv_k_cache_save": (_I, [_P] * 4 + [_I] * 8 + [_P]),
     "akv_k_cache_compute": (_I, [_P] * 7 + [_I] * 7 + [_F, _I, _P]),

@@ -663,3 +663,11 @@ extern "C" int akv_device_error_flag(void) {
     if (e != cudaSuccess) return akv::cuda_status(e, "device_error_flag");
     return (int)v;
 }
+
+extern "C" int akv_device_error_clear(void) {
+    // Puts the flag back to zero (after the caller has dealt with a run that raised it).  Synchronises the device.
+    const unsigned int v = 0;
+    cudaError_t e = cudaMemcpyToSymbol(akv::g_v_wait_gave_up, &v, sizeof(v));
+    if (e != cudaSuccess) return akv::cuda_status(e, "device_error_clear");
+    return AKV_OK;
+}

@@ -44,6 +44,13 @@ const char* akv_last_error(void);
  * Reading it copies a word from the device, i.e. synchronises; negative values are AKV_ERR_* codes.
  */
 int akv_device_error_flag(void);
+/*
+ * Sets the flag back to zero; returns 0 or a negative AKV_ERR_* code.  The flag is per process and device image and
+ * sticky: poll it where a wrong output would matter and a synchronisation is affordable (end of a request, of a
+ * benchmark run, of a test), and clear it after handling the failure.  A P.V kernel whose wait ran out also writes
+ * NaN into the rows it could not finish, so an unpolled failure cannot pass for a result.
+ */
+int akv_device_error_clear(void);
 
 /*
  * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16, "k_gqa_kch" 8|16,
