@@ -61,6 +61,7 @@ class DecodeLayer:
             raise ValueError("bad extents")
         self.scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._static_ptrs = None
         self.launches = 0
 
     @property
@@ -150,16 +151,24 @@ class DecodeLayer:
         if out is None and not packed:
             out = torch.empty((B, 1, Hq, D), dtype=torch.half, device=self.device)
         rec = torch.empty((B * Hq, D + 2), dtype=torch.float32, device=self.device) if packed else None
-        with torch.cuda.device(self.device):
-            rc = self.lib.akv_decode_step_masked(
-                self.k_first_8.data_ptr(), self.k_mid_4.data_ptr(), self.k_last_4.data_ptr(),
-                self.v_first_8.data_ptr(), self.v_mid_4.data_ptr(), self.v_last_4.data_ptr(),
-                self.k_exp_max.data_ptr(), self.v_exp_max.data_ptr(), self.restk.data_ptr(), self.restv.data_ptr(),
-                q.data_ptr(), k.data_ptr() if append else None, v.data_ptr() if append else None,
-                out.data_ptr() if out is not None else None, rec.data_ptr() if rec is not None else None,
-                mask_ptr, mask_stride,
-                self.scratch.data_ptr(), self.scratch.numel(), B, H, self.G, D, self.L, self.rest_len, self.rest_start,
-                self._flags(append), torch.cuda.current_stream(self.device).cuda_stream)
+        # (the planes, exponent maxima, residual buffers and the workspace never move: their addresses are taken once;
+        # the device is only switched when it is not the current one - both keep the host's share of a step small,
+        # which is what bounds a rank whose CPU is slow)
+        ptrs = self._static_ptrs
+        if ptrs is None:
+            ptrs = self._static_ptrs = tuple(t.data_ptr() for t in (
+                self.k_first_8, self.k_mid_4, self.k_last_4, self.v_first_8, self.v_mid_4, self.v_last_4,
+                self.k_exp_max, self.v_exp_max, self.restk, self.restv)) + (self.scratch.data_ptr(), self.scratch.numel())
+        args = ptrs[:10] + (
+            q.data_ptr(), k.data_ptr() if append else None, v.data_ptr() if append else None,
+            out.data_ptr() if out is not None else None, rec.data_ptr() if rec is not None else None,
+            mask_ptr, mask_stride, ptrs[10], ptrs[11], B, H, self.G, D, self.L, self.rest_len, self.rest_start,
+            self._flags(append), torch.cuda.current_stream(self.device).cuda_stream)
+        if torch.cuda.current_device() == self.device.index:
+            rc = self.lib.akv_decode_step_masked(*args)
+        else:
+            with torch.cuda.device(self.device):
+                rc = self.lib.akv_decode_step_masked(*args)
         _lib.check("decode_step", rc)
         self.last_q = q                                   # (for bytes_accounting)
         flush = append and self.rest_len + 1 == column_block

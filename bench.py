@@ -225,11 +225,12 @@ class ClockSampler:
         except OSError:
             return None
         rows = rows_in or rows_all[-3:]
-        sm, reasons, mx = [], set(), None
+        sm, reasons, mx, pw = [], set(), None, []
         for r in rows:
             try:
                 sm.append(float(r[1]))
                 mx = float(r[2])
+                pw.append(float(r[3]))
             except (ValueError, IndexError):
                 continue
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
@@ -237,7 +238,8 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return None
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm),
+                "power_w": statistics.median(pw) if pw else None}
 
 
 # ---------------------------------------------------------------------------------------------- our arm
@@ -427,11 +429,17 @@ def measure(name, args, ctx, min_seconds):
 
     # ---- the headline: runs of consecutive decode tokens from cache_len cached tokens (the state the step above left)
     run["snap"] = owner.snapshot()
-    sampler = ClockSampler(ctx["local"]) if rank == 0 else None
-    if sampler:
-        sampler.start()
+    sampler = ClockSampler(ctx["local"])                   # every rank watches its own GPU
+    sampler.start()
     blocks, per_rank, t0, t1, counts = timed_blocks(step_resident, args.steps, warm, min_seconds, in_run)   # no instrumentation inside
-    clocks = sampler.stop(t0, time.time()) if sampler else None
+    clocks = sampler.stop(t0, time.time())
+    if world > 1:
+        # the block time is the maximum over the ranks: the clocks and power of every rank's GPU beside its own times
+        every = [None] * world
+        dist.all_gather_object(every, clocks)
+        if clocks is not None:
+            clocks = dict(clocks, per_rank=[None if c is None else {k_: c[k_] for k_ in ("sm_mhz", "power_w", "reasons")}
+                                            for c in every])
     launches = int(statistics.median(counts))              # kernels of this library per timed block (its own counter)
     # whole runs per block: all blocks are alike, take the median; else the blocks differ (some hold the flush and the
     # rewind, some do not) and the mean is the cost per token
