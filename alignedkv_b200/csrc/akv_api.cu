@@ -96,7 +96,7 @@ int akv_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "v_nside") && (value == 0 || value == 128 || value == 256 || value == 512))
         t.v_nside = value;
     else if (!strcmp(key, "v_cps") && value >= 0 && value <= 8) t.v_cps = value;
-    else if (!strcmp(key, "v_gqa_chain_waves") && value >= 0 && value <= 64) t.v_gqa_chain_waves = value;
+    else if (!strcmp(key, "v_gqa_form") && value >= 0 && value <= 2) t.v_gqa_form = value;
     else if (!strcmp(key, "v_npt") && value >= 0 && value <= 8) t.v_npt = value;
     else if (!strcmp(key, "v_split_impl") && (value == 0 || value == 1)) t.v_split_impl = value;
     else if (!strcmp(key, "v_upc") && value >= 0 && value <= 2) t.v_upc = value;

@@ -28,7 +28,7 @@ struct Tuning {
     int v_nside = 0;    // exact P.V (form 0): rows of the nibble side ring, a power of two >= 128 (0 = default)
     int v_cps = 0;      // exact P.V (form 0): CTAs per SM the shared-memory budget is cut for (0 = one wave)
     int v_upc = 0;      // exact P.V (form 0): (batch, head) units per CTA, 1 or 2 (0 = default)
-    int v_gqa_chain_waves = 0;   // exact P.V, grouped queries (form 0): 0 = by size, 1 = one ring per query head, 2 = the group's heads share a ring
+    int v_gqa_form = 0;   // exact P.V, grouped queries (form 0): 0 = by size, 1 = one ring per query head, 2 = the group's heads share a ring
     int v_npt = 0;      // exact P.V (form 0): low-byte tables per head, 2, 4, 6 or 8 (0 = default)
     int v_split_impl = 0;   // order-free P.V, multi-head, aligned mode: 0 = staged through shared memory by bulk copies, 1 = direct loads
 };

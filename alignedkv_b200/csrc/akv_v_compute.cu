@@ -565,7 +565,7 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
         // one ring per query head, whose heads meet in L2, stays selectable for measurements
         // (measured at 8192 tokens, 8 KV heads x 4: batch 8: 98 us grouped kernel, 84 shared ring, 65 ring per head;
         // batch 16: 117 / 102 / 125): a ring per head while the heads fit one wave of CTAs, else the shared ring
-        const int w = tuning().v_gqa_chain_waves;
+        const int w = tuning().v_gqa_form;
         const bool per_head = group == 1 || w == 1 || (w == 0 && heads <= 2ll * sm_count());
         const int gh = per_head ? 1 : group;
         const VChainCfg c = v_chain_config(heads, gh, reference);

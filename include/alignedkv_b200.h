@@ -54,8 +54,12 @@ int akv_device_error_clear(void);
 
 /*
  * Launch-shape knobs for benchmarking ("k_kch" 8|16, "k_stages" 3..6, "k_wpc" 0..16, "k_gqa_kch" 8|16,
- * "timing" 0|1, "pdl" 0|1: chain the kernels of a decode step with programmatic dependent launch).
- * Process-wide; results never depend on them.  No counterpart in the reference.
+ * "timing" 0|1, "pdl" 0|1: chain the kernels of a decode step with programmatic dependent launch; exact P.V:
+ * "v_impl" 0 chain kernel | 1 producer-transposed kernel, "v_nf" ring depth cap, "v_nside" side-ring rows, "v_upc"
+ * rings per CTA, "v_npt" low-byte tables per head, "v_gqa_form" 0 by size | 1 a ring per query head | 2 one ring per
+ * KV head; order-free P.V: "v_split_impl" 0 staged through shared memory | 1 direct loads).
+ * Process-wide; results never depend on them (the order-free forms agree within their tolerance, every exact form
+ * bit for bit).  Returns 0, or AKV_ERR_SHAPE for an unknown key or value.  No counterpart in the reference.
  */
 int akv_set_tuning(const char* key, int value);
 

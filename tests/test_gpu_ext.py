@@ -106,6 +106,42 @@ def test_v_compute_gqa_and_order_free(akv_lib, B, H, G, n, max_len, amin_val, re
     assert lib.akv_device_error_flag() == 0
 
 
+@pytest.mark.parametrize("form", [1, 2])
+@pytest.mark.parametrize("B,H,G,n,max_len,amin_val", [
+    (2, 3, 4, 1100, 1152, 13),      # ragged token count, several stages, four query heads per KV head
+    (1, 2, 2, 640, 640, 14),
+    (1, 2, 4, 2048, 2048, 11),      # a low threshold: many stages hold flagged tokens (the tables are handed around)
+])
+def test_v_chain_grouped_forms(akv_lib, form, B, H, G, n, max_len, amin_val):
+    """Exact P.V with grouped queries through both forms of the chain kernel - a ring per query head (1) and one ring
+    shared by the heads of a KV head (2) - bit-exact against the oracle on repeated heads."""
+    from oracle import akv_oracle as orc
+    lib = akv_lib
+    D, Hq = 128, H * G
+    _, planes = v_state(33, B, H, n, max_len)
+    pad = (-n) % 8
+    p = softmax_probs(34, B, Hq, n, pad=pad)
+    amin = np.full((B, Hq, 1, 1), amin_val, np.uint8)
+    amin[0, 1] = amin_val - 1
+    exp_planes = [np.ascontiguousarray(np.repeat(x, G, axis=1)) for x in planes]
+    want_u8, _ = orc.v_cache_compute(*exp_planes, u8(p), amin, B, Hq, max_len, D, n + pad, n, False)
+    want = want_u8.view(np.float16).reshape(B, Hq, D)
+    dp = [dev(x) for x in planes]
+    ds, da = dev(u8(p)), dev(amin)
+    out = torch.empty((B, Hq, 1, D), dtype=torch.half, device="cuda")
+    assert lib.akv_set_tuning(b"v_gqa_form", form) == 0
+    try:
+        check(lib, lib.akv_v_cache_compute_gqa(dp[0].data_ptr(), dp[1].data_ptr(), dp[2].data_ptr(), ds.data_ptr(),
+                                               da.data_ptr(), out.data_ptr(), None, 0, B, H, G, max_len, D, n + pad, n,
+                                               0, stream()))
+        torch.cuda.synchronize()
+    finally:
+        lib.akv_set_tuning(b"v_gqa_form", 0)
+    got = out.cpu().numpy().reshape(B, Hq, D)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), "grouped P.V (chain kernel) differs from the oracle"
+    assert lib.akv_device_error_flag() == 0
+
+
 @pytest.mark.parametrize("B,H,G,nb,nmb", [(2, 2, 4, 6, 8), (1, 4, 2, 3, 3), (1, 1, 8, 9, 12)])
 @pytest.mark.parametrize("reference", [False, True])
 def test_k_compute_gqa(akv_lib, B, H, G, nb, nmb, reference):
