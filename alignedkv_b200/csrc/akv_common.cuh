@@ -30,6 +30,7 @@ struct Tuning {
     int v_upc = 0;      // exact P.V (form 0): (batch, head) units per CTA, 1 or 2 (0 = default)
     int v_gqa_form = 0;   // exact P.V, grouped queries (form 0): 0 = by size, 1 = one ring per query head, 2 = the group's heads share a ring
     int v_npt = 0;      // exact P.V (form 0): low-byte tables per head, 2, 4, 6 or 8 (0 = default)
+    int v_ndw = 0;      // exact P.V (form 0), two rings of one head each: decision warps per head, 2 or 4 (0 = default)
     int v_split_impl = 0;   // order-free P.V, multi-head, aligned mode: 0 = staged through shared memory by bulk copies, 1 = direct loads
 };
 Tuning& tuning();

@@ -23,7 +23,7 @@
 //   chain warp: all 64 channel pairs of the head, one 64-token stage per loop iteration.
 //   copy warp: stage i -> ring slot i % nf as soon as the chain has released the slot's previous stage: one 8 KB bulk
 //     asynchronous copy of the high bytes exactly as they lie in the plane.
-//   decision warp: lane = tokens (lane, lane + 32) of a stage.  EARLY part, a ring ahead of its use: takes the
+//   decision warps (two or four per head, taking the stages in turn): lane = tokens (lane, lane + 32) of a stage.  EARLY part, a ring ahead of its use: takes the
 //     probabilities from a buffer bulk-copied a chunk ahead, decides the read codes (V_cache.cu:211,250-251), reserves
 //     rows of a small side ring for the tokens that read a nibble plane and starts 64-byte copies of just those
 //     rows (one 4 KB copy when the whole stage reads a plane), counted on a barrier of their own.  LATE part, when the
@@ -244,8 +244,10 @@ __device__ __noinline__ void v_restore_low_rows(uint32_t lw, uint32_t m0, uint32
                          "r"(0x80808080u) : "memory");
 }
 
-template <int UPC, int GH>
-__global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(const VParams p) {
+// UPC rings per CTA, GH heads per ring, NDW decision warps per head (2, or 4 with two rings of one head each).
+template <int UPC, int GH, int NDW>
+__global__ void __launch_bounds__(NDW == 2 ? ((1 + NDW) * UPC * GH + UPC) * 32 : 512, 1) v_chain_kernel(const VParams p) {
+    static_assert(NDW == 2 || (NDW == 4 && UPC == 2 && GH == 1), "decision warps per head");
     using namespace vch;
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NU = UPC * GH;                   // heads of the CTA
@@ -261,11 +263,20 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
     // four schedulers by index, so with two rings of one head each chain warp shares its scheduler only with its copy
     // warp (a handful of instructions per stage) and the four decision warps have the other two; with four heads on
     // one ring every scheduler has one chain warp.
-    int role, hu;                                  // 0: chain, 1, 2: decision (even, odd stages), 3: copy; head of the CTA
-    if (wcta < NU) { role = 0; hu = wcta; }
-    else if (wcta < 2 * NU) { role = 1; hu = wcta - NU; }
-    else if (wcta < 2 * NU + UPC) { role = 3; hu = (wcta - 2 * NU) * GH; }
-    else { role = 2; hu = wcta - 2 * NU - UPC; }
+    int role, hu, dw = 0;                          // 0: chain, 1: decision (warp dw of its head), 3: copy, -1: none; head of the CTA
+    if (NDW == 2) {
+        if (wcta < NU) { role = 0; hu = wcta; }
+        else if (wcta < 2 * NU) { role = 1; hu = wcta - NU; }
+        else if (wcta < 2 * NU + UPC) { role = 3; hu = (wcta - 2 * NU) * GH; }
+        else { role = 1; dw = 1; hu = wcta - 2 * NU - UPC; }
+    } else {
+        // sixteen warps in groups of four (one per scheduler): schedulers 0, 1 get [chain, copy, -, -] of ring 0 / 1,
+        // schedulers 2, 3 the four decision warps of head 0 / 1 - a chain warp never shares its scheduler with a
+        // decision warp, whose bursts of work would take issue slots from it
+        const int q4 = wcta >> 2, r4 = wcta & 3;
+        if (r4 < 2) { hu = r4; role = q4 == 0 ? 0 : (q4 == 1 ? 3 : -1); }
+        else { hu = r4 - 2; role = 1; dw = q4; }
+    }
     const int ring = hu / GH, hg = hu - ring * GH;
     const long long ru = (long long)blockIdx.x * UPC + ring;   // ring unit
     const long long bh = ru * GH + hg;                         // (batch, query head)
@@ -300,7 +311,7 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
             asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(base + pl.lw + i * 16), "r"(0x80808080u) : "memory");
     }
     __syncthreads();
-    if (ru >= p.units) return;                     // (odd number of ring units: the last CTA's second ring has none)
+    if (role < 0 || ru >= p.units) return;         // (odd number of ring units: the last CTA's second ring has none)
 
     if (role == 3) {
         // ------------------------------------------------------------------ copy warp: the high bytes
@@ -311,7 +322,7 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
         // The decision warp's first loads (probe result, exponent maxima) go out before this warp floods the memory
         // system with the first ring of copies - behind that flood they would take several times as long, and the
         // first stage cannot be consumed before the threshold is known.
-        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + ring), "r"((2 * GH + 1) * 32) : "memory");
+        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + ring), "r"((NDW * GH + 1) * 32) : "memory");
 #pragma unroll 1
         for (int i = 0; i < nst; ++i) {
             if (i >= nf) {
@@ -329,11 +340,12 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
         if (!alive) v_sleep_ms();
         return;
     }
-    if (role == 1 || role == 2) {
+    if (role == 1) {
         // ------------------------------------------------------------------ decision warps
-        // Warp w (0, 1) owns the stages of parity w.  The ring depth nf is even, so the previous stage of a ring slot
-        // belongs to the same warp, and each warp has its own half of the side ring: the two never share state.
-        const int w = role - 1;
+        // Warp w (0 .. NDW-1) owns the stages i with i % NDW == w.  The ring depth nf is a multiple of NDW, so the
+        // previous stage of a ring slot belongs to the same warp, and each warp has its own part of the side ring: the
+        // warps never share state.
+        const int w = dw;
         const uint8_t* M = p.mid4 + (size_t)kv * p.max_seq_len * HD;
         const uint8_t* L = p.last4 + (size_t)kv * p.max_seq_len * HD;
         const uint16_t* s_row = p.s + (size_t)bh * p.s_last_dim;
@@ -357,8 +369,8 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
             a = p.amin[bh];
         }
         const uint32_t A = (a << 10) & 0xFFFFu;
-        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + ring), "r"((2 * GH + 1) * 32) : "memory");
-        const int hside = nside / 2;                       // rows of this warp's half of the side ring
+        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + ring), "r"((NDW * GH + 1) * 32) : "memory");
+        const int hside = nside / NDW;                     // rows of this warp's part of the side ring
         const uint32_t ma = base + pl.mid + (uint32_t)w * hside * HD, la = base + pl.low + (uint32_t)w * hside * HD;
         const uint32_t wrap = (uint32_t)(hside - 1);
         uint32_t side_head = 0, side_tail = 0;    // side rows handed out / taken back so far
@@ -368,7 +380,7 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
         uint32_t nib_par = 0;                           // bit r: parity of the NEXT phase of nibble barrier r
         // low-byte tables of this warp, used in turn by its stages with flagged tokens; t_out = tables in use (built
         // and not yet restored)
-        const int npw = p.npt >> 1;
+        const int npw = p.npt / NDW;
         int t_next = 0, t_out = 0;
         // consume the release of own stage `freed`: its side rows are free again, its patched table rows become 0x80 again
         auto reclaim = [&]() {
@@ -381,9 +393,9 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
                     --t_out;
                 }
             }
-            freed += 2;
-            if ((freed_slot += 2) >= nf) { freed_slot -= nf; freed_parity ^= 1u; }
-            if ((freed_rec += 2) >= nrec) freed_rec -= nrec;
+            freed += NDW;
+            if ((freed_slot += NDW) >= nf) { freed_slot -= nf; freed_parity ^= 1u; }
+            if ((freed_rec += NDW) >= nrec) freed_rec -= nrec;
         };
         // EARLY part for own stage j (position state advances with j).  armed = next own stage to be armed: side rows
         // can only be waited for while an armed own stage is still unreleased; otherwise the stage is prepared later
@@ -392,7 +404,7 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
         uint32_t e_par = 0;                             // ((j / sch) / 3) & 1
         bool e_chunk = false;                           // the chunk of stage j has been entered
         auto early = [&](int j, int armed) -> bool {
-            if (e_sic < 2 && !e_chunk) {    // entering chunk c: ask for the next one (warp 0), make sure this one has landed
+            if (e_sic < NDW && !e_chunk) {    // entering chunk c: ask for the next one (warp 0), make sure this one has landed
                 if (w == 0 && (e_c + 1) * sch < nst && lane == 0) request_s(e_c + 1, e_buf == 2 ? 0 : e_buf + 1);
                 alive = mbar_wait(bar_sb + e_buf * 8, e_par);
                 if (!alive) return false;
@@ -429,9 +441,9 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(base + pl.rec + e_rec * REC), "r"(start), "r"(um0),
                              "r"(um1), "r"(rows) : "memory");
             __syncwarp();               // (the record is read back by every lane in the late part)
-            if ((e_rec += 2) >= nrec) e_rec -= nrec;
+            if ((e_rec += NDW) >= nrec) e_rec -= nrec;
             e_chunk = false;
-            if ((e_sic += 2) >= sch) {
+            if ((e_sic += NDW) >= sch) {
                 e_sic -= sch;
                 ++e_c;
                 if (++e_buf == 3) { e_buf = 0; e_par ^= 1u; }
@@ -441,7 +453,7 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
         int slot = w, rec = w, j = w;             // of stage i: i % nf, i % 2nf; j: next own stage to prepare
         int l_sic = w, l_buf = 0;                 // of stage i: i % sch, (i / sch) % 3
 #pragma unroll 1
-        for (int i = w; i < nst && alive; i += 2) {
+        for (int i = w; i < nst && alive; i += NDW) {
             while (alive && freed <= i - nf) reclaim();
             // phase 0: stage i must be prepared (it normally is, a ring ago), then it is armed; phase 1: run ahead, up
             // to a ring's length (one call site of the early part for both)
@@ -450,8 +462,8 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
                 const int lim = phase == 0 ? i : i + nf;
 #pragma unroll 1
                 while (alive && j <= lim && j < nst) {
-                    if (!early(j, i + 2 * phase)) break;
-                    j += 2;
+                    if (!early(j, i + NDW * phase)) break;
+                    j += NDW;
                 }
                 if (phase == 0 && alive) {
                     // LATE part of stage i: its nibble rows (requested long ago) must have landed and its rows of the
@@ -475,9 +487,9 @@ __global__ void __launch_bounds__((3 * UPC * GH + UPC) * 32, 1) v_chain_kernel(c
                     }
                     __syncwarp();
                     if (lane == 0 && alive) mbar_arrive(bar_full + slot * 8);   // publishes the table rows; the copy warp adds the bytes
-                    if ((slot += 2) >= nf) slot -= nf;
-                    if ((rec += 2) >= nrec) rec -= nrec;
-                    if ((l_sic += 2) >= sch) { l_sic -= sch; l_buf = l_buf == 2 ? 0 : l_buf + 1; }
+                    if ((slot += NDW) >= nf) slot -= nf;
+                    if ((rec += NDW) >= nrec) rec -= nrec;
+                    if ((l_sic += NDW) >= sch) { l_sic -= sch; l_buf = l_buf == 2 ? 0 : l_buf + 1; }
                 }
             }
         }

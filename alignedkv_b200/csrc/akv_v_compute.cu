@@ -480,7 +480,7 @@ static int launch_v_fast(const VParams& p, int BH, cudaStream_t st) {
 // capacity / units per SM, of which the probability buffers and the side ring take a fixed part and the two rings
 // (high bytes, low-byte table: 16 KB per stage) the rest.
 struct VChainCfg {
-    int upc, gh, nf, nside, sch, npt, smem;
+    int upc, gh, ndw, nf, nside, sch, npt, smem;
 };
 // heads: (batch, query head) rows; gh: heads that share a ring (1, or the group size: the query heads of a KV head)
 static VChainCfg v_chain_config(long long heads, int gh, int reference) {
@@ -491,9 +491,13 @@ static VChainCfg v_chain_config(long long heads, int gh, int reference) {
     c.upc = (gh == 1 && heads >= 2) ? 2 : 1;
     if (gh == 1 && t.v_upc > 0) c.upc = t.v_upc;
     const int budget = max_dyn_smem();
-    c.nside = reference ? 256 : 128;                       // (each decision warp owns half: at least a stage's 64 rows)
+    // decision warps per head: a stage with flagged tokens costs its warp three out-of-line calls (copy issue, row
+    // build, row restore), and two warps per head fell behind the chain on them; four have the time.  They need
+    // schedulers of their own, which two rings of one head each can give them.
+    c.ndw = (c.upc == 2 && gh == 1 && tuning().v_ndw != 2) ? 4 : 2;
+    c.nside = (reference ? 128 : 64) * c.ndw;              // (each decision warp owns a part: at least a stage's 64 rows)
     c.sch = 16;
-    if (t.v_nside >= 128) c.nside = t.v_nside;
+    if (t.v_nside >= 64 * c.ndw) c.nside = t.v_nside;
     // low-byte tables per head: two per decision warp where they fit (a third stage with flagged tokens among a warp's
     // stages in flight is rare and only makes that warp wait for the oldest one), one with four heads on a ring
     c.npt = c.upc * gh >= 4 ? 2 : 4;
@@ -502,23 +506,23 @@ static VChainCfg v_chain_config(long long heads, int gh, int reference) {
     // four stages (measured: 4, 6 and 8 alike), heads that share a ring wait for each other and use what fits
     int nf = gh == 1 ? 4 : c.sch / 2;
     if (t.v_nf > 0 && t.v_nf < nf) nf = t.v_nf;
-    nf &= ~1;                                              // even: a ring slot's stages all belong to one decision warp
+    nf -= nf % c.ndw;                                      // a ring slot's stages all belong to one decision warp
+    if (nf < c.ndw) nf = c.ndw;
     // (one head per ring: a table per ring slot)
-    while (nf > 2 && vch::plan(nf, c.nside, c.sch, gh == 1 ? nf : c.npt, c.upc, gh).bytes > budget) nf -= 2;
-    if (nf < 2) nf = 2;
+    while (nf > c.ndw && vch::plan(nf, c.nside, c.sch, gh == 1 ? nf : c.npt, c.upc, gh).bytes > budget) nf -= c.ndw;
     c.nf = nf;
     if (gh == 1) c.npt = nf;
     c.smem = vch::plan(c.nf, c.nside, c.sch, c.npt, c.upc, gh).bytes;
     return c;
 }
 
-template <int UPC, int GH>
+template <int UPC, int GH, int NDW>
 static int launch_v_chain_u(VParams& p, const VChainCfg& c, long long heads, cudaStream_t st) {
     static bool configured[64] = {false};   // the attribute is per device (one array per instantiation)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(v_chain_kernel<UPC, GH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(v_chain_kernel<UPC, GH, NDW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              max_dyn_smem());
         if (e != cudaSuccess) return cuda_status(e, "v_cache_compute smem attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
@@ -527,7 +531,7 @@ static int launch_v_chain_u(VParams& p, const VChainCfg& c, long long heads, cud
     p.nf = c.nf; p.nside = c.nside; p.sch = c.sch; p.npt = c.npt;
     p.units = (int)(heads / GH);
     const int grid = (p.units + UPC - 1) / UPC;
-    launch_chained(v_chain_kernel<UPC, GH>, dim3(grid), dim3((3 * UPC * GH + UPC) * 32), (size_t)c.smem, st, p);
+    launch_chained(v_chain_kernel<UPC, GH, NDW>, dim3(grid), dim3(NDW == 2 ? ((1 + NDW) * UPC * GH + UPC) * 32 : 512), (size_t)c.smem, st, p);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
 }
 
@@ -569,9 +573,10 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
         const bool per_head = group == 1 || w == 1 || (w == 0 && heads <= 2ll * sm_count());
         const int gh = per_head ? 1 : group;
         const VChainCfg c = v_chain_config(heads, gh, reference);
-        if (gh == 4) return launch_v_chain_u<1, 4>(p, c, heads, st);
-        if (gh == 2) return launch_v_chain_u<1, 2>(p, c, heads, st);
-        return c.upc == 2 ? launch_v_chain_u<2, 1>(p, c, heads, st) : launch_v_chain_u<1, 1>(p, c, heads, st);
+        if (gh == 4) return launch_v_chain_u<1, 4, 2>(p, c, heads, st);
+        if (gh == 2) return launch_v_chain_u<1, 2, 2>(p, c, heads, st);
+        if (c.upc == 2) return c.ndw == 4 ? launch_v_chain_u<2, 1, 4>(p, c, heads, st) : launch_v_chain_u<2, 1, 2>(p, c, heads, st);
+        return launch_v_chain_u<1, 1, 2>(p, c, heads, st);
     }
     if (fast && group == 1) return launch_v_fast<1, 6, 2, 1>(p, BH, st);
     if (fast && group == 2) return launch_v_fast<2, 6, 2, 2>(p, BH, st);
