@@ -515,40 +515,55 @@ __global__ void __launch_bounds__(NDW == 2 ? ((1 + NDW) * UPC * GH + UPC) * 32 :
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                      : "=r"(r[o]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]) : "r"(a));
     };
-    // la: the low-byte table of the stage - one of the head's own tables when the stage has flagged tokens, else the
-    // CTA's constant table (an address select, no branch)
-    auto fetch = [&](Grp& r, uint32_t fa, uint32_t la, uint32_t sa, int grp) {
+    // A stage without flagged tokens (most of them) has the constant low byte 0x80 everywhere: it is consumed by a
+    // second copy of the stage body that neither loads the table nor holds its words (LEAN).  la: the low-byte table of
+    // a stage WITH flagged tokens (0 for the others): the table of its ring slot, or one of the head's own tables.
+    auto fetch_high = [&](Grp& r, uint32_t fa, uint32_t sa, int grp) {
         const uint32_t a = (uint32_t)grp * (8 * D) + lm_off;
         ldm(r.h, 0, fa + a);
         ldm(r.h, 4, fa + a + 4 * D);
-        ldm(r.l, 0, la + a);
-        ldm(r.l, 4, la + a + 4 * D);
         r.s = lds128(sa + grp * 16);
     };
-    auto consume = [&](const Grp& r) {
+    auto fetch_low = [&](Grp& r, uint32_t la, int grp) {
+        const uint32_t a = (uint32_t)grp * (8 * D) + lm_off;
+        ldm(r.l, 0, la + a);
+        ldm(r.l, 4, la + a + 4 * D);
+    };
+    auto consume = [&](const Grp& r, auto lean) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const __half2 sd = v_dup(u4w(r.s, u >> 1), u & 1);
-            accA = v_fma(__byte_perm(r.h[u], r.l[u], 0x1504), sd, accA);
-            accB = v_fma(__byte_perm(r.h[u], r.l[u], 0x3726), sd, accB);
+            if (decltype(lean)::value) {
+                accA = v_fma(__byte_perm(r.h[u], 0x80808080u, 0x1404), sd, accA);
+                accB = v_fma(__byte_perm(r.h[u], 0x80808080u, 0x3424), sd, accB);
+            } else {
+                accA = v_fma(__byte_perm(r.h[u], r.l[u], 0x1504), sd, accA);
+                accB = v_fma(__byte_perm(r.h[u], r.l[u], 0x3726), sd, accB);
+            }
         }
     };
     int slot = 0, sic = 0, buf = 0, crec = 0;                          // of the current stage: % nf, % sch, chunk % 3, % 2 nf
     uint32_t parity = 0;
     auto f_addr = [&]() { return rbase + (uint32_t)slot * F_BYTES; };
     auto s_addr = [&]() { return base + pl.sb + (uint32_t)buf * (sch * TOK * 2) + (uint32_t)sic * (TOK * 2); };
-    // the stage's table, from its record (word 3: flagged rows | (table + 1) << 8; 0 = no flagged token)
-    auto l_addr = [&]() {
+    // the stage's table: the one of its ring slot (which holds the constant for a stage without flagged tokens, so
+    // that form runs one copy of the stage body only: the second copy costs it more in instruction fetch than the
+    // skipped loads save - 31.8 against 29.0 us), or from its record (word 3: flagged rows | (table + 1) << 8;
+    // 0 = no flagged token -> 0)
+    auto l_addr = [&]() -> uint32_t {
         if (SLOT_TABLES) return base + pl.lw + (uint32_t)slot * F_BYTES;
         const uint32_t w = lds32(base + pl.rec + (uint32_t)crec * REC + 12);
-        return w ? base + pl.lw + ((w >> 8) - 1u) * F_BYTES : ctab;
+        return w ? base + pl.lw + ((w >> 8) - 1u) * F_BYTES : 0u;
     };
     Grp ra, rb;
-    uint32_t fa = f_addr(), sa = s_addr(), la = ctab;
+    uint32_t fa = f_addr(), sa = s_addr(), la = 0;
     if (nst > 0) {
         alive = mbar_wait(bar_full, 0);
         if (alive) la = l_addr();
-        if (alive && nsf > 0) fetch(ra, fa, la, sa, 0);
+        if (alive && nsf > 0) {
+            fetch_high(ra, fa, sa, 0);
+            if (la) fetch_low(ra, la, 0);
+        }
     }
     // One full stage per iteration, straight-line: groups alternate between ra and rb, the group after next is
     // fetched while one is consumed; on entry ra holds group 0 of the stage.
@@ -559,25 +574,39 @@ __global__ void __launch_bounds__(NDW == 2 ? ((1 + NDW) * UPC * GH + UPC) * 32 :
         if (++sic == sch) { sic = 0; buf = buf == 2 ? 0 : buf + 1; }
         if (++crec == nrec) crec = 0;
         const uint32_t nfa = f_addr(), nsa = s_addr();
-        uint32_t landed = 0, nla = ctab;
+        uint32_t nla = 0;
+        auto stage = [&](auto lean) {
+            uint32_t landed = 0;
 #pragma unroll
-        for (int ga = 0; ga < 8; ga += 2) {
-            fetch(rb, fa, la, sa, ga + 1);
-            consume(ra);
-            if (ga < 6) {
-                fetch(ra, fa, la, sa, ga + 2);
-                // the next stage has normally landed long ago (the ring is several stages deep): probe its barrier two
-                // groups before the answer is needed, so that the probe's latency is hidden; then read its record
-                if (ga == 2 && left > 1) landed = mbar_test(bar_full + slot * 8, parity);
-                if (ga == 4 && left > 1) nla = l_addr();              // (valid only if it had landed)
-            } else if (left > 1) {
-                if (__builtin_expect(!landed, 0)) {
-                    alive = mbar_wait(bar_full + slot * 8, parity);
-                    nla = l_addr();
+            for (int ga = 0; ga < 8; ga += 2) {
+                fetch_high(rb, fa, sa, ga + 1);
+                if (!decltype(lean)::value) fetch_low(rb, la, ga + 1);
+                consume(ra, lean);
+                if (ga < 6) {
+                    fetch_high(ra, fa, sa, ga + 2);
+                    if (!decltype(lean)::value) fetch_low(ra, la, ga + 2);
+                    // the next stage has normally landed long ago (the ring is several stages deep): probe its barrier
+                    // two groups before the answer is needed, so that the probe's latency is hidden; then its record
+                    if (ga == 2 && left > 1) landed = mbar_test(bar_full + slot * 8, parity);
+                    if (ga == 4 && left > 1) nla = l_addr();          // (valid only if it had landed)
+                } else if (left > 1) {
+                    if (__builtin_expect(!landed, 0)) {
+                        alive = mbar_wait(bar_full + slot * 8, parity);
+                        nla = l_addr();
+                    }
+                    if (alive) {                                      // first group of the next stage
+                        fetch_high(ra, nfa, nsa, 0);
+                        if (nla) fetch_low(ra, nla, 0);
+                    }
                 }
-                if (alive) fetch(ra, nfa, nla, nsa, 0);      // first group of the next stage
+                consume(rb, lean);
             }
-            consume(rb);
+        };
+        if constexpr (SLOT_TABLES) {
+            stage(std::false_type{});               // (the only copy of the stage body in this instantiation)
+        } else {
+            if (la) stage(std::false_type{});
+            else stage(std::true_type{});
         }
         // the stage is consumed: hand back its ring slot
         __syncwarp();
@@ -593,7 +622,8 @@ __global__ void __launch_bounds__(NDW == 2 ? ((1 + NDW) * UPC * GH + UPC) * 32 :
 #pragma unroll 1
             for (int t = 0; t < tail; ++t) {
                 const uint32_t hw = lds16(fa + (uint32_t)t * D + pairA * 2) | (lds16(fa + (uint32_t)t * D + pairB * 2) << 16);
-                const uint32_t lw = lds16(la + (uint32_t)t * D + pairA * 2) | (lds16(la + (uint32_t)t * D + pairB * 2) << 16);
+                const uint32_t lw = la ? lds16(la + (uint32_t)t * D + pairA * 2) | (lds16(la + (uint32_t)t * D + pairB * 2) << 16)
+                                       : 0x80808080u;
                 const uint32_t sb = lds16(sa + t * 2);
                 accA = hfma2_bits(__byte_perm(hw, lw, 0x1504), sb | (sb << 16), accA);
                 accB = hfma2_bits(__byte_perm(hw, lw, 0x3726), sb | (sb << 16), accB);
