@@ -17,20 +17,24 @@
 // chains per thread, which hide the FMA latency.  That matters more than it seems: a warp whose steady loop carries
 // branches and rarely-run code, or does not fit the scheduler's instruction cache, was measured at a third of the
 // speed of the same arithmetic in a straight line.
-//   A unit = one (batch, query head); a CTA holds UPC units, each with its own warps, rings and barriers.  With grouped
-//   queries the heads of a KV head are neighbouring units that stream the same planes at the same pace: the first
-//   one's copies bring a stage into L2, the others' hit there.
+//   A unit = one (batch, query head).  A CTA holds UPC rings of high bytes; a ring serves GH heads - one, or the query
+//   heads of one KV head, which need the same high bytes - and every head has its own chain warp, decision warps,
+//   tables and barriers.  (With a ring per query head the heads of a KV head are neighbouring units that stream the same
+//   planes at the same pace: the first one's copies bring a stage into L2, the others' hit there.)
 //   chain warp: all 64 channel pairs of the head, one 64-token stage per loop iteration.
-//   copy warp: stage i -> ring slot i % nf as soon as the chain has released the slot's previous stage: one 8 KB bulk
-//     asynchronous copy of the high bytes exactly as they lie in the plane.
-//   decision warps (two or four per head, taking the stages in turn): lane = tokens (lane, lane + 32) of a stage.  EARLY part, a ring ahead of its use: takes the
-//     probabilities from a buffer bulk-copied a chunk ahead, decides the read codes (V_cache.cu:211,250-251), reserves
-//     rows of a small side ring for the tokens that read a nibble plane and starts 64-byte copies of just those
-//     rows (one 4 KB copy when the whole stage reads a plane), counted on a barrier of their own.  LATE part, when the
-//     stage's ring slot is free: restores the table rows the slot's previous stage had patched, makes sure the nibble
-//     rows have landed (long ago), builds the flagged tokens' rows of the low-byte table, and arrives on the stage's
-//     barrier.  Requesting the nibble rows a ring ahead matters: issued together with the stage's high bytes, the few
-//     small copies completed late under load and held up every stage that had one.
+//   copy warp (one per ring): stage i -> ring slot i % nf as soon as every chain of the ring has released the slot's
+//     previous stage: one 8 KB bulk asynchronous copy of the high bytes exactly as they lie in the plane.
+//   decision warps (NDW per head, stage i belongs to warp i % NDW): lane = tokens (lane, lane + 32) of a stage.  EARLY
+//     part, a ring ahead of its use: takes the probabilities from a buffer bulk-copied a chunk ahead, decides the read
+//     codes (V_cache.cu:211,250-251), reserves rows of a small side ring for the tokens that read a nibble plane and
+//     starts 64-byte copies of just those rows (one 4 KB copy when the whole stage reads a plane), counted on a barrier
+//     of their own.  LATE part, when the stage's ring slot is free: restores the table rows the slot's previous stage
+//     had patched, makes sure the nibble rows have landed (long ago), builds the flagged tokens' rows of the low-byte
+//     table, and arrives on the stage's barrier.  Requesting the nibble rows a ring ahead matters: issued together with
+//     the stage's high bytes, the few small copies completed late under load and held up every stage that had one.
+//     And the NUMBER of these warps matters: a stage with flagged tokens costs its warp three out-of-line calls, and
+//     two warps per head fell behind the chain on every such stage (34.9 us for batch 8 x 32 heads x 4096 tokens);
+//     four, on schedulers the chain warps do not use, keep up (28.5 us, with or without flagged tokens).
 // Every wait is bounded (about a second); a wait that runs out raises the device error flag, the chain stores NaN
 // instead of a result, and the producers give their copies in flight time to land before the CTA leaves.
 #pragma once
