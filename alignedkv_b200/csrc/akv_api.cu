@@ -100,6 +100,8 @@ int akv_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "v_npt") && value >= 0 && value <= 8) t.v_npt = value;
     else if (!strcmp(key, "v_split_impl") && (value == 0 || value == 1)) t.v_split_impl = value;
     else if (!strcmp(key, "v_ndw") && (value == 0 || value == 2 || value == 4)) t.v_ndw = value;
+    else if (!strcmp(key, "v_split_nf") && (value == 0 || value == 4 || value == 8)) t.v_split_nf = value;
+    else if (!strcmp(key, "v_split_cps") && value >= 0 && value <= 8) t.v_split_cps = value;
     else if (!strcmp(key, "v_upc") && value >= 0 && value <= 2) t.v_upc = value;
     else {
         set_error("set_tuning: unknown key or value out of range (%s = %d)", key, value);

@@ -32,6 +32,8 @@ struct Tuning {
     int v_npt = 0;      // exact P.V (form 0): low-byte tables per head, 2, 4, 6 or 8 (0 = default)
     int v_ndw = 0;      // exact P.V (form 0), two rings of one head each: decision warps per head, 2 or 4 (0 = default)
     int v_split_impl = 0;   // order-free P.V, multi-head, aligned mode: 0 = staged through shared memory by bulk copies, 1 = direct loads
+    int v_split_nf = 0;     // order-free P.V, streaming form: ring depth 4 or 8 (0 = default 8)
+    int v_split_cps = 0;    // order-free P.V, streaming form: CTAs per SM the chunking aims at (0 = default 3)
 };
 Tuning& tuning();
 

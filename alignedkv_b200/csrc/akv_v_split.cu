@@ -193,7 +193,8 @@ static void split_plan(int BH, int n, int* chunk_tokens, int* chunks) {
 // The streaming form (akv_v_stream.cuh; multi-head attention, aligned mode) wants about three long-lived CTAs per SM:
 // fewer, longer chunks than the direct form - so the direct form's plan bounds the scratch of both.
 static void stream_plan(int BH, int n, int* chunk_tokens, int* chunks) {
-    const int target = sm_count() * 3;
+    const int per_sm = tuning().v_split_cps > 0 ? tuning().v_split_cps : 3;
+    const int target = sm_count() * per_sm;
     int want = (target + BH - 1) / BH;
     if (want < 1) want = 1;
     int ct = (n + want - 1) / want;

@@ -260,12 +260,13 @@ static int launch_v_stream(const VStreamParams& q, int BH, cudaStream_t st) {
     // ring depth: a multiple of the consumer warps, so that a ring slot's stages all go to ONE warp, which then sees
     // the slot's barrier phases in order (a parity wait cannot tell phase k from phase k - 2: a warp that asked for
     // stage i + 2 nf's phase before stage i + nf's had completed would be let through)
-    p.nf = 2 * vst::CONSUMERS;
+    p.nf = tuning().v_split_nf == 4 ? 4 : 2 * vst::CONSUMERS;      // (4, 8 and 2..6 CTAs per SM all measure 33-35 us at batch 8 x 32 x 4096)
     const int smem = vst::smem_bytes(p.nf);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(v_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(v_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             vst::smem_bytes(2 * vst::CONSUMERS));     // (the deepest ring in use)
         if (e != cudaSuccess) return cuda_status(e, "v_cache_compute (order-free) smem attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
