@@ -414,16 +414,39 @@ softmax_chunk_write_kernel(uint16_t* __restrict__ s, const float* __restrict__ c
     };
     __shared__ uint32_t cand_v[256];
     __shared__ int32_t cand_i[256];
+    __shared__ float term[256];
+    __shared__ float wmax[8];
     const int bhq = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
     uint16_t* row = s + (size_t)bhq * R;
     const __half* mrow = mask ? mask + (size_t)(bhq / Hq) * mask_stride : nullptr;
-    // row statistics from the chunk statistics, in chunk order (every CTA of the row computes the same values)
+    // Row statistics from the chunk statistics (every CTA of the row computes the same values): the maximum, then the
+    // sum of l_c exp(m_c - m) added IN CHUNK ORDER.  The loads and the exponentials of up to 256 chunks are done in
+    // parallel, one per thread; only the additions are serial, out of shared memory - the same operations in the same
+    // order as a loop over the chunks, at a fraction of its latency (an empty chunk contributes an exact 0).
     float m = -INFINITY;
-    for (int c = 0; c < stat_chunks; ++c) m = fmaxf(m, stat(c)[0]);
+    for (int c0 = 0; c0 < stat_chunks; c0 += 256) {
+        float v = c0 + tid < stat_chunks ? stat(c0 + tid)[0] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+        if ((tid & 31) == 0) wmax[tid >> 5] = v;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < 8; ++w) m = fmaxf(m, wmax[w]);
+        __syncthreads();
+    }
     float sum = 0.f;
-    for (int c = 0; c < stat_chunks; ++c) {
-        const float mc = stat(c)[0];
-        if (mc > -INFINITY) sum += stat(c)[1] * expf(mc - m);
+    for (int c0 = 0; c0 < stat_chunks; c0 += 256) {
+        float tm = 0.f;
+        if (c0 + tid < stat_chunks) {
+            const float* st2 = stat(c0 + tid);
+            const float mc = st2[0];
+            if (mc > -INFINITY) tm = st2[1] * expf(mc - m);
+        }
+        term[tid] = tm;
+        __syncthreads();
+        const int cnt = min(256, stat_chunks - c0);
+        for (int c = 0; c < cnt; ++c) sum += term[c];
+        __syncthreads();
     }
     const int t0 = ch * SM_CHUNK, t1 = min(R, t0 + SM_CHUNK);
     uint32_t best = 0;
@@ -463,28 +486,56 @@ softmax_class_reduce_kernel(const float* __restrict__ cstat, const uint32_t* __r
     const int bhq = blockIdx.x, tid = threadIdx.x;
     const int cpr = chunks / ranks;
     const size_t block = (size_t)gridDim.x * cpr * TOPK;          // one array of one rank
-    uint32_t bv = 0;
-    int32_t bi = 0;
-    for (int c = 0; c < chunks; ++c) {      // chunks are in position order: a later chunk wins only when larger
+    auto val_at = [&](int c) -> const uint32_t* {
         const int r = c / cpr;
         const size_t e = ((size_t)bhq * cpr + (c - r * cpr)) * TOPK + tid;
-        const uint32_t v = ranks == 1 ? cand_val[e] : cand_val[(size_t)r * 2 * block + e];
-        if (v > bv) {
-            bv = v;
-            bi = ranks == 1 ? cand_idx[e] : reinterpret_cast<const int32_t*>(cand_val)[(size_t)r * 2 * block + block + e];
-        }
+        return ranks == 1 ? cand_val + e : cand_val + (size_t)r * 2 * block + e;
+    };
+    // chunks are in position order: a later chunk wins only when larger.  Eight chunks' values are loaded at a time;
+    // the position is fetched for the winner only.
+    uint32_t bv = 0;
+    int bc = -1;
+    for (int c0 = 0; c0 < chunks; c0 += 8) {
+        uint32_t v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = c0 + j < chunks ? *val_at(c0 + j) : 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (v[j] > bv) { bv = v[j]; bc = c0 + j; }
+    }
+    int32_t bi = 0;
+    if (bc >= 0) {
+        const int r = bc / cpr;
+        const size_t e = ((size_t)bhq * cpr + (bc - r * cpr)) * TOPK + tid;
+        bi = ranks == 1 ? cand_idx[e] : reinterpret_cast<const int32_t*>(cand_val)[(size_t)r * 2 * block + block + e];
     }
     pval[(size_t)bhq * TOPK + tid] = (uint16_t)bv;
     pidx[(size_t)bhq * TOPK + tid] = bi;
-    if (tid == 0 && cstat != nullptr) {
-        float m = -INFINITY, sum = 0.f;
-        for (int c = 0; c < chunks; ++c) m = fmaxf(m, cstat[((size_t)bhq * chunks + c) * 2]);
-        for (int c = 0; c < chunks; ++c) {
-            const float mc = cstat[((size_t)bhq * chunks + c) * 2];
-            if (mc > -INFINITY) sum += cstat[((size_t)bhq * chunks + c) * 2 + 1] * expf(mc - m);
+    if (cstat != nullptr) {
+        // row statistics: maximum, then the sum of l_c exp(m_c - m) in chunk order; lane = chunk, 32 at a time, the
+        // additions serial through shuffles (the same operations in the same order as a loop over the chunks)
+        const float* cs = cstat + (size_t)bhq * chunks * 2;
+        float m = -INFINITY;
+        for (int c0 = 0; c0 < chunks; c0 += 32) {
+            float v = c0 + tid < chunks ? cs[(size_t)(c0 + tid) * 2] : -INFINITY;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+            m = fmaxf(m, v);
         }
-        stats[(size_t)bhq * 2] = m;
-        stats[(size_t)bhq * 2 + 1] = sum;
+        float sum = 0.f;
+        for (int c0 = 0; c0 < chunks; c0 += 32) {
+            float tm = 0.f;
+            if (c0 + tid < chunks) {
+                const float mc = cs[(size_t)(c0 + tid) * 2];
+                if (mc > -INFINITY) tm = cs[(size_t)(c0 + tid) * 2 + 1] * expf(mc - m);
+            }
+            const int cnt = min(32, chunks - c0);
+            for (int c = 0; c < cnt; ++c) sum += __shfl_sync(0xFFFFFFFFu, tm, c);
+        }
+        if (tid == 0) {
+            stats[(size_t)bhq * 2] = m;
+            stats[(size_t)bhq * 2 + 1] = sum;
+        }
     }
 }
 
