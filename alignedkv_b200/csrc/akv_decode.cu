@@ -182,6 +182,7 @@ append_flush_kernel(uint32_t* __restrict__ restk, uint32_t* __restrict__ restv, 
 // or two and the step is bound by the latency of its kernel chain; with many rows the plain form plus a separate
 // probe launch keeps more CTAs per SM and is faster.
 constexpr int SM_REGS = 32;
+constexpr int SM_REGS_512 = 34;   // with 512 threads: rows of up to 17408 scores (16384 cached tokens plus residual blocks)
 // Score t of a row as the fp32 softmax sees it: the fp16 score, plus (optional) the additive fp16 mask of its batch
 // row, added in fp16 as the reference's in-place `scores += mask` on fp16 tensors does (model/KVCache_AlignedKV.py:119-120).
 __device__ __forceinline__ float masked_score(const uint16_t* __restrict__ row, const __half* __restrict__ mrow, int t) {
@@ -221,15 +222,18 @@ __device__ __forceinline__ void residual_scores(uint16_t* __restrict__ row, cons
     }
 }
 
-template <bool CACHED, bool PROBE>
-__global__ void __launch_bounds__(256)
+// NT threads per CTA (256, or 512 for rows of up to 512*SM_REGS scores that one CTA keeps in registers).
+template <bool CACHED, bool PROBE, int NT>
+__global__ void __launch_bounds__(NT)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
                uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats,
                const uint8_t* __restrict__ first8, uint16_t* __restrict__ test_o, int max_seq_len, int H, int G, int D,
                int R, int qn, int rest, float sqrt_d, const __half* __restrict__ mask, long long mask_stride) {
-    __shared__ float redf[8];
-    __shared__ uint32_t cand_v[256];
-    __shared__ int32_t cand_i[256];
+    constexpr int NW = NT / 32;
+    constexpr int REGS = NT == 512 ? SM_REGS_512 : SM_REGS;      // scores a thread keeps (CACHED)
+    __shared__ float redf[NW];
+    __shared__ uint32_t cand_v[NT];
+    __shared__ int32_t cand_i[NT];
     pdl_enter();
     const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -238,18 +242,18 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     const int len = qn + rest;
     residual_scores(row, q + (size_t)bhq * D, restk, b, h, H, D, qn, rest, sqrt_d, 0, len);
     __syncthreads();
-    float x[CACHED ? SM_REGS : 1];
+    float x[CACHED ? REGS : 1];
     // pass 1: maximum
     float m = -INFINITY;
     if (CACHED) {
 #pragma unroll
-        for (int i = 0; i < SM_REGS; ++i) {
-            const int t = tid + 256 * i;
+        for (int i = 0; i < REGS; ++i) {
+            const int t = tid + NT * i;
             x[i] = t < len ? masked_score(row, mrow, t) : -INFINITY;
             m = fmaxf(m, x[i]);
         }
     } else {
-        for (int t = tid; t < len; t += 256) m = fmaxf(m, masked_score(row, mrow, t));
+        for (int t = tid; t < len; t += NT) m = fmaxf(m, masked_score(row, mrow, t));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
@@ -257,20 +261,20 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     __syncthreads();
     m = redf[0];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) m = fmaxf(m, redf[w]);
+    for (int w = 1; w < NW; ++w) m = fmaxf(m, redf[w]);
     __syncthreads();
     // pass 2: sum of exponentials (fp32, as F.softmax(scores.float()) does; model/KVCache_AlignedKV.py:121)
     float sum = 0.f;
     if (CACHED) {
 #pragma unroll
-        for (int i = 0; i < SM_REGS; ++i) {
-            if (tid + 256 * i < len) {
+        for (int i = 0; i < REGS; ++i) {
+            if (tid + NT * i < len) {
                 x[i] = expf(x[i] - m);
                 sum += x[i];
             }
         }
     } else {
-        for (int t = tid; t < len; t += 256) sum += expf(masked_score(row, mrow, t) - m);
+        for (int t = tid; t < len; t += NT) sum += expf(masked_score(row, mrow, t) - m);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
@@ -278,7 +282,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     __syncthreads();
     sum = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) sum += redf[w];
+    for (int w = 0; w < NW; ++w) sum += redf[w];
     if (tid == 0) {
         stats[(size_t)bhq * 2] = m;
         stats[(size_t)bhq * 2 + 1] = sum;
@@ -289,8 +293,8 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     int32_t best_g = 0;
     if (CACHED) {
 #pragma unroll
-        for (int i = 0; i < SM_REGS; ++i) {
-            const int t = tid + 256 * i;
+        for (int i = 0; i < REGS; ++i) {
+            const int t = tid + NT * i;
             if (t < R) {
                 uint16_t pb = 0;   // exp(-inf - m) = 0
                 if (t < len) pb = __half_as_ushort(__float2half_rn(x[i] / sum));
@@ -302,7 +306,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
             }
         }
     } else {
-        for (int t = tid; t < R; t += 256) {
+        for (int t = tid; t < R; t += NT) {
             uint16_t pb = 0;
             if (t < len) pb = __half_as_ushort(__float2half_rn(expf(masked_score(row, mrow, t) - m) / sum));
             row[t] = pb;
@@ -318,7 +322,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     if (tid < TOPK) {
         uint32_t bv = cand_v[tid];
         int32_t bi = cand_i[tid];
-        for (int w = 1; w < 8; ++w) {
+        for (int w = 1; w < NW; ++w) {
             const uint32_t v = cand_v[tid + 32 * w];
             const int32_t i = cand_i[tid + 32 * w];
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
@@ -335,7 +339,7 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
     // probe: o_test[d] = sum_j |half((first_8[row_j][d] << 8) + 0x80)| * p_j over the class maxima, rows
     // row_j = class position * 32 + j, accumulated in fp16 in j order; all row gathers go out before the chain starts
     const uint8_t* F = first8 + (size_t)(bhq / G) * max_seq_len * D;
-    for (int c = tid; c < (D >> 1); c += 256) {
+    for (int c = tid; c < (D >> 1); c += NT) {
         uint32_t f[TOPK];
 #pragma unroll
         for (int j = 0; j < TOPK; ++j) {
@@ -837,7 +841,16 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
     // than they save below ~16k scores); else the split form
     const int sm_chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
     bool probed = false;
-    if (sm_chunks >= 4 && B * H * G < 2 * sm_count()) {
+    const int rows = B * H * G;
+    if (R > 256 * SM_REGS && R <= 512 * SM_REGS_512 && rows <= 2 * sm_count()) {
+        // few rows of up to 17408 scores: one CTA of 512 threads keeps the row in registers - one launch instead of the
+        // four of the split form (statistics, probabilities, class reduction, probe)
+        launch_chained(softmax_kernel<true, true, 512>, dim3(rows), dim3(512), 0, st, sc.s,
+                       static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
+                       static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn, rest,
+                       sqrtf((float)D), mk, mask_stride);
+        probed = true;
+    } else if (sm_chunks >= 4 && B * H * G < 2 * sm_count()) {
         dim3 grid(sm_chunks, B * H * G);
         count_launch();
         softmax_chunk_stats_kernel<<<grid, 256, 0, st>>>(sc.s, static_cast<const __half*>(q),
@@ -852,13 +865,13 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
     } else {
         if (R <= 256 * SM_REGS && B * H * G <= 4 * sm_count()) {
             // few rows: one pass over the row, and the probe runs inside the softmax CTA of its row
-            launch_chained(softmax_kernel<true, true>, dim3(B * H * G), dim3(256), 0, st, sc.s,
+            launch_chained(softmax_kernel<true, true, 256>, dim3(B * H * G), dim3(256), 0, st, sc.s,
                            static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
                            static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn, rest,
                            sqrtf((float)D), mk, mask_stride);
             probed = true;
         } else {
-            launch_chained(softmax_kernel<false, false>, dim3(B * H * G), dim3(256), 0, st, sc.s,
+            launch_chained(softmax_kernel<false, false, 256>, dim3(B * H * G), dim3(256), 0, st, sc.s,
                            static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
                            (const uint8_t*)nullptr, (uint16_t*)nullptr, max_seq_len, H, G, D, R, qn, rest,
                            sqrtf((float)D), mk, mask_stride);

@@ -176,7 +176,10 @@ def test_k_compute_gqa(akv_lib, B, H, G, nb, nmb, reference):
     (2, 2, 2, 128, 3, 256, "order_free"),
     (1, 2, 4, 29, 2, 64, "exact"),             # nothing quantized yet
     (1, 4, 1, 12400, 3, 12480, "exact"),       # few long rows: the softmax is split across CTAs (4 chunks)
-    (1, 2, 2, 12350, 2, 12416, "order_free"),  # split softmax with a residual tail in the last chunk
+    (1, 2, 2, 12350, 2, 12416, "order_free"),  # a row of 12416 scores: the 512-thread softmax with the probe fused in
+    (1, 2, 2, 19990, 2, 20032, "order_free"),  # split softmax (rows too long for one CTA), residual tail in the last chunk
+                                               # (heads in multiples of four: the reference's kernels, and with them
+                                               # the oracle, cover heads in groups of four)
     (1, 4, 1, 9000, 2, 9088, "exact"),         # rows too long for the register-cached softmax, too short to split:
                                                # plain softmax + separate probe and threshold launches
     (10, 8, 8, 100, 2, 128, "exact"),          # many rows (640): the probe is not fused into the softmax CTAs
