@@ -220,6 +220,13 @@ def test_decode_step_ex(akv_lib, B, H, G, prompt, steps, max_len, v_mode):
     assert akv_lib.akv_device_error_flag() == 0
 
 
+def test_device_error_flag_clear(akv_lib):
+    """The device error flag is zero after healthy runs, and akv_device_error_clear leaves it zero and returns 0."""
+    assert akv_lib.akv_device_error_flag() == 0
+    assert akv_lib.akv_device_error_clear() == 0
+    assert akv_lib.akv_device_error_flag() == 0
+
+
 def test_launch_count(akv_lib):
     """The library counts its own kernel launches: a decode step with one quantized block, no flush and a residual
     tail is append, q.K^T, softmax (+ probe), P.V (+ threshold), tail = 5 launches."""
