@@ -32,7 +32,10 @@ namespace akv {
 namespace kc {
 constexpr int TILES = 4;                         // 64-token blocks per warp unit
 constexpr int MAX_D = 256;
-constexpr int NMETA = 3;
+// Metadata slots per warp: the producer runs at most STAGES - 1 stages ahead of the consumer, which is less than one
+// unit's stages, so it is at most one (batch, KV head) ahead: two slots.  (A third is kept for multi-head attention,
+// whose slots are small and whose 16-channel stages make a unit only D/16 stages long.)
+__host__ __device__ constexpr int nmeta(int G) { return G > 1 ? 2 : 3; }
 __host__ __device__ constexpr int f_tile(int kch) { return kch * 64 + 64; }   // +64: tiles land on distinct banks
 __host__ __device__ constexpr int n_tile(int kch) { return kch * 32 + 32; }
 __host__ __device__ constexpr int stage_bytes(int kch) { return TILES * f_tile(kch) + 2 * TILES * n_tile(kch); }
@@ -95,6 +98,7 @@ __global__ void __launch_bounds__(G > 1 ? 256 : 512, 1) k_compute_kernel(const K
     const size_t tile_f = (size_t)p.D * 64, tile_n = (size_t)p.D * 32;
     const int META = meta_bytes(p.D, G), HMETA = head_meta(p.D);
 
+    constexpr int NMETA = nmeta(G);
     uint8_t* ring = smem + (size_t)warp * (STAGES * STAGE + NMETA * META + scratch_bytes(G));
     uint8_t* meta0 = ring + STAGES * STAGE;
     const uint32_t ring_a = smem_u32(ring);
@@ -404,7 +408,7 @@ int launch_k_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* 
     if (group > 1) stages = kch == 8 ? 4 : 3;
     else if (!((kch == 8 && (stages == 3 || stages == 4 || stages == 6)) || (kch == 16 && stages >= 3 && stages <= 5)))
         stages = (kch == 8) ? 4 : 3;
-    const int per_warp = stages * stage_bytes(kch) + NMETA * meta_bytes(D, group) + scratch_bytes(group);
+    const int per_warp = stages * stage_bytes(kch) + nmeta(group) * meta_bytes(D, group) + scratch_bytes(group);
     int wmax = budget / per_warp;
     if (wmax > (group > 1 ? 8 : 16)) wmax = group > 1 ? 8 : 16;   // (the grouped-query kernels are compiled for 256 threads)
     if (tuning().k_wpc > 0 && tuning().k_wpc < wmax) wmax = tuning().k_wpc;
