@@ -25,6 +25,10 @@ bool v_compute_takes_probe(const uint8_t*, const uint8_t*, const uint8_t*, const
                            int);
 int launch_v_compute_probe(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, const uint8_t*,
                            const uint8_t*, uint8_t*, int, int, int, int, int, int, int, int, cudaStream_t);
+int launch_v_compute_res(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, const uint8_t*,
+                         const uint8_t*, const uint8_t*, uint8_t*, int, int, int, int, int, int, int, int, cudaStream_t);
+bool v_compute_adds_residual(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, int, int, int,
+                             int, int, int, int);
 int launch_v_split(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, float*,
                    float*, int, int, int, int, int, int, int, int, cudaStream_t);
 int launch_v_split_probe(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, const uint8_t*,
@@ -228,7 +232,8 @@ __global__ void __launch_bounds__(NT)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
                uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats,
                const uint8_t* __restrict__ first8, uint16_t* __restrict__ test_o, int max_seq_len, int H, int G, int D,
-               int R, int qn, int rest, float sqrt_d, const __half* __restrict__ mask, long long mask_stride) {
+               int R, int qn, int rest, float sqrt_d, const __half* __restrict__ mask, long long mask_stride,
+               const __half* __restrict__ restv, uint16_t* __restrict__ res) {
     constexpr int NW = NT / 32;
     constexpr int REGS = NT == 512 ? SM_REGS_512 : SM_REGS;      // scores a thread keeps (CACHED)
     __shared__ float redf[NW];
@@ -355,6 +360,42 @@ softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __h
         }
         reinterpret_cast<uint32_t*>(test_o)[(size_t)bhq * (D >> 1) + c] = acc;
     }
+    if (res == nullptr || rest <= 0) return;              // (uniform)
+    // The residual tokens' part of the output, half(sum_r p[qn + r] * restv[r]) (extension/v_cache_file.py:189), for the
+    // P.V kernel to add in its epilogue - computed here by the threads the probe leaves idle (it occupies D/2 of them),
+    // so that no tail launch is needed.  Item = (channel pair, third of the tokens); fp32 sums, added in a fixed order.
+    __shared__ float part[3][256];
+    {
+        const int hd = D >> 1, idle0 = hd < NT ? hd : 0, nidle = NT - idle0;
+        if (tid >= idle0) {
+            for (int i = tid - idle0; i < 3 * hd; i += nidle) {
+                const int g = i / hd, c = i - g * hd;
+                const __half* vr = restv + ((size_t)b * BLK * H + h) * D + 2 * c;
+                const size_t vs = (size_t)H * D;
+                float pv[22];
+                __half2 vv[22];
+#pragma unroll
+                for (int j = 0; j < 22; ++j) {
+                    const int r = g + 3 * j;
+                    const bool on = r < rest;
+                    pv[j] = on ? __half2float(__ushort_as_half(row[qn + r])) : 0.f;
+                    vv[j] = on ? *reinterpret_cast<const __half2*>(vr + (size_t)r * vs) : __half2(__half(0.f), __half(0.f));
+                }
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 22; ++j) {
+                    const float2 f = __half22float2(vv[j]);
+                    a0 = fmaf(pv[j], f.x, a0);
+                    a1 = fmaf(pv[j], f.y, a1);
+                }
+                part[g][2 * c] = a0;
+                part[g][2 * c + 1] = a1;
+            }
+        }
+    }
+    __syncthreads();
+    for (int d = tid; d < D; d += NT)
+        res[(size_t)bhq * D + d] = __half_as_ushort(__float2half_rn((part[0][d] + part[1][d]) + part[2][d]));
 }
 
 // ------------------------------------------------------------------ softmax over long rows, split across CTAs
@@ -842,13 +883,24 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
     const int sm_chunks = (R + SM_CHUNK - 1) / SM_CHUNK;
     bool probed = false;
     const int rows = B * H * G;
-    if (R > 256 * SM_REGS && R <= 512 * SM_REGS_512 && rows <= 2 * sm_count()) {
+    const bool one_cta_512 = R > 256 * SM_REGS && R <= 512 * SM_REGS_512 && rows <= 2 * sm_count();
+    const bool one_cta_256 = !one_cta_512 && !(sm_chunks >= 4 && rows < 2 * sm_count()) && R <= 256 * SM_REGS &&
+                             rows <= 4 * sm_count();
+    // The residual tokens' part of the output without a launch of its own: the softmax CTA of a row computes it beside
+    // its probe (into o_main, as fp16), and the exact-order chain kernel adds it in its epilogue.
+    const bool fuse_tail = !order_free && !packed_out && qn > 0 && rest > 0 && D <= 256 && (one_cta_512 || one_cta_256) &&
+        v_compute_adds_residual(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                                static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s),
+                                static_cast<const uint8_t*>(out), B, H, G, D, R, qn, reference);
+    const __half* res_v = fuse_tail ? static_cast<const __half*>(restv) : nullptr;
+    uint16_t* res_o = fuse_tail ? sc.o_main : nullptr;
+    if (one_cta_512) {
         // few rows of up to 17408 scores: one CTA of 512 threads keeps the row in registers - one launch instead of the
         // four of the split form (statistics, probabilities, class reduction, probe)
         launch_chained(softmax_kernel<true, true, 512>, dim3(rows), dim3(512), 0, st, sc.s,
                        static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
                        static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn, rest,
-                       sqrtf((float)D), mk, mask_stride);
+                       sqrtf((float)D), mk, mask_stride, res_v, res_o);
         probed = true;
     } else if (sm_chunks >= 4 && B * H * G < 2 * sm_count()) {
         dim3 grid(sm_chunks, B * H * G);
@@ -868,17 +920,17 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
             launch_chained(softmax_kernel<true, true, 256>, dim3(B * H * G), dim3(256), 0, st, sc.s,
                            static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
                            static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn, rest,
-                           sqrtf((float)D), mk, mask_stride);
+                           sqrtf((float)D), mk, mask_stride, res_v, res_o);
             probed = true;
         } else {
             launch_chained(softmax_kernel<false, false, 256>, dim3(B * H * G), dim3(256), 0, st, sc.s,
                            static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
                            (const uint8_t*)nullptr, (uint16_t*)nullptr, max_seq_len, H, G, D, R, qn, rest,
-                           sqrtf((float)D), mk, mask_stride);
+                           sqrtf((float)D), mk, mask_stride, (const __half*)nullptr, (uint16_t*)nullptr);
         }
     }
     if ((rc = cuda_status(cudaGetLastError(), "decode_step softmax launch")) != AKV_OK) return rc;
-    const bool need_tail = rest > 0 || qn == 0 || packed_out != nullptr || order_free;
+    const bool need_tail = (rest > 0 && !fuse_tail) || qn == 0 || packed_out != nullptr || order_free;
     int v_chunks = 0;       // order-free P.V: chunk partials per row left for the tail kernel to add up
     if (qn > 0) {
         if (!probed) {
@@ -908,12 +960,13 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
                                       static_cast<const uint8_t*>(v_exp_max), nullptr, nullptr, sc.partial, &v_chunks, B,
                                       H, G, max_seq_len, D, R, qn, reference, st);
         else
-            rc = launch_v_compute_probe(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
-                                        static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s),
-                                        sc.amin, v_takes_probe ? (const uint8_t*)sc.test_o : nullptr,
-                                        static_cast<const uint8_t*>(v_exp_max),
-                                        reinterpret_cast<uint8_t*>(need_tail ? (void*)sc.o_main : out), B, H, G,
-                                        max_seq_len, D, R, qn, reference, st);
+            rc = launch_v_compute_res(static_cast<const uint8_t*>(v_first_8), static_cast<const uint8_t*>(v_mid_4),
+                                      static_cast<const uint8_t*>(v_last_4), reinterpret_cast<const uint8_t*>(sc.s),
+                                      sc.amin, v_takes_probe ? (const uint8_t*)sc.test_o : nullptr,
+                                      static_cast<const uint8_t*>(v_exp_max),
+                                      fuse_tail ? reinterpret_cast<const uint8_t*>(sc.o_main) : nullptr,
+                                      reinterpret_cast<uint8_t*>(need_tail ? (void*)sc.o_main : out), B, H, G,
+                                      max_seq_len, D, R, qn, reference, st);
         if (ev) cudaEventRecord(ev[3], st);
         if (rc != AKV_OK) return rc;
     } else if (order_free) {

@@ -60,6 +60,9 @@ struct VParams {
     int nf, nside, sch;     // streaming form: ring depth (stages), side-ring rows (power of two), stages per chunk
     int npt;                // streaming form: low-byte tables per head (even: half of them per decision warp)
     int units;              // streaming form: number of ring units (heads / heads per ring)
+    // streaming form: res != nullptr adds the residual tokens' part of the output, [B, Hq, D] fp16 computed by the
+    // softmax kernel: out = half(o + res) (extension/v_cache_file.py:189), which saves the tail launch
+    const uint16_t* res;
 };
 
 // ---- device error flag and shared-memory barriers (mbarrier) with bounded waits
@@ -633,6 +636,17 @@ __global__ void __launch_bounds__(NDW == 2 ? ((1 + NDW) * UPC * GH + UPC) * 32 :
                 accB = hfma2_bits(__byte_perm(hw, lw, 0x3726), sb | (sb << 16), accB);
             }
         }
+    }
+    if (p.res) {
+        const uint32_t* r = reinterpret_cast<const uint32_t*>(p.res) + (size_t)bh * 64;
+        auto add = [](uint32_t acc, uint32_t t) {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&acc));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t));
+            const __half2 c = __floats2half2_rn(a.x + b.x, a.y + b.y);
+            return *reinterpret_cast<const uint32_t*>(&c);
+        };
+        accA = add(accA, r[pairA]);
+        accB = add(accB, r[pairB]);
     }
     uint32_t* o = reinterpret_cast<uint32_t*>(p.o) + (size_t)bh * 64;
     o[pairA] = alive ? accA : 0x7E007E00u;

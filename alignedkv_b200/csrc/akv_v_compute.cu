@@ -548,10 +548,13 @@ bool v_compute_takes_probe(const uint8_t* first8, const uint8_t* mid4, const uin
 // are per (batch, query head) with query head = KV head * group + g.  test_o != nullptr (only when
 // v_compute_takes_probe() holds): the threshold bytes are computed in the kernel from the probe result and the
 // exponent maxima v_exp and written to amin_out; otherwise they are read from amin.
-int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
-                           uint8_t* amin, const uint8_t* test_o, const uint8_t* v_exp, uint8_t* o, int bsz, int H,
-                           int group, int max_seq_len, int D, int s_last_dim, int n, int reference, cudaStream_t st) {
+// res != nullptr (only when v_compute_adds_residual() holds): the kernel adds res [B, Hq, D] (fp16) to its result.
+int launch_v_compute_res(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                         uint8_t* amin, const uint8_t* test_o, const uint8_t* v_exp, const uint8_t* res, uint8_t* o,
+                         int bsz, int H, int group, int max_seq_len, int D, int s_last_dim, int n, int reference,
+                         cudaStream_t st) {
     VParams p;
+    p.res = reinterpret_cast<const uint16_t*>(res);
     p.first8 = first8; p.mid4 = mid4; p.last4 = last4;
     p.s = reinterpret_cast<const uint16_t*>(s);
     p.amin = amin;
@@ -564,7 +567,9 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
     const bool fast = v_compute_takes_probe(first8, mid4, last4, s, o, group, D, s_last_dim, n);
     AKV_REQUIRE(fast || !test_o, AKV_ERR_SHAPE, "v_cache_compute: the probe form needs the streaming kernel");
     const long long heads = (long long)BH * group;
-    if (fast && !reference && tuning().v_impl == 0 && heads < (1ll << 30)) {
+    const bool chain = fast && !reference && tuning().v_impl == 0 && heads < (1ll << 30);
+    AKV_REQUIRE(chain || !p.res, AKV_ERR_SHAPE, "v_cache_compute: the residual form needs the chain kernel");
+    if (chain) {
         // grouped queries: the heads of a KV head share one ring of high bytes in a CTA (gh = group); the form with
         // one ring per query head, whose heads meet in L2, stays selectable for measurements
         // (measured at 8192 tokens, 8 KV heads x 4: batch 8: 98 us grouped kernel, 84 shared ring, 65 ring per head;
@@ -588,6 +593,20 @@ int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uin
     count_launch();
     v_compute_generic_kernel<<<grid, 128, 0, st>>>(p, BH * group);
     return cuda_status(cudaGetLastError(), "v_cache_compute launch");
+}
+
+int launch_v_compute_probe(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                           uint8_t* amin, const uint8_t* test_o, const uint8_t* v_exp, uint8_t* o, int bsz, int H,
+                           int group, int max_seq_len, int D, int s_last_dim, int n, int reference, cudaStream_t st) {
+    return launch_v_compute_res(first8, mid4, last4, s, amin, test_o, v_exp, nullptr, o, bsz, H, group, max_seq_len, D,
+                                s_last_dim, n, reference, st);
+}
+
+// true when launch_v_compute_res runs the chain kernel, which can add the residual tokens' part to its result
+bool v_compute_adds_residual(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
+                             const uint8_t* o, int bsz, int H, int group, int D, int s_last_dim, int n, int reference) {
+    return v_compute_takes_probe(first8, mid4, last4, s, o, group, D, s_last_dim, n) && !reference &&
+           tuning().v_impl == 0 && (long long)bsz * H * group < (1ll << 30);
 }
 
 int launch_v_compute(const uint8_t* first8, const uint8_t* mid4, const uint8_t* last4, const uint8_t* s,
