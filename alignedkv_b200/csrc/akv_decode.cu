@@ -227,15 +227,17 @@ __device__ __forceinline__ void residual_scores(uint16_t* __restrict__ row, cons
 }
 
 // NT threads per CTA (256, or 512 for rows of up to 512*SM_REGS scores that one CTA keeps in registers).
-template <bool CACHED, bool PROBE, int NT>
-__global__ void __launch_bounds__(NT)
+// RG: scores a thread keeps in registers (CACHED): SM_REGS, or fewer for short rows - with 17 (rows of up to 4352
+// scores) two CTAs of 256 threads fit an SM instead of one, and 256 rows run as one wave.
+template <bool CACHED, bool PROBE, int NT, int RG = (NT == 512 ? SM_REGS_512 : SM_REGS)>
+__global__ void __launch_bounds__(NT, (RG <= 17 && NT == 256) ? 2 : 1)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
                uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats,
                const uint8_t* __restrict__ first8, uint16_t* __restrict__ test_o, int max_seq_len, int H, int G, int D,
                int R, int qn, int rest, float sqrt_d, const __half* __restrict__ mask, long long mask_stride,
                const __half* __restrict__ restv, uint16_t* __restrict__ res) {
     constexpr int NW = NT / 32;
-    constexpr int REGS = NT == 512 ? SM_REGS_512 : SM_REGS;      // scores a thread keeps (CACHED)
+    constexpr int REGS = RG;                                     // scores a thread keeps (CACHED)
     __shared__ float redf[NW];
     __shared__ uint32_t cand_v[NT];
     __shared__ int32_t cand_i[NT];
@@ -917,10 +919,16 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
     } else {
         if (R <= 256 * SM_REGS && B * H * G <= 4 * sm_count()) {
             // few rows: one pass over the row, and the probe runs inside the softmax CTA of its row
-            launch_chained(softmax_kernel<true, true, 256>, dim3(B * H * G), dim3(256), 0, st, sc.s,
-                           static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx, sc.stats,
-                           static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn, rest,
-                           sqrtf((float)D), mk, mask_stride, res_v, res_o);
+            if (R <= 256 * 17)
+                launch_chained(softmax_kernel<true, true, 256, 17>, dim3(B * H * G), dim3(256), 0, st, sc.s,
+                               static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx,
+                               sc.stats, static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn,
+                               rest, sqrtf((float)D), mk, mask_stride, res_v, res_o);
+            else
+                launch_chained(softmax_kernel<true, true, 256>, dim3(B * H * G), dim3(256), 0, st, sc.s,
+                               static_cast<const __half*>(q), static_cast<const __half*>(restk), sc.pval, sc.pidx,
+                               sc.stats, static_cast<const uint8_t*>(v_first_8), sc.test_o, max_seq_len, H, G, D, R, qn,
+                               rest, sqrtf((float)D), mk, mask_stride, res_v, res_o);
             probed = true;
         } else {
             launch_chained(softmax_kernel<false, false, 256>, dim3(B * H * G), dim3(256), 0, st, sc.s,
