@@ -230,7 +230,7 @@ __device__ __forceinline__ void residual_scores(uint16_t* __restrict__ row, cons
 // RG: scores a thread keeps in registers (CACHED): SM_REGS, or fewer for short rows - with 17 (rows of up to 4352
 // scores) two CTAs of 256 threads fit an SM instead of one, and 256 rows run as one wave.
 template <bool CACHED, bool PROBE, int NT, int RG = (NT == 512 ? SM_REGS_512 : SM_REGS)>
-__global__ void __launch_bounds__(NT, (RG <= 17 && NT == 256) ? 2 : 1)
+__global__ void __launch_bounds__(NT, (RG <= 17 && NT == 256) ? 2 : 0)
 softmax_kernel(uint16_t* __restrict__ s, const __half* __restrict__ q, const __half* __restrict__ restk,
                uint16_t* __restrict__ pval, int32_t* __restrict__ pidx, float* __restrict__ stats,
                const uint8_t* __restrict__ first8, uint16_t* __restrict__ test_o, int max_seq_len, int H, int G, int D,
