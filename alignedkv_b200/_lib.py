@@ -35,6 +35,14 @@ SIGNATURES = {
     "akv_decode_step_masked": (_I, [_P] * 16 + [ctypes.c_longlong, _P, ctypes.c_longlong] + [_I] * 8 + [_P]),
     "akv_shard_step": (_I, [_P] * 16 + [ctypes.c_longlong] + [_I] * 13 + [_P]),
     "akv_lse_merge": (_I, [_P] * 2 + [_I] * 3 + [_P]),
+    "akv_exchange_bytes": (ctypes.c_longlong, [_I] * 3),
+    "akv_peer_alloc": (_I, [ctypes.c_longlong, ctypes.POINTER(ctypes.c_void_p), _P]),
+    "akv_peer_open": (_I, [_P, ctypes.POINTER(ctypes.c_void_p)]),
+    "akv_peer_close": (_I, [_P]),
+    "akv_peer_free": (_I, [_P]),
+    "akv_exchange_merge": (_I, [ctypes.POINTER(ctypes.c_void_p), _I, _I, _P, _P, _I, _I, ctypes.c_uint, _I, _P]),
+    "akv_decode_step_exchange": (_I, [_P] * 16 + [ctypes.c_longlong] + [_I] * 8 + [ctypes.POINTER(ctypes.c_void_p), _I, _I,
+                                                                               ctypes.c_uint, _I, _P]),
     "akv_rollback": (_I, [_P] * 6 + [_I] * 6 + [_P]),
     "akv_prefill": (_I, [_P] * 13 + [ctypes.c_longlong] + [_I] * 5 + [_P]),
     "akv_prefill_scratch_bytes": (ctypes.c_longlong, [_I] * 4),

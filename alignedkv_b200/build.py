@@ -9,7 +9,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libalignedkv_b200.so")
-SOURCES = ["akv_api.cu", "akv_save.cu", "akv_k_compute.cu", "akv_v_compute.cu", "akv_v_split.cu", "akv_decode.cu", "akv_prefill.cu"]
+SOURCES = ["akv_api.cu", "akv_save.cu", "akv_k_compute.cu", "akv_v_compute.cu", "akv_v_split.cu", "akv_decode.cu", "akv_prefill.cu",
+           "akv_exchange.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

@@ -10,6 +10,7 @@
 //   probe       akv_v_compute.cu, then the threshold byte per (batch, head) with the reference's [B,H,H,D] broadcast
 //   P.V         akv_v_compute.cu
 //   tail        adds the residual tokens' contribution
+#include "akv_exchange.cuh"
 #include "akv_save.cuh"
 
 namespace akv {
@@ -603,11 +604,12 @@ amin_kernel(const uint16_t* __restrict__ test_o, const uint8_t* __restrict__ v_e
 // out = half(o_main + half(sum_r p[qn+r] * restv[r])) (v_cache_file.py:189); grid B*Hq.  With an fp32 main result
 // (order-free P.V) the residual sum is added in fp32 and rounded once.  packed (optional): one row
 // (max score, sum of exponentials, output[0..D-1]) in fp32 per (batch, query head), the record ranks exchange when
-// the sequence is sharded.
+// the sequence is sharded.  x.R > 0: the CTA then exchanges its record with the other ranks through peer memory and
+// writes the merged row (x.out).
 __global__ void __launch_bounds__(256)
 tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_main32, const uint16_t* __restrict__ p,
             const __half* __restrict__ restv, __half* __restrict__ out, const float* __restrict__ stats,
-            float* __restrict__ packed, int H, int G, int D, int R, int qn, int rest, int chunks) {
+            float* __restrict__ packed, int H, int G, int D, int R, int qn, int rest, int chunks, const XchgParams x) {
     pdl_enter();
     const int bhq = blockIdx.x, Hq = H * G, b = bhq / Hq, h = (bhq - b * Hq) / G;
     // residual sum: item = (channel pair, quarter g of the tokens: r = g, g+4, ...), all of an item's loads in flight
@@ -658,6 +660,12 @@ tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_mai
     if (packed && threadIdx.x == 0) {
         packed[(size_t)bhq * (D + 2)] = stats[(size_t)bhq * 2];
         packed[(size_t)bhq * (D + 2) + 1] = stats[(size_t)bhq * 2 + 1];
+    }
+    if (x.R > 0) {
+        // sequence shards: the row's record goes to every rank and the merged row comes back (akv_exchange.cuh)
+        __shared__ uint8_t* s_buf[XCHG_MAX_RANKS];
+        __syncthreads();
+        exchange_merge_row(x, packed + (size_t)bhq * (D + 2), bhq, s_buf);
     }
 }
 
@@ -802,12 +810,46 @@ int akv_decode_step_ex(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_f
                                   n_kv_heads, group, head_dim, max_seq_len, rest_len, rest_start, flags, stream);
 }
 
+static int decode_step_impl(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                            void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                            const void* v_new, void* out, void* packed_out, const void* mask, long long mask_stride,
+                            void* scratch, long long scratch_bytes, int bsz, int n_kv_heads, int group, int head_dim,
+                            int max_seq_len, int rest_len, int rest_start, int flags, void* stream, const XchgParams& xp);
+
 int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
                            void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
                            const void* v_new, void* out, void* packed_out, const void* mask, long long mask_stride,
                            void* scratch, long long scratch_bytes, int bsz, int n_kv_heads, int group, int head_dim,
                            int max_seq_len, int rest_len, int rest_start, int flags, void* stream) {
     set_error("");
+    return decode_step_impl(k_first_8, k_mid_4, k_last_4, v_first_8, v_mid_4, v_last_4, k_exp_max, v_exp_max, restk, restv,
+                            q, k_new, v_new, out, packed_out, mask, mask_stride, scratch, scratch_bytes, bsz, n_kv_heads,
+                            group, head_dim, max_seq_len, rest_len, rest_start, flags, stream, XchgParams{});
+}
+
+int akv_decode_step_exchange(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4,
+                             void* v_last_4, void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q,
+                             const void* k_new, const void* v_new, void* merged_out, void* packed_out, void* scratch,
+                             long long scratch_bytes, int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len,
+                             int rest_len, int rest_start, int flags, void* const* bufs, int rank, int n_ranks,
+                             unsigned int epoch, int timeout_ms, void* stream) {
+    set_error("");
+    AKV_REQUIRE(packed_out && merged_out, AKV_ERR_NULL, "decode_step_exchange: null pointer");
+    AKV_REQUIRE(bsz > 0 && n_kv_heads > 0 && group > 0, AKV_ERR_SHAPE, "decode_step_exchange: bad extent");
+    XchgParams xp;
+    const int rc = fill_exchange(&xp, bufs, rank, n_ranks, merged_out, bsz * n_kv_heads * group, head_dim, epoch,
+                                 timeout_ms);
+    if (rc != AKV_OK) return rc;
+    return decode_step_impl(k_first_8, k_mid_4, k_last_4, v_first_8, v_mid_4, v_last_4, k_exp_max, v_exp_max, restk, restv,
+                            q, k_new, v_new, nullptr, packed_out, nullptr, 0, scratch, scratch_bytes, bsz, n_kv_heads,
+                            group, head_dim, max_seq_len, rest_len, rest_start, flags, stream, xp);
+}
+
+static int decode_step_impl(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4, void* v_last_4,
+                            void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q, const void* k_new,
+                            const void* v_new, void* out, void* packed_out, const void* mask, long long mask_stride,
+                            void* scratch, long long scratch_bytes, int bsz, int n_kv_heads, int group, int head_dim,
+                            int max_seq_len, int rest_len, int rest_start, int flags, void* stream, const XchgParams& xp) {
     AKV_REQUIRE(!mask || ((reinterpret_cast<uintptr_t>(mask) & 1u) == 0 && mask_stride >= 0), AKV_ERR_ALIGN,
                 "decode_step: the mask must be 2-byte aligned with a non-negative row stride");
     const __half* mk = static_cast<const __half*>(mask);
@@ -987,7 +1029,7 @@ int akv_decode_step_masked(void* k_first_8, void* k_mid_4, void* k_last_4, void*
                        (const uint16_t*)((qn > 0 && !order_free) ? sc.o_main : nullptr),
                        (const float*)(order_free ? (v_chunks > 0 ? sc.partial : sc.o_main32) : nullptr), (const uint16_t*)sc.s,
                        static_cast<const __half*>(restv), static_cast<__half*>(out), (const float*)sc.stats,
-                       static_cast<float*>(packed_out), H, G, D, R, qn, rest, v_chunks);
+                       static_cast<float*>(packed_out), H, G, D, R, qn, rest, v_chunks, xp);
         if ((rc = cuda_status(cudaGetLastError(), "decode_step tail launch")) != AKV_OK) return rc;
     }
     return AKV_OK;
@@ -1126,7 +1168,7 @@ int akv_shard_step(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first
     g_shard_timing = nullptr;
     launch_chained(tail_kernel, dim3(rows), dim3(256), 0, st, (const uint16_t*)nullptr, (const float*)sc.o_main32,
                    (const uint16_t*)sc.s, static_cast<const __half*>(restv), static_cast<__half*>(nullptr),
-                   (const float*)sc.stats, static_cast<float*>(exch_out), H, G, D, R, qn, rest, 0);
+                   (const float*)sc.stats, static_cast<float*>(exch_out), H, G, D, R, qn, rest, 0, XchgParams{});
     return cuda_status(cudaGetLastError(), "shard_step tail launch");
 }
 

@@ -677,6 +677,10 @@ int launch_v_split_stream(const uint8_t* first8, const uint8_t* mid4, const uint
     return launch_v_stream(p, BH, st);
 }
 
+// (the peer exchange kernel keeps a flag of its own: akv_exchange.cu)
+unsigned int exchange_error_flag(cudaError_t* e);
+cudaError_t exchange_error_clear();
+
 }  // namespace akv
 
 extern "C" int akv_device_error_flag(void) {
@@ -685,6 +689,8 @@ extern "C" int akv_device_error_flag(void) {
     unsigned int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, akv::g_v_wait_gave_up, sizeof(v));
     if (e != cudaSuccess) return akv::cuda_status(e, "device_error_flag");
+    v |= akv::exchange_error_flag(&e);
+    if (e != cudaSuccess) return akv::cuda_status(e, "device_error_flag");
     return (int)v;
 }
 
@@ -692,6 +698,7 @@ extern "C" int akv_device_error_clear(void) {
     // Puts the flag back to zero (after the caller has dealt with a run that raised it).  Synchronises the device.
     const unsigned int v = 0;
     cudaError_t e = cudaMemcpyToSymbol(akv::g_v_wait_gave_up, &v, sizeof(v));
+    if (e == cudaSuccess) e = akv::exchange_error_clear();
     if (e != cudaSuccess) return akv::cuda_status(e, "device_error_clear");
     return AKV_OK;
 }

@@ -282,24 +282,7 @@ __global__ void __launch_bounds__(128)
 lse_merge_kernel(const float* __restrict__ packed, __half* __restrict__ out, int R, int rows, int D) {
     const int i = blockIdx.x;
     const int W = D + 2;
-    float M = -INFINITY;
-    for (int g = 0; g < R; ++g) {
-        const float l = packed[((size_t)g * rows + i) * W + 1];
-        if (l > 0.f) M = fmaxf(M, packed[((size_t)g * rows + i) * W]);
-    }
-    float denom = 0.f;
-    for (int g = 0; g < R; ++g) {
-        const float l = packed[((size_t)g * rows + i) * W + 1];
-        if (l > 0.f) denom += l * expf(packed[((size_t)g * rows + i) * W] - M);
-    }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float v = 0.f;
-        for (int g = 0; g < R; ++g) {
-            const float* row = packed + ((size_t)g * rows + i) * W;
-            if (row[1] > 0.f) v += (row[1] * expf(row[0] - M) / denom) * row[2 + d];
-        }
-        out[(size_t)i * D + d] = __float2half_rn(denom > 0.f ? v : 0.f);
-    }
+    lse_merge_row(packed + (size_t)i * W, (size_t)rows * W, R, D, out + (size_t)i * D, threadIdx.x, blockDim.x);
 }
 
 int launch_lse_merge(const float* packed, uint8_t* out, int R, int rows, int D, cudaStream_t st) {

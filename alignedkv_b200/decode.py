@@ -118,7 +118,7 @@ class DecodeLayer:
     # ------------------------------------------------------------------ one decode token
     def decode(self, q: torch.Tensor, k: torch.Tensor | None = None, v: torch.Tensor | None = None, *,
                append: bool = True, packed: bool = False, out: torch.Tensor | None = None,
-               mask: torch.Tensor | None = None):
+               mask: torch.Tensor | None = None, exchange=None):
         """Append (k, v) of one token per sequence and return the attention output [B,1,Hq,D] (fp16; written into
         `out` when given).
 
@@ -128,7 +128,14 @@ class DecodeLayer:
 
         mask: the additive attention mask of the reference's caller (model/KVCache_AlignedKV.py:119-120), an fp16 CUDA
         tensor of shape [B,1,1,n] or [1,1,1,n] with n >= the cache length after this step (one row per batch row,
-        broadcast over the heads); it is added to the fp16 scores in fp16 before the fp32 softmax."""
+        broadcast over the heads); it is added to the fp16 scores in fp16 before the fp32 softmax.
+
+        exchange: the ranks' exchange buffers (`sharded.PeerExchange`) when this layer holds one shard of a sequence:
+        the step's last kernel then stores the packed record into every rank's buffer, waits for the others' and the
+        call returns the MERGED attention output [B,1,Hq,D], the same on every rank (`akv_decode_step_exchange`)."""
+        if exchange is not None and (packed or mask is not None):
+            raise RuntimeError("exchange: not together with packed or mask")
+        packed = packed or exchange is not None
         B, H, Hq, D = self.B, self.H, self.Hq, self.D
         mask_ptr, mask_stride = None, 0
         if mask is not None:
@@ -164,11 +171,17 @@ class DecodeLayer:
             out.data_ptr() if out is not None else None, rec.data_ptr() if rec is not None else None,
             mask_ptr, mask_stride, ptrs[10], ptrs[11], B, H, self.G, D, self.L, self.rest_len, self.rest_start,
             self._flags(append), torch.cuda.current_stream(self.device).cuda_stream)
+        fn = self.lib.akv_decode_step_masked
+        if exchange is not None:
+            out = torch.empty((B, 1, Hq, D), dtype=torch.half, device=self.device)
+            fn = self.lib.akv_decode_step_exchange
+            args = args[:13] + (out.data_ptr(),) + args[14:15] + args[17:27] + (
+                exchange.bufs, exchange.rank, exchange.world, exchange.next_epoch(), exchange.timeout_ms, args[27])
         if torch.cuda.current_device() == self.device.index:
-            rc = self.lib.akv_decode_step_masked(*args)
+            rc = fn(*args)
         else:
             with torch.cuda.device(self.device):
-                rc = self.lib.akv_decode_step_masked(*args)
+                rc = fn(*args)
         _lib.check("decode_step", rc)
         self.last_q = q                                   # (for bytes_accounting)
         flush = append and self.rest_len + 1 == column_block
@@ -177,7 +190,7 @@ class DecodeLayer:
         self.rest_len, self.rest_start = rest, qn
         if append:
             self.cache_len += 1
-        return rec if packed else out
+        return out if exchange is not None else (rec if packed else out)
 
     # ------------------------------------------------------------------ benchmark helpers
     def snapshot(self):

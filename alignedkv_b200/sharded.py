@@ -7,8 +7,11 @@ Two ways to shard, neither of which exists in the reference (it is single-device
 * sequence sharding for long contexts - `SequenceShardedDecoder`: the cached tokens are split into contiguous,
   64-aligned shards, one per rank.  Every rank receives the query, runs the aligned q.K^T / softmax / P.V over its
   own shard and produces, per (batch, query head), the record (m, l, o): maximum score, sum of exponentials and
-  locally normalised output.  One all-gather of those records ((D+2) floats per row and rank, over NCCL) followed by
-  a log-sum-exp merge kernel gives every rank the full attention output.  New tokens are appended on the last rank.
+  locally normalised output.  The records ((D+2) floats per row and rank) are exchanged and merged (log-sum-exp) by
+  ONE kernel per rank that stores its record into every rank's exchange buffer over NVLink, publishes a flag and
+  waits, time-bounded, for the others' (`PeerExchange`, `akv_exchange_merge`); where peer memory cannot be set up
+  (or on request) an NCCL all-gather followed by the merge kernel does the same.  Every rank ends up with the full
+  attention output.  New tokens are appended on the last rank.
   Read decisions are taken from each shard's own softmax and magnitude probe, so they can differ from a
   single-device run over the whole sequence; the merged output is compared against fp32 dense attention.
 * the same split, decision-exact - `DecisionExactShardedDecoder`: the step is cut into four phases
@@ -62,6 +65,10 @@ class _CudaBackend:
     def record(self, q, k, v, append):
         return self.layer.decode(q, k, v, append=append, packed=True)
 
+    def decode_exchange(self, q, k, v, append, peer):
+        """The local step with the exchange and the merge inside its last kernel: the merged output [B,1,Hq,D]."""
+        return self.layer.decode(q, k, v, append=append, exchange=peer)
+
     def merge(self, gathered, rows, head_dim):
         out = torch.empty((rows, head_dim), dtype=torch.half, device=self.device)
         with torch.cuda.device(self.device):
@@ -71,14 +78,111 @@ class _CudaBackend:
         return out
 
 
+class PeerExchange:
+    """Exchange buffers of the ranks of `group` for `akv_exchange_merge`: every rank allocates one, the 64-byte IPC
+    handles travel through one all-gather, every rank maps the others' buffers.  All ranks must sit on GPUs of one
+    node with peer access to each other.  `setup` raises on EVERY rank when it failed on any of them."""
+
+    MAX_RANKS = 8
+
+    def __init__(self, rows: int, head_dim: int, device, group=None, timeout_ms: int = 2000):
+        import ctypes
+        import torch.distributed as dist
+        self.lib = _lib.load()
+        self.device = torch.device(device)
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.rows, self.D, self.timeout_ms = rows, head_dim, timeout_ms
+        self.epoch = 0
+        self.own = None
+        self.mapped = []
+        if self.world > self.MAX_RANKS:
+            raise ValueError(f"peer exchange covers at most {self.MAX_RANKS} ranks, the group has {self.world}")
+        nbytes = self.lib.akv_exchange_bytes(self.world, rows, head_dim)
+        handle = (ctypes.c_ubyte * 64)()
+        own = ctypes.c_void_p()
+        err = None
+        with torch.cuda.device(self.device):
+            rc = self.lib.akv_peer_alloc(nbytes, ctypes.byref(own), handle)
+            if rc != 0:
+                err = self.lib.akv_last_error().decode("utf-8", "replace")
+            else:
+                self.own = own.value
+            mine = torch.tensor(list(handle) + [0 if err is None else 1, torch.cuda.current_device()],
+                                dtype=torch.uint8, device=self.device)
+            every = torch.empty((self.world, 66), dtype=torch.uint8, device=self.device)
+            dist.all_gather_into_tensor(every, mine, group=group)
+            every = every.cpu()
+            ptrs = [None] * self.world
+            if len(set(every[:, 65].tolist())) != self.world:
+                # two ranks on one GPU: their exchange kernels would wait for each other on the same device
+                err = "two ranks of the group run on the same GPU"
+            elif err is None and int(every[:, 64].sum()) == 0:
+                for g in range(self.world):
+                    if g == self.rank:
+                        ptrs[g] = self.own
+                        continue
+                    h = (ctypes.c_ubyte * 64)(*every[g, :64].tolist())
+                    p = ctypes.c_void_p()
+                    rc = self.lib.akv_peer_open(h, ctypes.byref(p))
+                    if rc != 0:
+                        err = self.lib.akv_last_error().decode("utf-8", "replace")
+                        break
+                    self.mapped.append(p.value)
+                    ptrs[g] = p.value
+            elif err is None:
+                err = "another rank could not allocate its exchange buffer"
+            ok = torch.tensor([0 if err is None else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(ok, group=group)          # (also: nobody stores into a buffer before every rank mapped it)
+        if int(ok.item()) != 0:
+            self.close()
+            raise RuntimeError("peer exchange set-up failed" + (f": {err}" if err else " on another rank"))
+        self.bufs = (ctypes.c_void_p * self.world)(*ptrs)
+
+    def next_epoch(self) -> int:
+        """The epoch of the next exchange (every rank calls this once per step): never 0, and its parity alternates,
+        also across the wrap."""
+        self.epoch = self.epoch % 0x7FFFFFFE + 1
+        return self.epoch
+
+    def merge(self, rec: torch.Tensor) -> torch.Tensor:
+        """rec: this rank's packed fp32 [rows, D+2] -> merged fp16 [rows, D] (one launch on the current stream)."""
+        self.next_epoch()
+        out = torch.empty((self.rows, self.D), dtype=torch.half, device=self.device)
+        rec = rec.contiguous()
+        with torch.cuda.device(self.device):
+            rc = self.lib.akv_exchange_merge(self.bufs, self.rank, self.world, rec.data_ptr(), out.data_ptr(), self.rows,
+                                             self.D, self.epoch, self.timeout_ms,
+                                             torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check("exchange_merge", rc)
+        return out
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (call it on every rank, after a barrier: nobody may still
+        store into a buffer that is being freed)."""
+        with torch.cuda.device(self.device):
+            for p in self.mapped:
+                self.lib.akv_peer_close(p)
+            self.mapped = []
+            if self.own is not None:
+                torch.cuda.synchronize(self.device)
+                self.lib.akv_peer_free(self.own)
+                self.own = None
+
+
 class SequenceShardedDecoder:
     """One layer's cache with the sequence split across the ranks of `group` (see the module docstring).
 
     backend: object with prefill(k, v), record(q, k, v, append) -> fp32 [B*Hq, D+2] and merge(gathered, rows, D);
-    the default drives the CUDA kernels.  Tests substitute a CPU implementation to exercise the protocol with gloo."""
+    the default drives the CUDA kernels.  Tests substitute a CPU implementation to exercise the protocol with gloo.
+    exchange: "peer" (records exchanged through peer memory and merged at the end of the step's last kernel),
+    "peer_unfused" (the same exchange as a kernel of its own after the step), "collective" (all-gather + merge
+    kernel) or "auto": peer memory with the CUDA backend on 2..8 ranks when it can be set up on all of them, else the
+    collective; `self.exchange` says which one runs."""
 
     def __init__(self, bsz: int, prompt_len: int, max_new_tokens: int, n_kv_heads: int, head_dim: int, device,
-                 n_q_heads: int | None = None, v_mode: str = "order_free", group=None, backend=None):
+                 n_q_heads: int | None = None, v_mode: str = "order_free", group=None, backend=None,
+                 exchange: str = "auto"):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -94,6 +198,21 @@ class SequenceShardedDecoder:
         max_local = max(BLOCK, -(-max_local // BLOCK) * BLOCK)
         self.backend = backend if backend is not None else _CudaBackend(bsz, max_local, n_kv_heads, head_dim, device,
                                                                         self.Hq, v_mode)
+        if exchange not in ("auto", "peer", "peer_unfused", "collective"):
+            raise ValueError(f"exchange must be 'auto', 'peer', 'peer_unfused' or 'collective', not {exchange!r}")
+        self.peer = None
+        self.exchange_note = ""
+        wants_peer = exchange in ("peer", "peer_unfused") or (exchange == "auto" and backend is None and 2 <= self.world <= PeerExchange.MAX_RANKS
+                                            and torch.device(device).type == "cuda")
+        if wants_peer and self.world > 1:
+            try:
+                self.peer = PeerExchange(bsz * self.Hq, head_dim, device, group)
+            except RuntimeError as e:                 # (raised on every rank alike)
+                if exchange != "auto":
+                    raise
+                self.exchange_note = str(e)
+        self.exchange = "collective" if self.peer is None else ("peer_unfused" if exchange == "peer_unfused" else "peer")
+        self.fused = self.exchange == "peer" and hasattr(self.backend, "decode_exchange")
 
     def prefill(self, k_shard, v_shard) -> None:
         """k_shard, v_shard: this rank's tokens [B, hi-lo, H, D] of the prompt (ranks load their own shard)."""
@@ -105,8 +224,13 @@ class SequenceShardedDecoder:
     def decode(self, q, k_new, v_new):
         """q [B,1,Hq,D], k_new / v_new [B,1,H,D] (used on the last rank only) -> merged output [B,1,Hq,D] on every
         rank."""
+        if self.peer is not None and self.fused:
+            return self.backend.decode_exchange(q, k_new if self.is_last else None, v_new if self.is_last else None,
+                                                self.is_last, self.peer)
         rec = self.backend.record(q, k_new if self.is_last else None, v_new if self.is_last else None, self.is_last)
         rows = self.B * self.Hq
+        if self.peer is not None:
+            return self.peer.merge(rec.reshape(rows, self.D + 2)).reshape(self.B, 1, self.Hq, self.D)
         if self.world == 1:
             gathered = rec.reshape(1, rows, self.D + 2)
         else:

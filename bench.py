@@ -46,6 +46,9 @@ WORKLOADS = {
                                      v_mode="exact"),
     "long-context-decode": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072, sharding="sequence",
                                 v_mode="order_free"),
+    # one rank's shard of that sequence on 8 ranks, by itself (what a sharded step costs without its exchange)
+    "long-context-decode-shard8": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=16384,
+                                       sharding="replicate", v_mode="order_free"),
     # the same with the four-phase step whose read decisions are those of one device holding the whole sequence
     "long-context-decode-exact": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072,
                                       sharding="sequence_exact", v_mode="order_free"),
@@ -79,6 +82,10 @@ def parse():
     ap.add_argument("--v-mode", default=None, choices=["exact", "order_free"],
                     help="P.V kernel: exact = the reference's token order (bit-identical), order_free = split sequence, "
                          "fp32 accumulation (default: per workload)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "peer_unfused", "collective"],
+                    help="sequence-sharded workloads: how the shards' results meet - through peer memory at the end of the "
+                         "step's last kernel (peer) or in a kernel of its own (peer_unfused), or an NCCL all-gather "
+                         "followed by the merge kernel (auto: peer where it can be set up)")
     args = ap.parse_args()
     WORKLOAD.clear()
     WORKLOAD.update(name=args.workload, **WORKLOADS[args.workload])
@@ -90,7 +97,8 @@ RUN_TOKENS = 64     # consecutive decode tokens before the cache is rewound: one
 SHARDING_TEXT = {
     "replicate": "(batch, kv-head) units, no collective; every rank runs the full shape",
     "batch": "batch rows split across ranks, no collective",
-    "sequence": "cached sequence split across ranks; one all-gather of (max, sum, output) records + log-sum-exp merge",
+    "sequence": "cached sequence split across ranks; (max, sum, output) records exchanged and merged (log-sum-exp): see "
+                "`exchange`",
     "sequence_exact": "cached sequence split across ranks at multiples of 4096 tokens; four-phase step (akv_shard_step) "
                       "with exchanges of chunk statistics, probe candidates, winner rows and partial outputs: read "
                       "decisions of one device holding the whole sequence",
@@ -295,7 +303,8 @@ def measure(name, args, ctx, min_seconds):
 
     if sharding == "sequence":
         # rank r holds tokens [lo, hi) of the L-1 cached tokens; the last rank also takes the decode token
-        seq = SequenceShardedDecoder(B, L - 1, RUN_TOKENS + 1, H, D, dev, n_q_heads=Hq, v_mode=v_mode)
+        seq = SequenceShardedDecoder(B, L - 1, RUN_TOKENS + 1, H, D, dev, n_q_heads=Hq, v_mode=v_mode,
+                                     exchange=args.exchange)
         lo, hi = shard_bounds(L - 1, world)[rank]
         k, v = draw(hi - lo + 1)
         seq.prefill(k[:, :hi - lo].contiguous(), v[:, :hi - lo].contiguous())
@@ -374,15 +383,18 @@ def measure(name, args, ctx, min_seconds):
         for _ in range(warmup):
             stepper(fn)
         own, worst, counts = [], [], []
+        host_us = timed_blocks.host_us = []
         t0 = time.time()
         while len(worst) < 3 or (sum(worst) < seconds * 1e3 and len(worst) < 400):
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             n0 = layer.launches
+            h0 = time.perf_counter()
             e0.record()
             for _ in range(steps):
                 stepper(fn)
             e1.record()
+            host_us.append((time.perf_counter() - h0) / steps * 1e6)   # the host's share: enqueueing the block
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
             counts.append(layer.launches - n0)
@@ -396,10 +408,12 @@ def measure(name, args, ctx, min_seconds):
         t1 = time.time()
         per_rank = None
         if world > 1:
-            mine = torch.tensor([min(own), statistics.median(own), max(own)], device=dev, dtype=torch.float64)
+            mine = torch.tensor([min(own), statistics.median(own), max(own), statistics.median(host_us) * steps * 1e-3],
+                                device=dev, dtype=torch.float64)
             allr = [torch.zeros_like(mine) for _ in range(world)]
             dist.all_gather(allr, mine)
-            per_rank = [[round(float(x) / steps * 1e3, 2) for x in r.tolist()] for r in allr]   # us per step
+            per_rank = [[round(float(x) / steps * 1e3, 2) for x in r.tolist()[:3]] for r in allr]   # us per step
+            timed_blocks.host_us_per_rank = [round(float(r[3]) / steps * 1e3, 2) for r in allr]
         return worst, per_rank, t0, t1, counts
 
     warm = max(args.warmup, 3)
@@ -432,6 +446,8 @@ def measure(name, args, ctx, min_seconds):
     sampler = ClockSampler(ctx["local"])                   # every rank watches its own GPU
     sampler.start()
     blocks, per_rank, t0, t1, counts = timed_blocks(step_resident, args.steps, warm, min_seconds, in_run)   # no instrumentation inside
+    host_enqueue_us = statistics.median(timed_blocks.host_us)
+    host_enqueue_per_rank = getattr(timed_blocks, "host_us_per_rank", None) if world > 1 else None
     clocks = sampler.stop(t0, time.time())
     if world > 1:
         # the block time is the maximum over the ranks: the clocks and power of every rank's GPU beside its own times
@@ -494,6 +510,8 @@ def measure(name, args, ctx, min_seconds):
     cfg = config_dict(name, world, v_mode)
     if isinstance(seq, DecisionExactShardedDecoder):
         cfg["sharding"] = SHARDING_TEXT["sequence_exact"]
+    if isinstance(seq, SequenceShardedDecoder):
+        cfg["exchange"] = seq.exchange + (f" ({seq.exchange_note})" if seq.exchange_note else "")
     return {
         "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
@@ -505,9 +523,13 @@ def measure(name, args, ctx, min_seconds):
                    "block_ms_min": min(blocks),
                    "block_ms_max": max(blocks), "seconds_timed": sum(blocks) * 1e-3,
                    "per_rank_us_per_step_min_median_max": per_rank,
+                   "host_enqueue_us_per_step": round(host_enqueue_us, 2),
+                   "host_enqueue_us_per_step_per_rank": host_enqueue_per_rank,
                    "rule": "every block = exactly `steps` steps between barrier + synchronize pairs, CUDA events, max "
                            "over ranks; the reported step time is the median block when a block holds whole runs of "
-                           "%d tokens (the default), else the mean over the blocks" % RUN_TOKENS},
+                           "%d tokens (the default), else the mean over the blocks; host_enqueue_us_per_step = wall "
+                           "time rank 0's host needed to enqueue a block, per step (a step whose device time is close "
+                           "to it is bound by the host, not by the GPU)" % RUN_TOKENS},
         "effective_hbm_gbs": total["dense"] / (ms_step * 1e-3) / 1e9,
         "achieved_hbm_gbs": total["read"] / (ms_step * 1e-3) / 1e9,
         "bytes_read_over_dense": total["read"] / total["dense"],

@@ -241,6 +241,49 @@ int akv_rollback(void* k_mid_4, void* k_last_4, void* k_exp_max, void* v_exp_max
 int akv_lse_merge(const void* packed, void* out, int n_ranks, int rows, int head_dim, void* stream);
 
 /*
+ * The same merge with the exchange inside the kernel, through peer memory (no counterpart in the reference): one launch
+ * per decode step on every rank replaces the all-gather of the shards' packed results and akv_lse_merge.
+ * Every rank (one process per GPU of one node, at most 8) owns an exchange buffer of akv_exchange_bytes() bytes,
+ * zero at the start, and maps the other ranks' buffers:
+ *   akv_peer_alloc   device memory of the current device (cleared) and the 64-byte handle another process opens it by;
+ *   akv_peer_open    another process's buffer, by the handle that process got (CUDA IPC; the address is valid in the
+ *                    calling process only; peer access between the two GPUs is enabled on first use);
+ *   akv_peer_close / akv_peer_free   undo the two (close every mapping of a buffer before its owner frees it).
+ * Buffer layout for R ranks, rows = B*Hq, W = head_dim + 2: float data[2][R][rows][W] (slot g written by rank g, two
+ * epochs deep), then from the next multiple of 128 bytes uint32 flags[2][R][rows] (the epoch whose record is there).
+ * akv_exchange_merge(bufs, rank, ...): bufs[g] = the calling process's address of rank g's buffer (bufs[rank] its
+ * own).  record: this rank's fp32 [rows, head_dim+2] as akv_decode_step_ex packs it; out: fp16 [rows, head_dim] as
+ * akv_lse_merge.  epoch: 1 for the first step, one more each step, the same on every rank.  The kernel stores the
+ * record into slot `rank` of every buffer, publishes the epoch (release, system scope), waits until its own buffer
+ * holds every rank's record of this epoch and merges.  The wait is bounded by timeout_ms (1..10000): when it runs
+ * out, the kernel raises the device error flag (bit 2, akv_device_error_flag), writes zeros to `out` and returns;
+ * the context stays usable.  Ranks must be launched on different GPUs: a rank's kernel waits for the others.
+ */
+#define AKV_PEER_HANDLE_BYTES 64
+long long akv_exchange_bytes(int n_ranks, int rows, int head_dim);
+int akv_peer_alloc(long long bytes, void** ptr, void* handle);
+int akv_peer_open(const void* handle, void** ptr);
+int akv_peer_close(void* ptr);
+int akv_peer_free(void* ptr);
+int akv_exchange_merge(void* const* bufs, int rank, int n_ranks, const void* record, void* out, int rows,
+                       int head_dim, unsigned int epoch, int timeout_ms, void* stream);
+
+/*
+ * akv_decode_step_ex over one shard of a sequence-sharded cache with that exchange inside the step's last kernel (no
+ * counterpart in the reference): the kernel that finishes a (batch, query head) row's packed record also stores it
+ * into every rank's exchange buffer, waits for the other ranks' records of the row and writes the merged row - no
+ * launch and no collective between the shard's result and the attention output.  Arguments as akv_decode_step_ex
+ * (packed_out: this shard's records, required; flags: AKV_STEP_ORDER_FREE / AKV_STEP_NO_APPEND as there), then the
+ * exchange as akv_exchange_merge; merged_out: fp16 [bsz, 1, n_kv_heads*group, head_dim], the same on every rank.
+ */
+int akv_decode_step_exchange(void* k_first_8, void* k_mid_4, void* k_last_4, void* v_first_8, void* v_mid_4,
+                             void* v_last_4, void* k_exp_max, void* v_exp_max, void* restk, void* restv, const void* q,
+                             const void* k_new, const void* v_new, void* merged_out, void* packed_out, void* scratch,
+                             long long scratch_bytes, int bsz, int n_kv_heads, int group, int head_dim, int max_seq_len,
+                             int rest_len, int rest_start, int flags, void* const* bufs, int rank, int n_ranks,
+                             unsigned int epoch, int timeout_ms, void* stream);
+
+/*
  * akv_decode_step for callers that cannot allocate device memory (no counterpart in the reference).
  * Same arguments and results as akv_decode_step, minus the workspace: it lives in a fixed array of
  * AKV_NOALLOC_SCRATCH_BYTES bytes of device global memory inside the library image, which every GPU that loads the

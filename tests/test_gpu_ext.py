@@ -8,6 +8,7 @@ Specification used for each:
                   dequantized value rounded once to fp16: max-norm relative error <= 1e-3.
   merge           numpy restatement of the weighted sum; max-norm relative error <= 1e-3.
 """
+import ctypes
 import math
 
 import numpy as np
@@ -353,6 +354,123 @@ def test_sequence_shards_merge_to_dense_attention(akv_lib):
     err = rel_err(got, truth)
     print(f"sequence-sharded merge vs fp32 dense attention: {err:.2e}")
     assert err <= 6e-2
+
+
+def _exchange_buffers(lib, R, rows, D):
+    """R exchange buffers of one process (stand-ins for the ranks' buffers), with views of their records and flags."""
+    W = D + 2
+    nbytes = lib.akv_exchange_bytes(R, rows, D)
+    data_bytes = (2 * R * rows * W * 4 + 127) // 128 * 128
+    assert nbytes == data_bytes + 2 * R * rows * 4
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(R)]
+    data = [b[:2 * R * rows * W * 4].view(torch.float32).view(2, R, rows, W) for b in bufs]
+    flags = [b[data_bytes:].view(torch.int32).view(2, R, rows) for b in bufs]
+    ptrs = (ctypes.c_void_p * R)(*[b.data_ptr() for b in bufs])
+    return bufs, data, flags, ptrs
+
+
+@pytest.mark.parametrize("R", [2, 3, 8])
+def test_exchange_merge_matches_lse_merge(akv_lib, R):
+    """akv_exchange_merge (publish to every rank's buffer, wait, merge) on one GPU: the other ranks' records and flags
+    are put into the buffers beforehand from the host side, so the launch never waits for another kernel.  The merged
+    rows equal akv_lse_merge over the same records bit for bit; this rank's record and flags reach every buffer; two
+    consecutive epochs use the two halves of the buffers."""
+    lib = akv_lib
+    rows, D = 12, 128
+    W = D + 2
+    gen = torch.Generator(device="cuda").manual_seed(5 + R)
+    bufs, data, flags, ptrs = _exchange_buffers(lib, R, rows, D)
+    for epoch in (1, 2, 3):
+        par = epoch & 1
+        rec = torch.randn(R, rows, W, device="cuda", generator=gen)
+        rec[:, :, 1] = rec[:, :, 1].abs() + 0.1
+        rec[R - 1, ::3, 1] = 0.0                                # shards without tokens in some rows
+        want = torch.empty((rows, D), dtype=torch.half, device="cuda")
+        check(lib, lib.akv_lse_merge(rec.data_ptr(), want.data_ptr(), R, rows, D, stream()))
+        for r in range(R):
+            for g in range(R):
+                if g != r:
+                    data[r][par, g] = rec[g]
+                    flags[r][par, g] = epoch
+            out = torch.full((rows, D), 7.0, dtype=torch.half, device="cuda")
+            check(lib, lib.akv_exchange_merge(ptrs, r, R, rec[r].contiguous().data_ptr(), out.data_ptr(), rows, D, epoch,
+                                              1000, stream()))
+            torch.cuda.synchronize()
+            assert torch.equal(out, want), f"rank {r} of {R}, epoch {epoch}"
+            for g in range(R):
+                assert torch.equal(data[g][par, r], rec[r]) and bool((flags[g][par, r] == epoch).all())
+    assert lib.akv_device_error_flag() == 0
+
+
+def test_exchange_wait_runs_out(akv_lib):
+    """A rank whose peer never publishes: the bounded wait of akv_exchange_merge runs out after the given time, the
+    kernel raises the device error flag, writes zeros and returns; the context stays usable and the flag clears."""
+    lib = akv_lib
+    R, rows, D = 2, 4, 128
+    bufs, data, flags, ptrs = _exchange_buffers(lib, R, rows, D)
+    rec = torch.ones(rows, D + 2, device="cuda")
+    out = torch.full((rows, D), 7.0, dtype=torch.half, device="cuda")
+    check(lib, lib.akv_exchange_merge(ptrs, 0, R, rec.data_ptr(), out.data_ptr(), rows, D, 1, 20, stream()))
+    torch.cuda.synchronize()
+    assert lib.akv_device_error_flag() & 4
+    assert bool((out == 0).all())
+    assert lib.akv_device_error_clear() == 0 and lib.akv_device_error_flag() == 0
+    data[0][1, 1] = rec                                          # now the peer's record and flags are there
+    flags[0][1, 1] = 1
+    check(lib, lib.akv_exchange_merge(ptrs, 0, R, rec.data_ptr(), out.data_ptr(), rows, D, 1, 20, stream()))
+    torch.cuda.synchronize()
+    assert lib.akv_device_error_flag() == 0 and bool((out == 1).all())
+
+
+class _LocalPeers:
+    """Stands in for `sharded.PeerExchange` when all the "ranks'" buffers live in this process."""
+
+    def __init__(self, ptrs, rank, world):
+        self.bufs, self.rank, self.world, self.timeout_ms, self.epoch = ptrs, rank, world, 1000, 0
+
+    def next_epoch(self):
+        self.epoch += 1
+        return self.epoch
+
+
+def test_decode_step_exchange_matches_merge(akv_lib):
+    """akv_decode_step_exchange (the exchange and the merge at the end of the step's last kernel) for every shard of a
+    sequence in turn, the other shards' records and flags put into the buffers beforehand: the merged output equals
+    akv_lse_merge over the records of plain packed steps bit for bit, and the shard's own record is returned as before."""
+    from alignedkv_b200.decode import DecodeLayer
+    from alignedkv_b200.sharded import shard_bounds
+    lib = akv_lib
+    B, H, D, S, R = 1, 4, 128, 2048 + 40, 3
+    rows = B * H
+    k, v, q = make_kvq(73, B, S + 1, H, D)
+    bounds = shard_bounds(S, R)
+
+    def shard(r):
+        lo, hi = bounds[r]
+        last = r == R - 1
+        layer = DecodeLayer(B, -(-(hi - lo + (1 if last else 0)) // 64) * 64, H, D, "cuda:0", v_mode="order_free")
+        layer.prefill(dev(k[:, lo:hi]), dev(v[:, lo:hi]))
+        return layer, ((dev(k[:, S:]), dev(v[:, S:])) if last else (None, None)), last
+
+    recs = []
+    for r in range(R):
+        layer, (kt, vt), last = shard(r)
+        recs.append(layer.decode(dev(q), kt, vt, append=last, packed=True))
+    gathered = torch.stack(recs).contiguous()
+    want = torch.empty((rows, D), dtype=torch.half, device="cuda")
+    check(lib, lib.akv_lse_merge(gathered.data_ptr(), want.data_ptr(), R, rows, D, stream()))
+    for r in range(R):
+        bufs, data, flags, ptrs = _exchange_buffers(lib, R, rows, D)
+        for g in range(R):
+            if g != r:
+                data[r][1, g] = recs[g]
+                flags[r][1, g] = 1
+        layer, (kt, vt), last = shard(r)
+        out = layer.decode(dev(q), kt, vt, append=last, exchange=_LocalPeers(ptrs, r, R))
+        torch.cuda.synchronize()
+        assert out.shape == (B, 1, H, D) and torch.equal(out.view(rows, D), want), f"shard {r}"
+        assert torch.equal(data[(r + 1) % R][1, r], recs[r])        # its record reached the other buffers
+    assert lib.akv_device_error_flag() == 0
 
 
 class _LoneComm:
