@@ -166,27 +166,26 @@ __device__ __forceinline__ uint32_t v_threshold_warp(const uint16_t* __restrict_
     return m;
 }
 
-// Log-sum-exp merge of one (batch, head) row over R shards (used by lse_merge_kernel and by the peer exchange kernel,
-// which must agree bit for bit).  Shard g's record (m, l, o[0..D-1]) lies at base + g * gs; out[d] = sum_g w_g o_g[d],
-// w_g = l_g exp(m_g - M) / sum_g' l_g' exp(m_g' - M), M = max_g m_g; shards with l = 0 are ignored.  Loads go past L1
-// (the records may have been written by another GPU during this kernel).
-__device__ __forceinline__ void lse_merge_row(const float* base, size_t gs, int R, int D, __half* out, int tid, int nthreads) {
+// Log-sum-exp merge of one (batch, head) row over R shards (used by lse_merge_kernel and by the peer exchange, which
+// must agree bit for bit).  ld(g, c) = float c of shard g's record (m, l, o[0..D-1]); out[d] = sum_g w_g o_g[d],
+// w_g = l_g exp(m_g - M) / sum_g' l_g' exp(m_g' - M), M = max_g m_g; shards with l = 0 are ignored.
+template <class Load>
+__device__ __forceinline__ void lse_merge_row(Load ld, int R, int D, __half* out, int tid, int nthreads) {
     float M = -INFINITY;
     for (int g = 0; g < R; ++g) {
-        const float l = __ldcg(base + g * gs + 1);
-        if (l > 0.f) M = fmaxf(M, __ldcg(base + g * gs));
+        const float l = ld(g, 1);
+        if (l > 0.f) M = fmaxf(M, ld(g, 0));
     }
     float denom = 0.f;
     for (int g = 0; g < R; ++g) {
-        const float l = __ldcg(base + g * gs + 1);
-        if (l > 0.f) denom += l * expf(__ldcg(base + g * gs) - M);
+        const float l = ld(g, 1);
+        if (l > 0.f) denom += l * expf(ld(g, 0) - M);
     }
     for (int d = tid; d < D; d += nthreads) {
         float v = 0.f;
         for (int g = 0; g < R; ++g) {
-            const float* row = base + g * gs;
-            const float l = __ldcg(row + 1);
-            if (l > 0.f) v += (l * expf(__ldcg(row) - M) / denom) * __ldcg(row + 2 + d);
+            const float l = ld(g, 1);
+            if (l > 0.f) v += (l * expf(ld(g, 0) - M) / denom) * ld(g, 2 + d);
         }
         out[d] = __float2half_rn(denom > 0.f ? v : 0.f);
     }

@@ -663,9 +663,11 @@ tail_kernel(const uint16_t* __restrict__ o_main, const float* __restrict__ o_mai
     }
     if (x.R > 0) {
         // sequence shards: the row's record goes to every rank and the merged row comes back (akv_exchange.cuh)
+        // (the residual sums' scratch is free by now and holds the collected records)
+        static_assert(XCHG_ROW_FLOATS <= 4 * 1024, "the collected row has to fit the residual scratch");
         __shared__ uint8_t* s_buf[XCHG_MAX_RANKS];
         __syncthreads();
-        exchange_merge_row(x, packed + (size_t)bhq * (D + 2), bhq, s_buf);
+        exchange_merge_row(x, packed + (size_t)bhq * (D + 2), bhq, s_buf, &part[0][0]);
     }
 }
 

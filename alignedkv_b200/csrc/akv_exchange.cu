@@ -11,7 +11,8 @@ __global__ void __launch_bounds__(128)
 exchange_merge_kernel(const XchgParams p, const float* __restrict__ rec) {
     pdl_enter();
     __shared__ uint8_t* s_buf[XCHG_MAX_RANKS];
-    exchange_merge_row(p, rec + (size_t)blockIdx.x * (p.D + 2), blockIdx.x, s_buf);
+    __shared__ float s_rec[XCHG_ROW_FLOATS];
+    exchange_merge_row(p, rec + (size_t)blockIdx.x * (p.D + 2), blockIdx.x, s_buf, s_rec);
 }
 
 int fill_exchange(XchgParams* p, void* const* bufs, int rank, int n_ranks, void* out, int rows, int head_dim,
@@ -19,7 +20,8 @@ int fill_exchange(XchgParams* p, void* const* bufs, int rank, int n_ranks, void*
     AKV_REQUIRE(bufs && out, AKV_ERR_NULL, "exchange: null pointer");
     AKV_REQUIRE(n_ranks >= 1 && n_ranks <= XCHG_MAX_RANKS && rank >= 0 && rank < n_ranks, AKV_ERR_SHAPE,
                 "exchange: rank %d of %d (at most %d ranks)", rank, n_ranks, XCHG_MAX_RANKS);
-    AKV_REQUIRE(rows > 0 && head_dim > 0, AKV_ERR_SHAPE, "exchange: bad extent (%d rows, head_dim %d)", rows, head_dim);
+    AKV_REQUIRE(rows > 0 && head_dim > 0 && head_dim <= XCHG_MAX_D, AKV_ERR_SHAPE,
+                "exchange: bad extent (%d rows, head_dim %d [at most %d])", rows, head_dim, XCHG_MAX_D);
     AKV_REQUIRE(epoch != 0, AKV_ERR_SHAPE, "exchange: epoch 0 is the buffers' initial state");
     AKV_REQUIRE(timeout_ms > 0 && timeout_ms <= 10000, AKV_ERR_SHAPE, "exchange: timeout of %d ms", timeout_ms);
     for (int g = 0; g < XCHG_MAX_RANKS; ++g) {
@@ -59,8 +61,8 @@ cudaError_t exchange_error_clear() {
 using namespace akv;
 
 extern "C" long long akv_exchange_bytes(int n_ranks, int rows, int head_dim) {
-    if (n_ranks < 1 || n_ranks > XCHG_MAX_RANKS || rows < 1 || head_dim < 1) return -1;
-    return (long long)(exchange_data_bytes(n_ranks, rows, head_dim) + (size_t)2 * n_ranks * rows * sizeof(uint32_t));
+    if (n_ranks < 1 || n_ranks > XCHG_MAX_RANKS || rows < 1 || head_dim < 1 || head_dim > XCHG_MAX_D) return -1;
+    return (long long)exchange_buffer_bytes(n_ranks, rows, head_dim);
 }
 
 extern "C" int akv_peer_alloc(long long bytes, void** ptr, void* handle) {

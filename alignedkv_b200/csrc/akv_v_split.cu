@@ -282,7 +282,8 @@ __global__ void __launch_bounds__(128)
 lse_merge_kernel(const float* __restrict__ packed, __half* __restrict__ out, int R, int rows, int D) {
     const int i = blockIdx.x;
     const int W = D + 2;
-    lse_merge_row(packed + (size_t)i * W, (size_t)rows * W, R, D, out + (size_t)i * D, threadIdx.x, blockDim.x);
+    lse_merge_row([&](int g, int c) { return packed[((size_t)g * rows + i) * W + c]; }, R, D, out + (size_t)i * D,
+                  threadIdx.x, blockDim.x);
 }
 
 int launch_lse_merge(const float* packed, uint8_t* out, int R, int rows, int D, cudaStream_t st) {

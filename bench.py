@@ -49,6 +49,9 @@ WORKLOADS = {
     # one rank's shard of that sequence on 8 ranks, by itself (what a sharded step costs without its exchange)
     "long-context-decode-shard8": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=16384,
                                        sharding="replicate", v_mode="order_free"),
+    # a quarter of that sequence: on 2 GPUs every rank holds what a rank of the full workload holds on 8
+    "long-context-decode-32k": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=32768, sharding="sequence",
+                                    v_mode="order_free"),
     # the same with the four-phase step whose read decisions are those of one device holding the whole sequence
     "long-context-decode-exact": dict(batch=1, heads=32, kv_heads=32, head_dim=128, cache_len=131072,
                                       sharding="sequence_exact", v_mode="order_free"),

@@ -249,15 +249,16 @@ int akv_lse_merge(const void* packed, void* out, int n_ranks, int rows, int head
  *   akv_peer_open    another process's buffer, by the handle that process got (CUDA IPC; the address is valid in the
  *                    calling process only; peer access between the two GPUs is enabled on first use);
  *   akv_peer_close / akv_peer_free   undo the two (close every mapping of a buffer before its owner frees it).
- * Buffer layout for R ranks, rows = B*Hq, W = head_dim + 2: float data[2][R][rows][W] (slot g written by rank g, two
- * epochs deep), then from the next multiple of 128 bytes uint32 flags[2][R][rows] (the epoch whose record is there).
+ * Buffer layout for R ranks, rows = B*Hq, W = head_dim + 2 (head_dim at most 256): 8-byte words [2][R][rows][W], a word
+ * = (the bits of one float of a record, the epoch it belongs to); slot g is written by rank g; two epochs deep (index
+ * epoch & 1).  A float and its flag travel in one aligned 8-byte store, which is atomic, so neither side needs a fence.
  * akv_exchange_merge(bufs, rank, ...): bufs[g] = the calling process's address of rank g's buffer (bufs[rank] its
  * own).  record: this rank's fp32 [rows, head_dim+2] as akv_decode_step_ex packs it; out: fp16 [rows, head_dim] as
  * akv_lse_merge.  epoch: 1 for the first step, one more each step, the same on every rank.  The kernel stores the
- * record into slot `rank` of every buffer, publishes the epoch (release, system scope), waits until its own buffer
- * holds every rank's record of this epoch and merges.  The wait is bounded by timeout_ms (1..10000): when it runs
- * out, the kernel raises the device error flag (bit 2, akv_device_error_flag), writes zeros to `out` and returns;
- * the context stays usable.  Ranks must be launched on different GPUs: a rank's kernel waits for the others.
+ * record's words into slot `rank` of every buffer, reads the words of all ranks from its own buffer until each carries
+ * the epoch, and merges.  The wait is bounded by timeout_ms (1..10000): when it runs out, the kernel raises the device
+ * error flag (bit 2, akv_device_error_flag), writes zeros to `out` and returns; the context stays usable.  Ranks must
+ * be launched on different GPUs: a rank's kernel waits for the others.
  */
 #define AKV_PEER_HANDLE_BYTES 64
 long long akv_exchange_bytes(int n_ranks, int rows, int head_dim);

@@ -357,22 +357,28 @@ def test_sequence_shards_merge_to_dense_attention(akv_lib):
 
 
 def _exchange_buffers(lib, R, rows, D):
-    """R exchange buffers of one process (stand-ins for the ranks' buffers), with views of their records and flags."""
+    """R exchange buffers of one process (stand-ins for the ranks' buffers): words [2][R][rows][D+2] of (float bits,
+    epoch), with a float view (values at [..., 0]) and an int view (epochs at [..., 1]) of each."""
     W = D + 2
     nbytes = lib.akv_exchange_bytes(R, rows, D)
-    data_bytes = (2 * R * rows * W * 4 + 127) // 128 * 128
-    assert nbytes == data_bytes + 2 * R * rows * 4
+    assert nbytes == 2 * R * rows * W * 8
     bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(R)]
-    data = [b[:2 * R * rows * W * 4].view(torch.float32).view(2, R, rows, W) for b in bufs]
-    flags = [b[data_bytes:].view(torch.int32).view(2, R, rows) for b in bufs]
+    data = [b.view(torch.float32).view(2, R, rows, W, 2) for b in bufs]
+    flags = [b.view(torch.int32).view(2, R, rows, W, 2) for b in bufs]
     ptrs = (ctypes.c_void_p * R)(*[b.data_ptr() for b in bufs])
     return bufs, data, flags, ptrs
 
 
+def _place(data, flags, r, par, g, rec, epoch):
+    """Puts rank g's record and its epoch into rank r's buffer, as rank g's kernel would have."""
+    data[r][par, g, :, :, 0] = rec
+    flags[r][par, g, :, :, 1] = epoch
+
+
 @pytest.mark.parametrize("R", [2, 3, 8])
 def test_exchange_merge_matches_lse_merge(akv_lib, R):
-    """akv_exchange_merge (publish to every rank's buffer, wait, merge) on one GPU: the other ranks' records and flags
-    are put into the buffers beforehand from the host side, so the launch never waits for another kernel.  The merged
+    """akv_exchange_merge (publish to every rank's buffer, collect, merge) on one GPU: the other ranks' records (every
+    float with its epoch) are put into the buffers beforehand from the host side, so the launch never waits for another kernel.  The merged
     rows equal akv_lse_merge over the same records bit for bit; this rank's record and flags reach every buffer; two
     consecutive epochs use the two halves of the buffers."""
     lib = akv_lib
@@ -390,15 +396,14 @@ def test_exchange_merge_matches_lse_merge(akv_lib, R):
         for r in range(R):
             for g in range(R):
                 if g != r:
-                    data[r][par, g] = rec[g]
-                    flags[r][par, g] = epoch
+                    _place(data, flags, r, par, g, rec[g], epoch)
             out = torch.full((rows, D), 7.0, dtype=torch.half, device="cuda")
             check(lib, lib.akv_exchange_merge(ptrs, r, R, rec[r].contiguous().data_ptr(), out.data_ptr(), rows, D, epoch,
                                               1000, stream()))
             torch.cuda.synchronize()
             assert torch.equal(out, want), f"rank {r} of {R}, epoch {epoch}"
             for g in range(R):
-                assert torch.equal(data[g][par, r], rec[r]) and bool((flags[g][par, r] == epoch).all())
+                assert torch.equal(data[g][par, r, :, :, 0], rec[r]) and bool((flags[g][par, r, :, :, 1] == epoch).all())
     assert lib.akv_device_error_flag() == 0
 
 
@@ -415,8 +420,7 @@ def test_exchange_wait_runs_out(akv_lib):
     assert lib.akv_device_error_flag() & 4
     assert bool((out == 0).all())
     assert lib.akv_device_error_clear() == 0 and lib.akv_device_error_flag() == 0
-    data[0][1, 1] = rec                                          # now the peer's record and flags are there
-    flags[0][1, 1] = 1
+    _place(data, flags, 0, 1, 1, rec, 1)                         # now the peer's record is there
     check(lib, lib.akv_exchange_merge(ptrs, 0, R, rec.data_ptr(), out.data_ptr(), rows, D, 1, 20, stream()))
     torch.cuda.synchronize()
     assert lib.akv_device_error_flag() == 0 and bool((out == 1).all())
@@ -463,13 +467,12 @@ def test_decode_step_exchange_matches_merge(akv_lib):
         bufs, data, flags, ptrs = _exchange_buffers(lib, R, rows, D)
         for g in range(R):
             if g != r:
-                data[r][1, g] = recs[g]
-                flags[r][1, g] = 1
+                _place(data, flags, r, 1, g, recs[g], 1)
         layer, (kt, vt), last = shard(r)
         out = layer.decode(dev(q), kt, vt, append=last, exchange=_LocalPeers(ptrs, r, R))
         torch.cuda.synchronize()
         assert out.shape == (B, 1, H, D) and torch.equal(out.view(rows, D), want), f"shard {r}"
-        assert torch.equal(data[(r + 1) % R][1, r], recs[r])        # its record reached the other buffers
+        assert torch.equal(data[(r + 1) % R][1, r, :, :, 0], recs[r])        # its record reached the other buffers
     assert lib.akv_device_error_flag() == 0
 
 
