@@ -473,6 +473,18 @@ def measure(name, args, ctx, min_seconds):
     check["device_error_flag"] = int(flag.item())
     if check["device_error_flag"] != 0:
         raise SystemExit("bench: a bounded wait inside a kernel gave up during the run (akv_device_error_flag != 0)")
+    if seq is not None and world > 1:
+        # sequence shards: no rank can check the output against the whole sequence, but every rank must hold the SAME
+        # merged output, finite and not zero (a wait that ran out, or a record that did not arrive, shows here)
+        mine = out_last.float().flatten().contiguous()
+        first = mine.clone()
+        dist.broadcast(first, src=0)
+        same = torch.tensor([int(torch.equal(mine, first) and bool(torch.isfinite(mine).all()) and
+                                 float(mine.abs().max()) > 0.0)], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        check["sharded_outputs_identical"] = bool(same.item())
+        if not check["sharded_outputs_identical"]:
+            raise SystemExit("bench: the ranks of a sequence-sharded step do not hold the same finite non-zero output")
     for key_, bound in (("exact_vs_ref_kernel", 1e-3), ("step_output_vs_fp32_dense", 0.1)):
         if check["accuracy"].get(key_) is not None and check["accuracy"][key_] > bound:
             raise SystemExit(f"bench: {key_} = {check['accuracy'][key_]:.3e} exceeds {bound}")
@@ -549,7 +561,8 @@ def measure(name, args, ctx, min_seconds):
         "gpu_launches": launches,
         "clocks": clocks,
         "accuracy": check["accuracy"],
-        "validation": {"device_error_flag": check["device_error_flag"], "note": check["note"]},
+        "validation": {"device_error_flag": check["device_error_flag"], "note": check["note"],
+                       "sharded_outputs_identical": check.get("sharded_outputs_identical")},
         "ref_cuda_kernels_us": check["ref_cuda_kernels_us"],
     }
 
