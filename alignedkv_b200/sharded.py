@@ -178,11 +178,13 @@ class SequenceShardedDecoder:
     exchange: "peer" (records exchanged through peer memory and merged at the end of the step's last kernel),
     "peer_unfused" (the same exchange as a kernel of its own after the step), "collective" (all-gather + merge
     kernel) or "auto": peer memory with the CUDA backend on 2..8 ranks when it can be set up on all of them, else the
-    collective; `self.exchange` says which one runs."""
+    collective; `self.exchange` says which one runs.  With peer memory a rank's step waits inside its last kernel for
+    the other ranks' results for at most `exchange_timeout_ms` (then: zeros, and bit 2 of `akv_device_error_flag()`):
+    the ranks have to reach every step within that time of each other."""
 
     def __init__(self, bsz: int, prompt_len: int, max_new_tokens: int, n_kv_heads: int, head_dim: int, device,
                  n_q_heads: int | None = None, v_mode: str = "order_free", group=None, backend=None,
-                 exchange: str = "auto"):
+                 exchange: str = "auto", exchange_timeout_ms: int = 2000):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -206,7 +208,7 @@ class SequenceShardedDecoder:
                                             and torch.device(device).type == "cuda")
         if wants_peer and self.world > 1:
             try:
-                self.peer = PeerExchange(bsz * self.Hq, head_dim, device, group)
+                self.peer = PeerExchange(bsz * self.Hq, head_dim, device, group, exchange_timeout_ms)
             except RuntimeError as e:                 # (raised on every rank alike)
                 if exchange != "auto":
                     raise

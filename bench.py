@@ -383,6 +383,7 @@ def measure(name, args, ctx, min_seconds):
         CUDA events; repeated until `seconds` of device time have been measured (at least 3 blocks).  Returns, per
         block, the MAX over the ranks of the block's time, every rank's own times (on rank 0), and the library's
         launch count per block."""
+        barrier()          # (ranks whose steps wait for each other start their warm-up together)
         for _ in range(warmup):
             stepper(fn)
         own, worst, counts = [], [], []
