@@ -61,6 +61,9 @@ def _worker(rank, world, port, results):
         lo, hi = shard_bounds(S, world)[rank]
         max_local = -(-(hi - lo + (steps if rank == world - 1 else 0)) // 64) * 64
         dec = SequenceShardedDecoder(B, S, steps, H, D, "cpu", backend=NumpyBackend(B, max(64, max_local), H, D))
+        # (a backend of the caller's and CPU tensors: the records meet through the process group's all-gather, never
+        # through peer memory)
+        assert dec.exchange == "collective" and dec.peer is None
         dec.prefill(torch.from_numpy(k[:, lo:hi].copy()), torch.from_numpy(v[:, lo:hi].copy()))
         errs = []
         for i in range(steps):
