@@ -22,6 +22,10 @@ int fill_exchange(XchgParams* p, void* const* bufs, int rank, int n_ranks, void*
                 "exchange: rank %d of %d (at most %d ranks)", rank, n_ranks, XCHG_MAX_RANKS);
     AKV_REQUIRE(rows > 0 && head_dim > 0 && head_dim <= XCHG_MAX_D, AKV_ERR_SHAPE,
                 "exchange: bad extent (%d rows, head_dim %d [at most %d])", rows, head_dim, XCHG_MAX_D);
+    // every row's CTA has to be resident at once on every rank: a CTA that waits for a peer's row whose CTA waits for
+    // a free SM behind CTAs that in turn wait for this rank could only end by the time limit
+    AKV_REQUIRE(rows <= 2 * sm_count(), AKV_ERR_SHAPE, "exchange: %d rows are more than two per SM (%d SMs)", rows,
+                sm_count());
     AKV_REQUIRE(epoch != 0, AKV_ERR_SHAPE, "exchange: epoch 0 is the buffers' initial state");
     AKV_REQUIRE(timeout_ms > 0 && timeout_ms <= 10000, AKV_ERR_SHAPE, "exchange: timeout of %d ms", timeout_ms);
     for (int g = 0; g < XCHG_MAX_RANKS; ++g) {

@@ -98,6 +98,11 @@ class PeerExchange:
         self.mapped = []
         if self.world > self.MAX_RANKS:
             raise ValueError(f"peer exchange covers at most {self.MAX_RANKS} ranks, the group has {self.world}")
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        if rows > 2 * sms or head_dim > 256:
+            # (every row's CTA must be resident at once, and the collected row lives in shared memory; the same on
+            # every rank, so all of them take the other path together)
+            raise RuntimeError(f"peer exchange serves at most {2 * sms} rows of head_dim <= 256, not {rows} x {head_dim}")
         nbytes = self.lib.akv_exchange_bytes(self.world, rows, head_dim)
         handle = (ctypes.c_ubyte * 64)()
         own = ctypes.c_void_p()

@@ -249,6 +249,7 @@ int akv_lse_merge(const void* packed, void* out, int n_ranks, int rows, int head
  *   akv_peer_open    another process's buffer, by the handle that process got (CUDA IPC; the address is valid in the
  *                    calling process only; peer access between the two GPUs is enabled on first use);
  *   akv_peer_close / akv_peer_free   undo the two (close every mapping of a buffer before its owner frees it).
+ * Limits: head_dim at most 256, and at most two rows per SM (every row's CTA has to be resident at once).
  * Buffer layout for R ranks, rows = B*Hq, W = head_dim + 2 (head_dim at most 256): 8-byte words [2][R][rows][W], a word
  * = (the bits of one float of a record, the epoch it belongs to); slot g is written by rank g; two epochs deep (index
  * epoch & 1).  A float and its flag travel in one aligned 8-byte store, which is atomic, so neither side needs a fence.
