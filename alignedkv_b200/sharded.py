@@ -81,7 +81,7 @@ class _CudaBackend:
 class PeerExchange:
     """Exchange buffers of the ranks of `group` for `akv_exchange_merge`: every rank allocates one, the 64-byte IPC
     handles travel through one all-gather, every rank maps the others' buffers.  All ranks must sit on GPUs of one
-    node with peer access to each other.  `setup` raises on EVERY rank when it failed on any of them."""
+    node with peer access to each other.  The constructor raises on EVERY rank when the set-up failed on any of them."""
 
     MAX_RANKS = 8
 
@@ -209,8 +209,9 @@ class SequenceShardedDecoder:
             raise ValueError(f"exchange must be 'auto', 'peer', 'peer_unfused' or 'collective', not {exchange!r}")
         self.peer = None
         self.exchange_note = ""
-        wants_peer = exchange in ("peer", "peer_unfused") or (exchange == "auto" and backend is None and 2 <= self.world <= PeerExchange.MAX_RANKS
-                                            and torch.device(device).type == "cuda")
+        wants_peer = exchange in ("peer", "peer_unfused") or (
+            exchange == "auto" and backend is None and 2 <= self.world <= PeerExchange.MAX_RANKS and
+            torch.device(device).type == "cuda")
         if wants_peer and self.world > 1:
             try:
                 self.peer = PeerExchange(bsz * self.Hq, head_dim, device, group, exchange_timeout_ms)
